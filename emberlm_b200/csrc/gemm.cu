@@ -1,0 +1,142 @@
+// ctdk_gemm / ctdk_bmm entry points and the exact-fp32 SIMT kernel used for shapes the
+// tensor-core path cannot take (leading dimensions that are not multiples of 4 floats,
+// unaligned pointers, N < 8) or when CTDK_GEMM_FP32_SIMT is requested.
+#include "common.cuh"
+
+namespace ctdk {
+
+int gemm_tcgen05(const float* A, const float* B, float* C, int64_t M, int64_t N, int64_t K,
+                 int64_t lda, int64_t ldb, int64_t ldc, int transa, int transb, int epilogue,
+                 const float* aux, cudaStream_t stream);
+int gemm_3xtf32(const float* A, const float* B, float* C, int64_t M, int64_t N, int64_t K,
+                int64_t lda, int64_t ldb, int64_t ldc, int transa, int transb, int epilogue,
+                const float* aux, cudaStream_t stream);
+
+namespace {
+
+constexpr int TS = 64;  // C tile
+constexpr int TK = 16;
+
+// 256 threads, each owns a 4x4 block of the 64x64 tile. fp32 FMA, k ascending.
+__global__ void __launch_bounds__(256)
+    gemm_simt_kernel(const float* __restrict__ A, const float* __restrict__ B,
+                     float* __restrict__ C, const float* __restrict__ aux, int64_t M, int64_t N,
+                     int64_t K, int64_t lda, int64_t ldb, int64_t ldc, int transa, int transb,
+                     int epilogue) {
+  __shared__ float As[TK][TS + 1];
+  __shared__ float Bs[TK][TS + 1];
+  const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+  const int64_t m0 = static_cast<int64_t>(blockIdx.y) * TS, n0 = static_cast<int64_t>(blockIdx.x) * TS;
+  float acc[4][4] = {};
+  for (int64_t k0 = 0; k0 < K; k0 += TK) {
+    for (int i = threadIdx.x; i < TS * TK; i += 256) {
+      const int kk = i % TK, mm = i / TK;
+      const int64_t gm = m0 + mm, gk = k0 + kk;
+      float va = 0.0f;
+      if (gm < M && gk < K) va = transa ? A[gk * lda + gm] : A[gm * lda + gk];
+      As[kk][mm] = va;
+      const int64_t gn = n0 + mm;
+      float vb = 0.0f;
+      if (gn < N && gk < K) vb = transb ? B[gn * ldb + gk] : B[gk * ldb + gn];
+      Bs[kk][mm] = vb;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int kk = 0; kk < TK; ++kk) {
+      float a[4], b[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        a[i] = As[kk][ty * 4 + i];
+        b[i] = Bs[kk][tx * 4 + i];
+      }
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int64_t gm = m0 + ty * 4 + i;
+    if (gm >= M) continue;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int64_t gn = n0 + tx * 4 + j;
+      if (gn >= N) continue;
+      float r = acc[i][j];
+      if (epilogue == CTDK_EPI_ACCUMULATE) r += C[gm * ldc + gn];
+      else if (epilogue == CTDK_EPI_RESIDUAL) r += aux[gm * ldc + gn];
+      C[gm * ldc + gn] = r;
+    }
+  }
+}
+
+__global__ void fill_rows_kernel(float* C, const float* aux, int64_t M, int64_t N, int64_t ldc,
+                                 int epilogue) {
+  const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= M * N) return;
+  const int64_t r = i / N, c = i - r * N;
+  if (epilogue == CTDK_EPI_STORE) C[r * ldc + c] = 0.0f;
+  else if (epilogue == CTDK_EPI_RESIDUAL) C[r * ldc + c] = aux[r * ldc + c];
+}
+
+}  // namespace
+}  // namespace ctdk
+
+using namespace ctdk;
+
+extern "C" {
+
+int ctdk_gemm(const float* A, const float* B, float* C, int64_t M, int64_t N, int64_t K,
+              int64_t lda, int64_t ldb, int64_t ldc, int transa, int transb, int precision,
+              int epilogue, const float* aux, void* stream) {
+  CTDK_REQUIRE(M >= 0 && N >= 0 && K >= 0, "ctdk_gemm: negative dimension");
+  CTDK_REQUIRE(epilogue == CTDK_EPI_STORE || epilogue == CTDK_EPI_ACCUMULATE ||
+                   epilogue == CTDK_EPI_RESIDUAL,
+               "ctdk_gemm: unknown epilogue %d", epilogue);
+  CTDK_REQUIRE(precision == CTDK_GEMM_TF32 || precision == CTDK_GEMM_3XTF32 ||
+                   precision == CTDK_GEMM_FP32_SIMT,
+               "ctdk_gemm: unknown precision %d", precision);
+  if (M == 0 || N == 0) return CTDK_OK;
+  CTDK_REQUIRE(C != nullptr, "ctdk_gemm: null C");
+  CTDK_REQUIRE(epilogue != CTDK_EPI_RESIDUAL || aux != nullptr, "ctdk_gemm: residual needs aux");
+  CTDK_REQUIRE(ldc >= N, "ctdk_gemm: ldc < N");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (K == 0) {
+    if (epilogue != CTDK_EPI_ACCUMULATE) {
+      fill_rows_kernel<<<ceil_div(M * N, 256), 256, 0, s>>>(C, aux, M, N, ldc, epilogue);
+      return check_launch("ctdk_gemm(K=0)");
+    }
+    return CTDK_OK;
+  }
+  CTDK_REQUIRE(A && B, "ctdk_gemm: null operand");
+  CTDK_REQUIRE(lda >= (transa ? M : K), "ctdk_gemm: lda too small");
+  CTDK_REQUIRE(ldb >= (transb ? K : N), "ctdk_gemm: ldb too small");
+  if (precision != CTDK_GEMM_FP32_SIMT) {
+    int rc = (precision == CTDK_GEMM_3XTF32)
+                 ? gemm_3xtf32(A, B, C, M, N, K, lda, ldb, ldc, transa, transb, epilogue, aux, s)
+                 : gemm_tcgen05(A, B, C, M, N, K, lda, ldb, ldc, transa, transb, epilogue, aux,
+                                s);
+    if (rc <= 0) return rc;  // enqueued, or a real error
+  }
+  dim3 grid(static_cast<unsigned>((N + TS - 1) / TS), static_cast<unsigned>((M + TS - 1) / TS));
+  CTDK_REQUIRE(grid.y <= 65535u, "ctdk_gemm: M too large for the SIMT path");
+  gemm_simt_kernel<<<grid, 256, 0, s>>>(A, B, C, aux, M, N, K, lda, ldb, ldc, transa, transb,
+                                        epilogue);
+  return check_launch("ctdk_gemm(simt)");
+}
+
+int ctdk_bmm(const float* A, const float* B, float* C, int64_t batch, int64_t M, int64_t N,
+             int64_t K, int transa, int transb, int precision, void* stream) {
+  CTDK_REQUIRE(batch >= 0 && M >= 0 && N >= 0 && K >= 0, "ctdk_bmm: negative dimension");
+  const int64_t lda = transa ? M : K, ldb = transb ? K : N;
+  for (int64_t b = 0; b < batch; ++b) {
+    int rc = ctdk_gemm(A + b * M * K, B + b * K * N, C + b * M * N, M, N, K, lda, ldb, N,
+                       transa, transb, precision, CTDK_EPI_STORE, nullptr, stream);
+    if (rc != CTDK_OK) return rc;
+  }
+  return CTDK_OK;
+}
+
+}  // extern "C"

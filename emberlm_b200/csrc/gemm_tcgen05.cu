@@ -1,0 +1,430 @@
+// TF32 GEMM on the 5th-generation tensor cores: C[M,N] = op(A)·op(B) with fp32 operands in
+// HBM, fp32 accumulators in tensor memory.
+//
+// One persistent CTA per SM, 6 warps:
+//   warp 0   TMA producer: fills a ring of shared-memory stages (128-byte swizzled tiles),
+//            one elected lane, plain (non-multicast) cp.async.bulk.tensor loads.
+//   warp 1   MMA issuer: one elected lane issues tcgen05.mma.kind::tf32 (M=128, N=BN, K=8)
+//            four times per 32-float stage and releases the stage with tcgen05.commit.
+//   warps 2-5 epilogue: read the accumulator with tcgen05.ld (each warp owns one 32-lane
+//            quarter of tensor memory) and write C. Two accumulator buffers let the epilogue
+//            of tile i overlap the main loop of tile i+1.
+// Operands that are contiguous along K are loaded as one box {32 floats, rows}; operands
+// contiguous along M or N (the transposed cases of the reference's matmul, emberlm
+// src/ops/matmul.cpp:25-47,99-118) are loaded as {32 floats of M/N, 32 rows of K} boxes and
+// described to the tensor core as MN-major. M, N and K tails are zero-filled by TMA bounds
+// checking; the epilogue predicates stores. Every mbarrier wait is bounded.
+#include <cuda.h>
+#include <cudaTypedefs.h>
+
+#include <cstdlib>
+#include <mutex>
+
+#include "common.cuh"
+
+namespace ctdk {
+namespace {
+
+constexpr int BM = 128;
+constexpr int BK = 32;                    // floats per stage along K = one 128-byte swizzle row
+constexpr int kATileBytes = BM * BK * 4;  // 16 KB
+constexpr int kChunkBytes = 32 * BK * 4;  // 4 KB: one {32 x 32} box of an MN-major operand
+constexpr int kThreads = 192;
+constexpr int kGroupM = 16;               // m-blocks per scheduling group (L2 reuse of B tiles)
+
+template <int BN>
+struct Cfg {
+  static constexpr int kBTileBytes = BN * BK * 4;
+  static constexpr int kStageBytes = kATileBytes + kBTileBytes;
+  static constexpr int kStages = (BN == 256) ? 4 : (BN == 128 ? 6 : 8);
+  static constexpr int kTmemCols = 2 * BN;  // two accumulator buffers
+  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*align*/ + 256 /*barriers*/;
+};
+
+struct GemmArgs {
+  float* C;
+  const float* aux;
+  int64_t ldc;
+  int M, N, K;
+  int epilogue;
+  int vec_ok;  // C (and aux) rows are 16-byte aligned and N%4==0
+  int* status;
+};
+
+// Instruction descriptor for kind::tf32: D=F32 (bit 4), A,B=TF32 (value 2 at bits 7 and 10),
+// major-ness bits 15/16 (0 = K-major, 1 = MN-major), N>>3 at bit 17, M>>4 at bit 24.
+__host__ __device__ constexpr uint32_t make_idesc(bool a_mn, bool b_mn, int n) {
+  return (1u << 4) | (2u << 7) | (2u << 10) | (static_cast<uint32_t>(a_mn) << 15) |
+         (static_cast<uint32_t>(b_mn) << 16) | (static_cast<uint32_t>(n >> 3) << 17) |
+         (static_cast<uint32_t>(BM >> 4) << 24);
+}
+
+__device__ __forceinline__ void tile_coords(int tile, int m_blocks, int n_blocks, int& mb,
+                                            int& nb) {
+  const int per_group = kGroupM * n_blocks;
+  const int g = tile / per_group;
+  const int first_m = g * kGroupM;
+  const int gm = min(kGroupM, m_blocks - first_m);
+  const int local = tile - g * per_group;
+  mb = first_m + local % gm;
+  nb = local / gm;
+}
+
+template <int BN, bool A_MN, bool B_MN>
+__global__ void __launch_bounds__(kThreads, 1)
+    gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmA,
+                     const __grid_constant__ CUtensorMap tmB, const GemmArgs args) {
+  using C = Cfg<BN>;
+  extern __shared__ unsigned char smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  unsigned char* smem = smem_raw + ((1024u - (raw & 1023u)) & 1023u);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::kStages * C::kStageBytes);
+  uint64_t* full = bars;                      // [kStages]
+  uint64_t* empty = bars + C::kStages;        // [kStages]
+  uint64_t* tfull = bars + 2 * C::kStages;    // [2]
+  uint64_t* tempty = tfull + 2;               // [2]
+  uint64_t* final_bar = tempty + 2;           // [1]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(final_bar + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int m_blocks = (args.M + BM - 1) / BM;
+  const int n_blocks = (args.N + BN - 1) / BN;
+  const int num_tiles = m_blocks * n_blocks;
+  const int k_blocks = (args.K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < C::kStages; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&tfull[a], 1);
+      mbar_init(&tempty[a], 4);
+    }
+    mbar_init(final_bar, 1);
+    mbar_fence_init();
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmB);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, C::kTmemCols);
+    tmem_relinquish();
+    tc_fence_before();
+  }
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------- TMA producer -------------------------------
+    if (lane == 0) {
+      int s = 0;
+      uint32_t ph = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        int mb, nb;
+        tile_coords(tile, m_blocks, n_blocks, mb, nb);
+        const int m0 = mb * BM, n0 = nb * BN;
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          if (!mbar_wait_bounded(&empty[s], ph ^ 1u, args.status, 1)) {
+            ok = false;
+            break;
+          }
+          unsigned char* a_dst = smem + s * C::kStageBytes;
+          unsigned char* b_dst = a_dst + kATileBytes;
+          mbar_expect_tx(&full[s], C::kStageBytes);
+          const int k0 = kb * BK;
+          if (A_MN) {
+#pragma unroll
+            for (int c = 0; c < BM / 32; ++c)
+              tma_load_2d(a_dst + c * kChunkBytes, &tmA, &full[s], m0 + 32 * c, k0);
+          } else {
+            tma_load_2d(a_dst, &tmA, &full[s], k0, m0);
+          }
+          if (B_MN) {
+#pragma unroll
+            for (int c = 0; c < BN / 32; ++c)
+              tma_load_2d(b_dst + c * kChunkBytes, &tmB, &full[s], n0 + 32 * c, k0);
+          } else {
+            tma_load_2d(b_dst, &tmB, &full[s], k0, n0);
+          }
+          if (++s == C::kStages) {
+            s = 0;
+            ph ^= 1u;
+          }
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ------------------------------- MMA issuer -------------------------------
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc(A_MN, B_MN, BN);
+      int s = 0;
+      uint32_t ph = 0;
+      bool ok = true;
+      int it = 0;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++it) {
+        const int acc = it & 1;
+        const uint32_t acc_ph = (static_cast<uint32_t>(it) >> 1) & 1u;
+        if (!mbar_wait_bounded(&tempty[acc], acc_ph ^ 1u, args.status, 2)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BN);
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          if (!mbar_wait_bounded(&full[s], ph, args.status, 3)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t a_addr = smem_u32(smem + s * C::kStageBytes);
+          const uint32_t b_addr = a_addr + kATileBytes;
+#pragma unroll
+          for (int ks = 0; ks < BK / 8; ++ks) {
+            // K-major: the 8-float k-slice starts 32 bytes further inside the swizzled row;
+            // rows are 128 bytes apart, 8-row groups 1024 bytes apart (SBO).
+            // MN-major: the 8 k-rows of a slice are one 1024-byte group; the 32-float chunks
+            // along M/N are kChunkBytes apart (LBO).
+            const uint64_t adesc = A_MN ? make_sw128_desc(a_addr + ks * 1024, kChunkBytes, 1024)
+                                        : make_sw128_desc(a_addr + ks * 32, 16, 1024);
+            const uint64_t bdesc = B_MN ? make_sw128_desc(b_addr + ks * 1024, kChunkBytes, 1024)
+                                        : make_sw128_desc(b_addr + ks * 32, 16, 1024);
+            umma_tf32(d_tmem, adesc, bdesc, idesc, (kb | ks) != 0 ? 1u : 0u);
+          }
+          umma_commit(&empty[s]);  // stage is free once these MMAs have read it
+          if (++s == C::kStages) {
+            s = 0;
+            ph ^= 1u;
+          }
+        }
+        if (ok) umma_commit(&tfull[acc]);  // accumulator complete
+      }
+      // All MMAs retired before tensor memory is released.
+      umma_commit(final_bar);
+      mbar_wait_bounded(final_bar, 0, args.status, 4);
+    }
+    __syncwarp();
+  } else {
+    // ------------------------------- epilogue -------------------------------
+    const int q = warp & 3;  // tensor-memory lane quarter this warp may access
+    const int row_in_tile = q * 32 + lane;
+    int it = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++it) {
+      int mb, nb;
+      tile_coords(tile, m_blocks, n_blocks, mb, nb);
+      const int acc = it & 1;
+      const uint32_t acc_ph = (static_cast<uint32_t>(it) >> 1) & 1u;
+      if (!mbar_wait_bounded(&tfull[acc], acc_ph, args.status, 5)) {
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      const int64_t grow = static_cast<int64_t>(mb) * BM + row_in_tile;
+      const bool row_ok = grow < args.M;
+      float* crow = args.C + grow * args.ldc;
+      const float* xrow = args.aux != nullptr ? args.aux + grow * args.ldc : nullptr;
+      const uint32_t t_row = tmem_base + static_cast<uint32_t>(acc * BN) +
+                             (static_cast<uint32_t>(q * 32) << 16);
+#pragma unroll 1
+      for (int ch = 0; ch < BN / 32; ++ch) {
+        const int col0 = nb * BN + ch * 32;
+        if (col0 >= args.N) break;  // warp-uniform
+        float v[32];
+        tmem_ld_32x32(t_row + static_cast<uint32_t>(ch * 32), v);
+        if (!row_ok) {
+          // rows past M hold zero-filled garbage: nothing to store
+        } else if (args.vec_ok && col0 + 32 <= args.N) {
+          float4* c4 = reinterpret_cast<float4*>(crow + col0);
+          if (args.epilogue == CTDK_EPI_STORE) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+              c4[j] = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+          } else {
+            const float4* x4 = args.epilogue == CTDK_EPI_ACCUMULATE
+                                   ? reinterpret_cast<const float4*>(crow + col0)
+                                   : reinterpret_cast<const float4*>(xrow + col0);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              const float4 x = x4[j];
+              c4[j] = make_float4(v[4 * j] + x.x, v[4 * j + 1] + x.y, v[4 * j + 2] + x.z,
+                                  v[4 * j + 3] + x.w);
+            }
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const int col = col0 + j;
+            if (col < args.N) {
+              float r = v[j];
+              if (args.epilogue == CTDK_EPI_ACCUMULATE) r += crow[col];
+              else if (args.epilogue == CTDK_EPI_RESIDUAL) r += xrow[col];
+              crow[col] = r;
+            }
+          }
+        }
+        __syncwarp();  // tcgen05.ld is warp-collective: reconverge before the next chunk
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tempty[acc]);
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, C::kTmemCols);
+  }
+}
+
+// ----------------------------------------------------------------------------------------
+// Host side
+// ----------------------------------------------------------------------------------------
+PFN_cuTensorMapEncodeTiled_v12000 g_encode = nullptr;
+std::once_flag g_encode_once;
+
+PFN_cuTensorMapEncodeTiled_v12000 encode_fn() {
+  std::call_once(g_encode_once, [] {
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres) ==
+            cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      g_encode = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(fn);
+  });
+  return g_encode;
+}
+
+bool tma_rounds_to_tf32() {
+  // CTDK_TMA_F32=1 loads raw fp32 bits (the tensor core then ignores the low mantissa bits);
+  // the default asks the copy engine for the TF32 data type.
+  static const bool raw = [] {
+    const char* e = std::getenv("CTDK_TMA_F32");
+    return e != nullptr && e[0] == '1';
+  }();
+  return !raw;
+}
+
+// 2-D map over a row-major fp32 matrix: dim0 = contiguous extent `inner`, dim1 = `outer`
+// rows `ld` floats apart; box = {32, box_rows}; 128-byte swizzle; out-of-range reads give 0.
+int make_map(CUtensorMap* map, const float* base, int64_t inner, int64_t outer, int64_t ld,
+             int box_rows, bool exact_fp32) {
+  auto enc = encode_fn();
+  if (enc == nullptr) return fail(CTDK_ELAUNCH, "cuTensorMapEncodeTiled unavailable");
+  cuuint64_t dims[2] = {static_cast<cuuint64_t>(inner), static_cast<cuuint64_t>(outer)};
+  cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld) * sizeof(float)};
+  cuuint32_t box[2] = {32u, static_cast<cuuint32_t>(box_rows)};
+  cuuint32_t estr[2] = {1u, 1u};
+  const CUtensorMapDataType dt = (!exact_fp32 && tma_rounds_to_tf32())
+                                     ? CU_TENSOR_MAP_DATA_TYPE_TFLOAT32
+                                     : CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
+  CUresult r = enc(map, dt, 2, const_cast<float*>(base), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS)
+    return fail(CTDK_ELAUNCH, "cuTensorMapEncodeTiled failed (%d): inner=%lld outer=%lld ld=%lld",
+                static_cast<int>(r), static_cast<long long>(inner),
+                static_cast<long long>(outer), static_cast<long long>(ld));
+  return CTDK_OK;
+}
+
+template <int BN, bool A_MN, bool B_MN>
+int launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmArgs& args,
+           cudaStream_t stream) {
+  using C = Cfg<BN>;
+  static bool attr_set[64] = {false};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  auto* kern = gemm_tf32_kernel<BN, A_MN, B_MN>;
+  if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+    cudaError_t e =
+        cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
+    if (e != cudaSuccess)
+      return fail(CTDK_ELAUNCH, "gemm: cannot opt in to %d bytes of shared memory: %s",
+                  C::kSmemBytes, cudaGetErrorString(e));
+    attr_set[dev] = true;
+  }
+  const int m_blocks = (args.M + BM - 1) / BM, n_blocks = (args.N + BN - 1) / BN;
+  const int tiles = m_blocks * n_blocks;
+  const int sms = sm_count();
+  const int grid = tiles < sms ? tiles : sms;
+  kern<<<grid, kThreads, C::kSmemBytes, stream>>>(ta, tb, args);
+  return check_launch("ctdk_gemm(tcgen05)");
+}
+
+template <int BN>
+int dispatch_major(bool a_mn, bool b_mn, const CUtensorMap& ta, const CUtensorMap& tb,
+                   const GemmArgs& args, cudaStream_t stream) {
+  if (!a_mn && !b_mn) return launch<BN, false, false>(ta, tb, args, stream);
+  if (!a_mn && b_mn) return launch<BN, false, true>(ta, tb, args, stream);
+  if (a_mn && !b_mn) return launch<BN, true, false>(ta, tb, args, stream);
+  return launch<BN, true, true>(ta, tb, args, stream);
+}
+
+}  // namespace
+
+// Returns CTDK_OK after enqueueing, or 1 when the shape/alignment is not eligible for the
+// tensor-core path (the caller then uses the SIMT kernel).
+int gemm_tcgen05(const float* A, const float* B, float* Cp, int64_t M, int64_t N, int64_t K,
+                 int64_t lda, int64_t ldb, int64_t ldc, int transa, int transb, int epilogue,
+                 const float* aux, cudaStream_t stream) {
+  auto a16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; };
+  if (!a16(A) || !a16(B) || (lda & 3) || (ldb & 3)) return 1;
+  if (M > INT32_MAX || N > INT32_MAX || K > INT32_MAX) return 1;
+  if (M < 1 || N < 8 || K < 1) return 1;
+
+  const bool a_mn = transa != 0;  // A stored [K,M]: contiguous along M
+  const bool b_mn = transb == 0;  // B stored [K,N]: contiguous along N
+  int bn = 256;
+  if (N <= 64) bn = 64;
+  else if (N <= 128) bn = 128;
+  else {
+    // Tensor-core time of a tile grows with its width, so compare waves x width and keep
+    // the wide tile on ties (fewer A re-reads).
+    const int64_t m_blocks = (M + BM - 1) / BM;
+    const int sms = sm_count();
+    const int64_t cost256 = ((m_blocks * ((N + 255) / 256) + sms - 1) / sms) * 256;
+    const int64_t cost128 = ((m_blocks * ((N + 127) / 128) + sms - 1) / sms) * 128;
+    bn = cost128 < cost256 ? 128 : 256;
+  }
+
+  CUtensorMap ta, tb;
+  int rc;
+  if (a_mn) rc = make_map(&ta, A, M, K, lda, BK, false);
+  else rc = make_map(&ta, A, K, M, lda, BM, false);
+  if (rc != CTDK_OK) return rc;
+  if (b_mn) rc = make_map(&tb, B, N, K, ldb, BK, false);
+  else rc = make_map(&tb, B, K, N, ldb, bn, false);
+  if (rc != CTDK_OK) return rc;
+
+  GemmArgs args;
+  args.C = Cp;
+  args.aux = aux;
+  args.ldc = ldc;
+  args.M = static_cast<int>(M);
+  args.N = static_cast<int>(N);
+  args.K = static_cast<int>(K);
+  args.epilogue = epilogue;
+  args.vec_ok = (a16(Cp) && (ldc & 3) == 0 && (aux == nullptr || a16(aux))) ? 1 : 0;
+  args.status = device_status_word();
+  if (args.status == nullptr) return fail(CTDK_ELAUNCH, "gemm: no status word");
+
+  switch (bn) {
+    case 64: return dispatch_major<64>(a_mn, b_mn, ta, tb, args, stream);
+    case 128: return dispatch_major<128>(a_mn, b_mn, ta, tb, args, stream);
+    default: return dispatch_major<256>(a_mn, b_mn, ta, tb, args, stream);
+  }
+}
+
+// Near-fp32 GEMM (3xTF32 split). Returns 1 (not eligible) until the split kernel is built,
+// so the caller computes the exact fp32 result with the SIMT kernel.
+int gemm_3xtf32(const float*, const float*, float*, int64_t, int64_t, int64_t, int64_t, int64_t,
+                int64_t, int, int, int, const float*, cudaStream_t) {
+  return 1;
+}
+
+}  // namespace ctdk

@@ -1,0 +1,649 @@
+// RMSNorm forward/backward, RoPE, and the fused per-head QK-Norm + RoPE kernels.
+//
+// Arithmetic follows the reference (emberlm src/ops/norm.cu:18-106, src/ops/rope.cu:17-56):
+//   scale = rsqrtf(sum(x^2)/H + eps);  y = x*scale*w
+//   dx = s*(dy*w - x*s*s*c/H), c = sum(dy*w*x);  dw = sum_rows dy*x*s
+//   rope: pairs (i, i+D/2), angle = float(pos)*freq_i, freq_i = theta^(-2i/D) with the
+//   llama3 wavelength branches; backward = same rotation with sin negated.
+// Differences are in the execution only: one CTA per row with 128-bit accesses and
+// warp-shuffle reductions, dw reduced through per-CTA partial rows instead of one atomic per
+// element, cos/sin from libm-accurate functions instead of the fast intrinsics.
+#include "common.cuh"
+
+namespace ctdk {
+namespace {
+
+constexpr int kMaxPartialRows = 512;
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+// Block-wide sum of up to two values; `slot` toggles between two smem buffers so that one
+// __syncthreads per reduction is enough.
+template <int N>
+__device__ __forceinline__ void block_sum(float (&v)[N], float* smem /* [2][N][32] */,
+                                          int slot) {
+  const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+  const int nw = (blockDim.x + 31) >> 5;
+#pragma unroll
+  for (int k = 0; k < N; ++k) v[k] = warp_sum(v[k]);
+  float* s = smem + slot * N * 32;
+  if (lane == 0) {
+#pragma unroll
+    for (int k = 0; k < N; ++k) s[k * 32 + wid] = v[k];
+  }
+  __syncthreads();
+#pragma unroll
+  for (int k = 0; k < N; ++k) {
+    float t = (lane < nw) ? s[k * 32 + lane] : 0.0f;
+    v[k] = warp_sum(t);
+  }
+}
+
+// ---------------------------------------------------------------------------------------
+// RMSNorm forward: one CTA per row (grid-stride), NV float4 per thread kept in registers.
+// ---------------------------------------------------------------------------------------
+template <int NV>
+__global__ void __launch_bounds__(256) rmsnorm_fwd_kernel(const float* __restrict__ x,
+                                                          const float* __restrict__ w,
+                                                          float* __restrict__ y,
+                                                          float* __restrict__ rstd,
+                                                          int64_t rows, int H4, float inv_H,
+                                                          float eps) {
+  __shared__ float red[2 * 1 * 32];
+  const float4* w4 = reinterpret_cast<const float4*>(w);
+  float4 wv[NV];
+#pragma unroll
+  for (int j = 0; j < NV; ++j) {
+    const int c = threadIdx.x + j * blockDim.x;
+    wv[j] = (c < H4) ? w4[c] : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+  int slot = 0;
+  for (int64_t row = blockIdx.x; row < rows; row += gridDim.x, slot ^= 1) {
+    const float4* x4 = reinterpret_cast<const float4*>(x) + row * H4;
+    float4* y4 = reinterpret_cast<float4*>(y) + row * H4;
+    float4 xv[NV];
+    float acc[1] = {0.0f};
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
+      const int c = threadIdx.x + j * blockDim.x;
+      xv[j] = (c < H4) ? x4[c] : make_float4(0.f, 0.f, 0.f, 0.f);
+      acc[0] += xv[j].x * xv[j].x + xv[j].y * xv[j].y + xv[j].z * xv[j].z + xv[j].w * xv[j].w;
+    }
+    block_sum<1>(acc, red, slot);
+    const float s = rsqrtf(acc[0] * inv_H + eps);
+    if (rstd != nullptr && threadIdx.x == 0) rstd[row] = s;
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
+      const int c = threadIdx.x + j * blockDim.x;
+      if (c < H4) {
+        float4 o;
+        o.x = xv[j].x * s * wv[j].x;
+        o.y = xv[j].y * s * wv[j].y;
+        o.z = xv[j].z * s * wv[j].z;
+        o.w = xv[j].w * s * wv[j].w;
+        y4[c] = o;
+      }
+    }
+  }
+}
+
+// Any H / any alignment: scalar loads, row re-read from cache for the second pass.
+__global__ void __launch_bounds__(256) rmsnorm_fwd_generic_kernel(const float* __restrict__ x,
+                                                                  const float* __restrict__ w,
+                                                                  float* __restrict__ y,
+                                                                  float* __restrict__ rstd,
+                                                                  int64_t rows, int H,
+                                                                  float eps) {
+  __shared__ float red[2 * 1 * 32];
+  int slot = 0;
+  for (int64_t row = blockIdx.x; row < rows; row += gridDim.x, slot ^= 1) {
+    const float* xr = x + row * H;
+    float acc[1] = {0.0f};
+    for (int i = threadIdx.x; i < H; i += blockDim.x) acc[0] += xr[i] * xr[i];
+    block_sum<1>(acc, red, slot);
+    const float s = rsqrtf(acc[0] / static_cast<float>(H) + eps);
+    if (rstd != nullptr && threadIdx.x == 0) rstd[row] = s;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) y[row * H + i] = xr[i] * s * w[i];
+  }
+}
+
+// ---------------------------------------------------------------------------------------
+// RMSNorm backward. dw partial sums stay in registers across the rows of a CTA and are
+// written once per CTA to partial[blockIdx.x][H]; rmsnorm_dw_finalize sums the partial rows.
+// ---------------------------------------------------------------------------------------
+template <int NV>
+__global__ void __launch_bounds__(256)
+    rmsnorm_bwd_kernel(const float* __restrict__ dy, const float* __restrict__ x,
+                       const float* __restrict__ w, float* __restrict__ dx,
+                       float* __restrict__ partial, int64_t rows, int H4, float inv_H,
+                       float eps, int add_to_dx) {
+  __shared__ float red[2 * 2 * 32];
+  const float4* w4 = reinterpret_cast<const float4*>(w);
+  float4 wv[NV], dwv[NV];
+#pragma unroll
+  for (int j = 0; j < NV; ++j) {
+    const int c = threadIdx.x + j * blockDim.x;
+    wv[j] = (c < H4) ? w4[c] : make_float4(0.f, 0.f, 0.f, 0.f);
+    dwv[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+  int slot = 0;
+  for (int64_t row = blockIdx.x; row < rows; row += gridDim.x, slot ^= 1) {
+    const float4* x4 = reinterpret_cast<const float4*>(x) + row * H4;
+    const float4* g4 = reinterpret_cast<const float4*>(dy) + row * H4;
+    float4* dx4 = reinterpret_cast<float4*>(dx) + row * H4;
+    float4 xv[NV], gv[NV];
+    float acc[2] = {0.0f, 0.0f};
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
+      const int c = threadIdx.x + j * blockDim.x;
+      if (c < H4) {
+        xv[j] = x4[c];
+        gv[j] = g4[c];
+      } else {
+        xv[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+        gv[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+      acc[0] += xv[j].x * xv[j].x + xv[j].y * xv[j].y + xv[j].z * xv[j].z + xv[j].w * xv[j].w;
+      acc[1] += gv[j].x * wv[j].x * xv[j].x + gv[j].y * wv[j].y * xv[j].y +
+                gv[j].z * wv[j].z * xv[j].z + gv[j].w * wv[j].w * xv[j].w;
+    }
+    block_sum<2>(acc, red, slot);
+    const float s = rsqrtf(acc[0] * inv_H + eps);
+    const float k = s * s * acc[1] * inv_H;
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
+      const int c = threadIdx.x + j * blockDim.x;
+      if (c < H4) {
+        float4 o;
+        o.x = s * (gv[j].x * wv[j].x - xv[j].x * k);
+        o.y = s * (gv[j].y * wv[j].y - xv[j].y * k);
+        o.z = s * (gv[j].z * wv[j].z - xv[j].z * k);
+        o.w = s * (gv[j].w * wv[j].w - xv[j].w * k);
+        if (add_to_dx) {
+          const float4 p = dx4[c];
+          o.x += p.x;
+          o.y += p.y;
+          o.z += p.z;
+          o.w += p.w;
+        }
+        dx4[c] = o;
+        dwv[j].x += gv[j].x * xv[j].x * s;
+        dwv[j].y += gv[j].y * xv[j].y * s;
+        dwv[j].z += gv[j].z * xv[j].z * s;
+        dwv[j].w += gv[j].w * xv[j].w * s;
+      }
+    }
+  }
+  float4* p4 = reinterpret_cast<float4*>(partial) + static_cast<int64_t>(blockIdx.x) * H4;
+#pragma unroll
+  for (int j = 0; j < NV; ++j) {
+    const int c = threadIdx.x + j * blockDim.x;
+    if (c < H4) p4[c] = dwv[j];
+  }
+}
+
+// Generic backward (any H): partial sums accumulated in the CTA's own partial row in global
+// memory (each element is owned by one thread, so no atomics are needed).
+__global__ void __launch_bounds__(256)
+    rmsnorm_bwd_generic_kernel(const float* __restrict__ dy, const float* __restrict__ x,
+                               const float* __restrict__ w, float* __restrict__ dx,
+                               float* __restrict__ partial, int64_t rows, int H, float eps,
+                               int add_to_dx) {
+  __shared__ float red[2 * 2 * 32];
+  float* prow = partial + static_cast<int64_t>(blockIdx.x) * H;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) prow[i] = 0.0f;
+  int slot = 0;
+  for (int64_t row = blockIdx.x; row < rows; row += gridDim.x, slot ^= 1) {
+    const float* xr = x + row * H;
+    const float* gr = dy + row * H;
+    float acc[2] = {0.0f, 0.0f};
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+      acc[0] += xr[i] * xr[i];
+      acc[1] += gr[i] * w[i] * xr[i];
+    }
+    block_sum<2>(acc, red, slot);
+    const float inv_H = 1.0f / static_cast<float>(H);
+    const float s = rsqrtf(acc[0] * inv_H + eps);
+    const float k = s * s * acc[1] * inv_H;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+      float o = s * (gr[i] * w[i] - xr[i] * k);
+      if (add_to_dx) o += dx[row * H + i];
+      dx[row * H + i] = o;
+      prow[i] += gr[i] * xr[i] * s;
+    }
+  }
+}
+
+// dw[c] (+)= sum_p partial[p][c]; one thread per column, coalesced across the CTA.
+__global__ void __launch_bounds__(128) dw_finalize_kernel(const float* __restrict__ partial,
+                                                          float* __restrict__ dw, int nparts,
+                                                          int H, int accumulate) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= H) return;
+  float acc = 0.0f;
+  for (int p = 0; p < nparts; ++p) acc += partial[static_cast<int64_t>(p) * H + c];
+  dw[c] = accumulate ? dw[c] + acc : acc;
+}
+
+// partial rows are [2][D] (q-norm then k-norm); dwq/dwk (+)= column sums.
+__global__ void __launch_bounds__(128) qk_dw_finalize_kernel(const float* __restrict__ partial,
+                                                             float* __restrict__ dwq,
+                                                             float* __restrict__ dwk,
+                                                             int nparts, int D,
+                                                             int accumulate) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= 2 * D) return;
+  float acc = 0.0f;
+  for (int p = 0; p < nparts; ++p) acc += partial[static_cast<int64_t>(p) * 2 * D + c];
+  float* dst = (c < D) ? dwq + c : dwk + (c - D);
+  *dst = accumulate ? *dst + acc : acc;
+}
+
+// ---------------------------------------------------------------------------------------
+// RoPE
+// ---------------------------------------------------------------------------------------
+__device__ __forceinline__ float rope_freq(int i, int D, const ctdk_rope_params& p) {
+  const float base_freq = powf(p.theta, -(2.0f * i) / static_cast<float>(D));
+  float freq = base_freq;
+  if (p.scaling_factor > 1.0f) {
+    const float wavelen = 6.2831853f / base_freq;
+    if (wavelen > p.low_freq_wavelen) {
+      freq = base_freq / p.scaling_factor;
+    } else if (wavelen > p.high_freq_wavelen) {
+      const float smooth =
+          (wavelen - p.high_freq_wavelen) / (p.low_freq_wavelen - p.high_freq_wavelen);
+      freq = (1.0f - smooth) * base_freq + smooth * (base_freq / p.scaling_factor);
+    }
+  }
+  return freq;
+}
+
+// table[t][i] = (cos, sin) of float(position_start+t)*freq_i, i < D/2.
+__global__ void rope_table_kernel(float2* __restrict__ table, int64_t T, int D,
+                                  int position_start, ctdk_rope_params p) {
+  const int Dh = D / 2;
+  const int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (idx >= T * Dh) return;
+  const int64_t t = idx / Dh;
+  const int i = static_cast<int>(idx - t * Dh);
+  const float angle = static_cast<float>(position_start + t) * rope_freq(i, D, p);
+  float s, c;
+  sincosf(angle, &s, &c);
+  table[idx] = make_float2(c, s);
+}
+
+// One warp per (b,t,h) slot.
+__global__ void __launch_bounds__(256)
+    rope_kernel(const float* __restrict__ x_in, float* __restrict__ x_out, int64_t slots,
+                int64_t T, int H, int D, int64_t row_stride, int position_start,
+                ctdk_rope_params p, float sin_sign) {
+  const int lane = threadIdx.x & 31;
+  const int64_t warp0 = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const int64_t nwarps = (static_cast<int64_t>(gridDim.x) * blockDim.x) >> 5;
+  const int Dh = D / 2;
+  for (int64_t slot = warp0; slot < slots; slot += nwarps) {
+    const int64_t bt = slot / H;
+    const int h = static_cast<int>(slot - bt * H);
+    const int64_t t = bt % T;
+    const float* xr = x_in + bt * row_stride + static_cast<int64_t>(h) * D;
+    float* yr = x_out + bt * row_stride + static_cast<int64_t>(h) * D;
+    for (int i = lane; i < Dh; i += 32) {
+      const float angle = static_cast<float>(position_start + t) * rope_freq(i, D, p);
+      float s, c;
+      sincosf(angle, &s, &c);
+      s *= sin_sign;
+      const float a = xr[i], b = xr[i + Dh];
+      yr[i] = a * c - b * s;
+      yr[i + Dh] = a * s + b * c;
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------
+// Fused QK-Norm + RoPE over a packed qkv row: one warp per (row, head) item. Each lane
+// owns NP rotation pairs (i, i+D/2), i = lane + 32*j: D = 64*NP.
+// ---------------------------------------------------------------------------------------
+template <int NP>
+__global__ void __launch_bounds__(256)
+    qk_norm_rope_fwd_kernel(const float* __restrict__ qkv, float* __restrict__ out,
+                            const float* __restrict__ wq, const float* __restrict__ wk,
+                            float* __restrict__ rstd_q, float* __restrict__ rstd_k,
+                            const float2* __restrict__ table, int64_t rows, int64_t T, int H,
+                            int Hk, float eps) {
+  constexpr int D = 64 * NP, Dh = 32 * NP;
+  const int lane = threadIdx.x & 31;
+  const int64_t warp0 = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const int64_t nwarps = (static_cast<int64_t>(gridDim.x) * blockDim.x) >> 5;
+  const int HT = H + 2 * Hk;
+  const int64_t items = rows * HT;
+  const bool copy_v = (out != qkv);
+  for (int64_t it = warp0; it < items; it += nwarps) {
+    const int64_t row = it / HT;
+    const int h = static_cast<int>(it - row * HT);
+    const float* xr = qkv + it * D;
+    float* yr = out + it * D;
+    if (h >= H + Hk) {  // v head: plain copy
+      if (copy_v) {
+#pragma unroll
+        for (int j = 0; j < 2 * NP; ++j) yr[lane + 32 * j] = xr[lane + 32 * j];
+      }
+      continue;
+    }
+    const bool is_q = h < H;
+    const float* w = is_q ? wq : wk;
+    float a[NP], b[NP];
+    float ss = 0.0f;
+#pragma unroll
+    for (int j = 0; j < NP; ++j) {
+      a[j] = xr[lane + 32 * j];
+      b[j] = xr[lane + 32 * j + Dh];
+      ss += a[j] * a[j] + b[j] * b[j];
+    }
+    if (w != nullptr) {
+      ss = warp_sum(ss);
+      const float s = rsqrtf(ss / static_cast<float>(D) + eps);
+      if (lane == 0) {
+        if (is_q) rstd_q[row * H + h] = s;
+        else rstd_k[row * Hk + (h - H)] = s;
+      }
+#pragma unroll
+      for (int j = 0; j < NP; ++j) {
+        a[j] = a[j] * s * w[lane + 32 * j];
+        b[j] = b[j] * s * w[lane + 32 * j + Dh];
+      }
+    }
+    const int64_t t = row % T;
+#pragma unroll
+    for (int j = 0; j < NP; ++j) {
+      const float2 cs = table[t * Dh + lane + 32 * j];
+      yr[lane + 32 * j] = a[j] * cs.x - b[j] * cs.y;
+      yr[lane + 32 * j + Dh] = a[j] * cs.y + b[j] * cs.x;
+    }
+  }
+}
+
+// Backward, in place on dqkv: un-rotate (R(-theta)), then the RMSNorm backward per head.
+// dw partials: per-warp registers -> smem -> partial[blockIdx.x][2][D].
+template <int NP>
+__global__ void __launch_bounds__(256)
+    qk_norm_rope_bwd_kernel(float* __restrict__ dqkv, const float* __restrict__ qkv_pre,
+                            const float* __restrict__ wq, const float* __restrict__ wk,
+                            const float* __restrict__ rstd_q, const float* __restrict__ rstd_k,
+                            float* __restrict__ partial, const float2* __restrict__ table,
+                            int64_t rows, int64_t T, int H, int Hk) {
+  constexpr int D = 64 * NP, Dh = 32 * NP;
+  __shared__ float sdw[8][2][D];
+  const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+  const int64_t warp0 = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const int64_t nwarps = (static_cast<int64_t>(gridDim.x) * blockDim.x) >> 5;
+  const int HT = H + 2 * Hk, HQK = H + Hk;
+  const int64_t items = rows * HQK;
+  const bool has_norm = (wq != nullptr);
+  float dwa[2][NP], dwb[2][NP];
+#pragma unroll
+  for (int j = 0; j < NP; ++j) {
+    dwa[0][j] = dwa[1][j] = dwb[0][j] = dwb[1][j] = 0.0f;
+  }
+  for (int64_t it = warp0; it < items; it += nwarps) {
+    const int64_t row = it / HQK;
+    const int h = static_cast<int>(it - row * HQK);
+    const bool is_q = h < H;
+    float* gr = dqkv + (row * HT + h) * D;
+    const int64_t t = row % T;
+    float ga[NP], gb[NP];
+#pragma unroll
+    for (int j = 0; j < NP; ++j) {
+      const float2 cs = table[t * Dh + lane + 32 * j];
+      const float a = gr[lane + 32 * j], b = gr[lane + 32 * j + Dh];
+      ga[j] = a * cs.x + b * cs.y;   // rotation by -angle
+      gb[j] = -a * cs.y + b * cs.x;
+    }
+    if (has_norm) {
+      const float* w = is_q ? wq : wk;
+      const float* xr = qkv_pre + (row * HT + h) * D;
+      const float s = is_q ? rstd_q[row * H + h] : rstd_k[row * Hk + (h - H)];
+      float xa[NP], xb[NP], wa[NP], wb[NP];
+      float c = 0.0f;
+#pragma unroll
+      for (int j = 0; j < NP; ++j) {
+        xa[j] = xr[lane + 32 * j];
+        xb[j] = xr[lane + 32 * j + Dh];
+        wa[j] = w[lane + 32 * j];
+        wb[j] = w[lane + 32 * j + Dh];
+        c += ga[j] * wa[j] * xa[j] + gb[j] * wb[j] * xb[j];
+      }
+      c = warp_sum(c);
+      const float k = s * s * c / static_cast<float>(D);
+      const int sel = is_q ? 0 : 1;
+#pragma unroll
+      for (int j = 0; j < NP; ++j) {
+        const float da = ga[j] * xa[j] * s, db = gb[j] * xb[j] * s;
+        if (sel == 0) {
+          dwa[0][j] += da;
+          dwb[0][j] += db;
+        } else {
+          dwa[1][j] += da;
+          dwb[1][j] += db;
+        }
+        ga[j] = s * (ga[j] * wa[j] - xa[j] * k);
+        gb[j] = s * (gb[j] * wb[j] - xb[j] * k);
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < NP; ++j) {
+      gr[lane + 32 * j] = ga[j];
+      gr[lane + 32 * j + Dh] = gb[j];
+    }
+  }
+  if (has_norm) {
+#pragma unroll
+    for (int sel = 0; sel < 2; ++sel)
+#pragma unroll
+      for (int j = 0; j < NP; ++j) {
+        sdw[wid][sel][lane + 32 * j] = dwa[sel][j];
+        sdw[wid][sel][lane + 32 * j + Dh] = dwb[sel][j];
+      }
+    __syncthreads();
+    const int nw = blockDim.x >> 5;
+    for (int i = threadIdx.x; i < 2 * D; i += blockDim.x) {
+      float acc = 0.0f;
+      for (int ww = 0; ww < nw; ++ww) acc += sdw[ww][i / D][i % D];
+      partial[static_cast<int64_t>(blockIdx.x) * 2 * D + i] = acc;
+    }
+  }
+}
+
+template <int NV>
+void launch_rmsnorm_fwd(const float* x, const float* w, float* y, float* rstd, int64_t rows,
+                        int H, float eps, int threads, int grid, cudaStream_t s) {
+  rmsnorm_fwd_kernel<NV><<<grid, threads, 0, s>>>(x, w, y, rstd, rows, H / 4,
+                                                  1.0f / static_cast<float>(H), eps);
+}
+template <int NV>
+void launch_rmsnorm_bwd(const float* dy, const float* x, const float* w, float* dx,
+                        float* partial, int64_t rows, int H, float eps, int add, int threads,
+                        int grid, cudaStream_t s) {
+  rmsnorm_bwd_kernel<NV><<<grid, threads, 0, s>>>(dy, x, w, dx, partial, rows, H / 4,
+                                                  1.0f / static_cast<float>(H), eps, add);
+}
+
+}  // namespace
+}  // namespace ctdk
+
+using namespace ctdk;
+
+extern "C" {
+
+int ctdk_rmsnorm_fwd(const float* x, const float* w, float* y, float* rstd, int64_t rows,
+                     int H, float eps, void* stream) {
+  CTDK_REQUIRE(rows >= 0 && H > 0, "ctdk_rmsnorm_fwd: bad shape");
+  if (rows == 0) return CTDK_OK;
+  CTDK_REQUIRE(x && w && y, "ctdk_rmsnorm_fwd: null pointer");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int64_t cap = static_cast<int64_t>(sm_count()) * 8;
+  const int grid = static_cast<int>(rows < cap ? rows : cap);
+  const bool vec = (H % 4 == 0) && aligned16(x) && aligned16(w) && aligned16(y) && H <= 4096;
+  if (vec) {
+    const int H4 = H / 4;
+    int threads = ((H4 + 31) / 32) * 32;
+    if (threads > 256) threads = 256;
+    const int nv = (H4 + threads - 1) / threads;
+    switch (nv) {
+      case 1: launch_rmsnorm_fwd<1>(x, w, y, rstd, rows, H, eps, threads, grid, s); break;
+      case 2: launch_rmsnorm_fwd<2>(x, w, y, rstd, rows, H, eps, threads, grid, s); break;
+      default: launch_rmsnorm_fwd<4>(x, w, y, rstd, rows, H, eps, threads, grid, s); break;
+    }
+  } else {
+    rmsnorm_fwd_generic_kernel<<<grid, 256, 0, s>>>(x, w, y, rstd, rows, H, eps);
+  }
+  return check_launch("ctdk_rmsnorm_fwd");
+}
+
+int64_t ctdk_rmsnorm_bwd_scratch_floats(int H) {
+  return static_cast<int64_t>(kMaxPartialRows) * (H > 0 ? H : 0);
+}
+
+int ctdk_rmsnorm_bwd(const float* dy, const float* x, const float* w, float* dx, float* dw,
+                     float* dw_scratch, int64_t rows, int H, float eps, int accumulate_dw,
+                     int add_to_dx, void* stream) {
+  CTDK_REQUIRE(rows >= 0 && H > 0, "ctdk_rmsnorm_bwd: bad shape");
+  CTDK_REQUIRE(dw && dw_scratch, "ctdk_rmsnorm_bwd: null dw / scratch");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (rows == 0) {
+    if (!accumulate_dw) cudaMemsetAsync(dw, 0, sizeof(float) * H, s);
+    return CTDK_OK;
+  }
+  CTDK_REQUIRE(dy && x && w && dx, "ctdk_rmsnorm_bwd: null pointer");
+  int64_t cap = static_cast<int64_t>(sm_count()) * 2;
+  if (cap > kMaxPartialRows) cap = kMaxPartialRows;
+  const int grid = static_cast<int>(rows < cap ? rows : cap);
+  const bool vec = (H % 4 == 0) && aligned16(dy) && aligned16(x) && aligned16(w) &&
+                   aligned16(dx) && aligned16(dw_scratch) && H <= 4096;
+  if (vec) {
+    const int H4 = H / 4;
+    int threads = ((H4 + 31) / 32) * 32;
+    if (threads > 256) threads = 256;
+    const int nv = (H4 + threads - 1) / threads;
+    switch (nv) {
+      case 1:
+        launch_rmsnorm_bwd<1>(dy, x, w, dx, dw_scratch, rows, H, eps, add_to_dx, threads, grid,
+                              s);
+        break;
+      case 2:
+        launch_rmsnorm_bwd<2>(dy, x, w, dx, dw_scratch, rows, H, eps, add_to_dx, threads, grid,
+                              s);
+        break;
+      default:
+        launch_rmsnorm_bwd<4>(dy, x, w, dx, dw_scratch, rows, H, eps, add_to_dx, threads, grid,
+                              s);
+        break;
+    }
+  } else {
+    rmsnorm_bwd_generic_kernel<<<grid, 256, 0, s>>>(dy, x, w, dx, dw_scratch, rows, H, eps,
+                                                    add_to_dx);
+  }
+  int rc = check_launch("ctdk_rmsnorm_bwd");
+  if (rc != CTDK_OK) return rc;
+  dw_finalize_kernel<<<ceil_div(H, 128), 128, 0, s>>>(dw_scratch, dw, grid, H, accumulate_dw);
+  return check_launch("ctdk_rmsnorm_bwd(finalize)");
+}
+
+int ctdk_rope_table(float* table, int64_t T, int D, int position_start,
+                    const ctdk_rope_params* p, void* stream) {
+  CTDK_REQUIRE(table && p, "ctdk_rope_table: null pointer");
+  CTDK_REQUIRE(T >= 0 && D > 0 && D % 2 == 0, "ctdk_rope_table: D must be even");
+  if (T == 0) return CTDK_OK;
+  const int64_t n = T * (D / 2);
+  rope_table_kernel<<<ceil_div(n, 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      reinterpret_cast<float2*>(table), T, D, position_start, *p);
+  return check_launch("ctdk_rope_table");
+}
+
+int ctdk_rope(const float* x_in, float* x_out, int64_t B, int64_t T, int H, int D,
+              int64_t row_stride, int position_start, const ctdk_rope_params* p,
+              float sin_sign, void* stream) {
+  CTDK_REQUIRE(p != nullptr, "ctdk_rope: null params");
+  CTDK_REQUIRE(B >= 0 && T >= 0 && H > 0 && D > 0 && D % 2 == 0, "ctdk_rope: D must be even");
+  const int64_t slots = B * T * H;
+  if (slots == 0) return CTDK_OK;
+  CTDK_REQUIRE(x_in && x_out, "ctdk_rope: null pointer");
+  CTDK_REQUIRE(row_stride >= static_cast<int64_t>(H) * D, "ctdk_rope: row_stride < H*D");
+  const int64_t cap = static_cast<int64_t>(sm_count()) * 8;
+  const int64_t need = (slots + 7) / 8;
+  rope_kernel<<<static_cast<int>(need < cap ? need : cap), 256, 0,
+                static_cast<cudaStream_t>(stream)>>>(x_in, x_out, slots, T, H, D, row_stride,
+                                                     position_start, *p, sin_sign);
+  return check_launch("ctdk_rope");
+}
+
+int ctdk_qk_norm_rope_fwd(const float* qkv, float* qkv_out, const float* wq, const float* wk,
+                          float* rstd_q, float* rstd_k, const float* rope_table, int64_t B,
+                          int64_t T, int H, int Hk, int D, float eps, void* stream) {
+  CTDK_REQUIRE(B >= 0 && T >= 0 && H > 0 && Hk > 0, "ctdk_qk_norm_rope_fwd: bad shape");
+  CTDK_REQUIRE(D == 64 || D == 128, "ctdk_qk_norm_rope_fwd: head_dim must be 64 or 128");
+  const int64_t rows = B * T;
+  if (rows == 0) return CTDK_OK;
+  CTDK_REQUIRE(qkv && qkv_out && rope_table, "ctdk_qk_norm_rope_fwd: null pointer");
+  CTDK_REQUIRE((wq == nullptr) == (wk == nullptr), "ctdk_qk_norm_rope_fwd: wq/wk mismatch");
+  CTDK_REQUIRE(wq == nullptr || (rstd_q && rstd_k), "ctdk_qk_norm_rope_fwd: rstd required");
+  CTDK_REQUIRE(wq == nullptr || qkv_out != qkv,
+               "ctdk_qk_norm_rope_fwd: QK-Norm needs an out-of-place result");
+  const int64_t items = rows * (H + 2 * Hk);
+  const int64_t cap = static_cast<int64_t>(sm_count()) * 8;
+  const int64_t need = (items + 7) / 8;
+  const int grid = static_cast<int>(need < cap ? need : cap);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const float2* tb = reinterpret_cast<const float2*>(rope_table);
+  if (D == 64)
+    qk_norm_rope_fwd_kernel<1><<<grid, 256, 0, s>>>(qkv, qkv_out, wq, wk, rstd_q, rstd_k, tb,
+                                                    rows, T, H, Hk, eps);
+  else
+    qk_norm_rope_fwd_kernel<2><<<grid, 256, 0, s>>>(qkv, qkv_out, wq, wk, rstd_q, rstd_k, tb,
+                                                    rows, T, H, Hk, eps);
+  return check_launch("ctdk_qk_norm_rope_fwd");
+}
+
+int64_t ctdk_qk_norm_rope_bwd_scratch_floats(int D) {
+  return static_cast<int64_t>(kMaxPartialRows) * 2 * (D > 0 ? D : 0);
+}
+
+int ctdk_qk_norm_rope_bwd(float* dqkv, const float* qkv_pre, const float* wq, const float* wk,
+                          const float* rstd_q, const float* rstd_k, float* dwq, float* dwk,
+                          float* scratch, const float* rope_table, int64_t B, int64_t T, int H,
+                          int Hk, int D, int accumulate_dw, void* stream) {
+  CTDK_REQUIRE(B >= 0 && T >= 0 && H > 0 && Hk > 0, "ctdk_qk_norm_rope_bwd: bad shape");
+  CTDK_REQUIRE(D == 64 || D == 128, "ctdk_qk_norm_rope_bwd: head_dim must be 64 or 128");
+  const int64_t rows = B * T;
+  const bool has_norm = wq != nullptr;
+  CTDK_REQUIRE((wq == nullptr) == (wk == nullptr), "ctdk_qk_norm_rope_bwd: wq/wk mismatch");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (rows == 0) {
+    if (has_norm && !accumulate_dw) {
+      cudaMemsetAsync(dwq, 0, sizeof(float) * D, s);
+      cudaMemsetAsync(dwk, 0, sizeof(float) * D, s);
+    }
+    return CTDK_OK;
+  }
+  CTDK_REQUIRE(dqkv && rope_table, "ctdk_qk_norm_rope_bwd: null pointer");
+  CTDK_REQUIRE(!has_norm || (qkv_pre && rstd_q && rstd_k && dwq && dwk && scratch),
+               "ctdk_qk_norm_rope_bwd: QK-Norm needs qkv_pre, rstd, dw and scratch");
+  const int64_t items = rows * (H + Hk);
+  int64_t cap = static_cast<int64_t>(sm_count()) * 2;
+  if (cap > kMaxPartialRows) cap = kMaxPartialRows;
+  const int64_t need = (items + 7) / 8;
+  const int grid = static_cast<int>(need < cap ? need : cap);
+  const float2* tb = reinterpret_cast<const float2*>(rope_table);
+  if (D == 64)
+    qk_norm_rope_bwd_kernel<1><<<grid, 256, 0, s>>>(dqkv, qkv_pre, wq, wk, rstd_q, rstd_k,
+                                                    scratch, tb, rows, T, H, Hk);
+  else
+    qk_norm_rope_bwd_kernel<2><<<grid, 256, 0, s>>>(dqkv, qkv_pre, wq, wk, rstd_q, rstd_k,
+                                                    scratch, tb, rows, T, H, Hk);
+  int rc = check_launch("ctdk_qk_norm_rope_bwd");
+  if (rc != CTDK_OK || !has_norm) return rc;
+  qk_dw_finalize_kernel<<<ceil_div(2 * D, 128), 128, 0, s>>>(scratch, dwq, dwk, grid, D,
+                                                             accumulate_dw);
+  return check_launch("ctdk_qk_norm_rope_bwd(finalize)");
+}
+
+}  // extern "C"

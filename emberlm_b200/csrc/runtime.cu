@@ -1,0 +1,102 @@
+// Error reporting, device properties and the device status word of the ctdk library.
+#include <cstdarg>
+#include <cstdio>
+#include <mutex>
+
+#include "common.cuh"
+
+namespace ctdk {
+
+namespace {
+thread_local char g_err[512] = "";
+constexpr int kMaxDevices = 64;
+int g_sm_count[kMaxDevices] = {0};
+
+// The status word lives in device global memory that belongs to the library image, so
+// kernels can report a bounded wait that ran out without any allocation.
+__device__ int g_status_word[4];
+int* g_status_ptr[kMaxDevices] = {nullptr};
+std::mutex g_mu;
+}  // namespace
+
+int fail(int code, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+  return code;
+}
+
+int check_launch(const char* what) {
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return fail(CTDK_ELAUNCH, "%s: %s", what, cudaGetErrorString(e));
+  return CTDK_OK;
+}
+
+int sm_count() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return 148;
+  if (g_sm_count[dev] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0)
+      n = 148;
+    g_sm_count[dev] = n;
+  }
+  return g_sm_count[dev];
+}
+
+int* device_status_word() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return nullptr;
+  std::lock_guard<std::mutex> lk(g_mu);
+  if (g_status_ptr[dev] == nullptr) {
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_status_word) != cudaSuccess) return nullptr;
+    g_status_ptr[dev] = static_cast<int*>(p);
+  }
+  return g_status_ptr[dev];
+}
+
+int read_device_status(cudaStream_t stream) {
+  int* p = device_status_word();
+  if (p == nullptr) return fail(CTDK_ELAUNCH, "status word unavailable");
+  int h[4] = {0, 0, 0, 0};
+  cudaError_t e = cudaMemcpyAsync(h, p, sizeof(h), cudaMemcpyDeviceToHost, stream);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(stream);
+  if (e != cudaSuccess) return fail(CTDK_ELAUNCH, "status read: %s", cudaGetErrorString(e));
+  if (h[0] != 0) {
+    cudaMemsetAsync(p, 0, sizeof(h), stream);
+    return fail(h[0], "device status %d at site %d (block %d, detail %d)", h[0], h[1], h[2],
+                h[3]);
+  }
+  return CTDK_OK;
+}
+
+}  // namespace ctdk
+
+extern "C" {
+
+const char* ctdk_last_error(void) { return ctdk::g_err; }
+
+int ctdk_sm_count(void) { return ctdk::sm_count(); }
+
+int ctdk_device_status(void* stream, int* where) {
+  int* p = ctdk::device_status_word();
+  if (p == nullptr) return ctdk::fail(CTDK_ELAUNCH, "status word unavailable");
+  int h[4] = {0, 0, 0, 0};
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  cudaError_t e = cudaMemcpyAsync(h, p, sizeof(h), cudaMemcpyDeviceToHost, s);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(s);
+  if (e != cudaSuccess) return ctdk::fail(CTDK_ELAUNCH, "status read: %s", cudaGetErrorString(e));
+  if (where != nullptr)
+    for (int i = 0; i < 4; ++i) where[i] = h[i];
+  if (h[0] != 0) {
+    cudaMemsetAsync(p, 0, sizeof(h), s);
+    cudaStreamSynchronize(s);
+    return ctdk::fail(h[0], "device status %d at site %d (block %d, detail %d)", h[0], h[1],
+                      h[2], h[3]);
+  }
+  return CTDK_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,325 @@
+"""Host-side driver of the training-step engine (libctdk.so's ctdk_engine_* entry points).
+
+torch is used for device memory, streams and torch.distributed only; every arithmetic
+kernel of the step is a ctdk kernel. Names and grouping follow the reference:
+parameters in Model::collect_parameters order with the decay / no-decay split
+(emberlm src/nn/model.cpp:63-100), AdamW hyper-parameters and bias corrections as
+optim::AdamW (src/core/optim.cu:132-168), clipping as optim::clip_grad_norm_
+(src/core/optim.cu:248-293), micro-batch semantics as tools/ctd_train/main.cpp:346-373.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import math
+from dataclasses import dataclass
+
+import numpy as np
+import torch
+
+from . import lib
+
+_L = lib.raw()
+
+
+class ModelConfig(C.Structure):
+    """ctdk_model_config; field names follow LlamaConfig (include/ctd/nn/model.h:19-37)."""
+    _fields_ = [
+        ("vocab_size", C.c_int), ("hidden_size", C.c_int), ("intermediate_size", C.c_int),
+        ("num_hidden_layers", C.c_int), ("num_attention_heads", C.c_int),
+        ("num_key_value_heads", C.c_int), ("head_dim", C.c_int),
+        ("rms_norm_eps", C.c_float), ("rope_theta", C.c_float), ("qk_norm", C.c_int),
+        ("rope_scaling_factor", C.c_float), ("rope_scaling_low_freq_factor", C.c_float),
+        ("rope_scaling_high_freq_factor", C.c_float), ("rope_scaling_original_max_pos", C.c_int),
+        ("gradient_checkpointing", C.c_int), ("precision", C.c_int),
+    ]
+
+
+def make_config(vocab_size, hidden_size, intermediate_size, num_hidden_layers, num_attention_heads,
+                num_key_value_heads, head_dim, rms_norm_eps=1e-5, rope_theta=100000.0,
+                qk_norm=False, rope_scaling_factor=0.0, rope_scaling_low_freq_factor=1.0,
+                rope_scaling_high_freq_factor=4.0, rope_scaling_original_max_pos=8192,
+                gradient_checkpointing=False, precision=lib.GEMM_TF32, **_ignored) -> ModelConfig:
+    return ModelConfig(vocab_size, hidden_size, intermediate_size, num_hidden_layers,
+                       num_attention_heads, num_key_value_heads, head_dim, rms_norm_eps, rope_theta,
+                       int(qk_norm), rope_scaling_factor, rope_scaling_low_freq_factor,
+                       rope_scaling_high_freq_factor, rope_scaling_original_max_pos,
+                       int(gradient_checkpointing), precision)
+
+
+# The five presets of include/ctd/nn/model.h:39-124.
+PRESETS = {
+    "smollm2_135m": dict(vocab_size=49152, hidden_size=576, intermediate_size=1536, num_hidden_layers=30,
+                         num_attention_heads=9, num_key_value_heads=3, head_dim=64, rms_norm_eps=1e-5,
+                         rope_theta=100000.0),
+    "smollm2_360m": dict(vocab_size=49152, hidden_size=960, intermediate_size=2560, num_hidden_layers=32,
+                         num_attention_heads=15, num_key_value_heads=5, head_dim=64, rms_norm_eps=1e-5,
+                         rope_theta=100000.0),
+    "qwen3_0_6b": dict(vocab_size=151936, hidden_size=1024, intermediate_size=3072, num_hidden_layers=28,
+                       num_attention_heads=16, num_key_value_heads=8, head_dim=128, rms_norm_eps=1e-6,
+                       rope_theta=1000000.0, qk_norm=True),
+    "qwen3_1_7b": dict(vocab_size=151936, hidden_size=2048, intermediate_size=6144, num_hidden_layers=28,
+                       num_attention_heads=16, num_key_value_heads=8, head_dim=128, rms_norm_eps=1e-6,
+                       rope_theta=1000000.0, qk_norm=True),
+    "llama3_2_1b": dict(vocab_size=128256, hidden_size=2048, intermediate_size=8192, num_hidden_layers=16,
+                        num_attention_heads=32, num_key_value_heads=8, head_dim=64, rms_norm_eps=1e-5,
+                        rope_theta=500000.0, rope_scaling_factor=32.0, rope_scaling_low_freq_factor=1.0,
+                        rope_scaling_high_freq_factor=4.0, rope_scaling_original_max_pos=8192),
+}
+
+
+def param_names(cfg: ModelConfig) -> list[str]:
+    """HF names in Model::collect_parameters order (src/nn/model.cpp:78-98)."""
+    names = ["model.embed_tokens.weight"]
+    for i in range(cfg.num_hidden_layers):
+        p = f"model.layers.{i}."
+        names += [p + "input_layernorm.weight", p + "self_attn.q_proj.weight", p + "self_attn.k_proj.weight",
+                  p + "self_attn.v_proj.weight", p + "self_attn.o_proj.weight"]
+        if cfg.qk_norm:
+            names += [p + "self_attn.q_norm.weight", p + "self_attn.k_norm.weight"]
+        names += [p + "post_attention_layernorm.weight", p + "mlp.gate_proj.weight", p + "mlp.up_proj.weight",
+                  p + "mlp.down_proj.weight"]
+    names.append("model.norm.weight")
+    return names
+
+
+def param_shapes(cfg: ModelConfig) -> list[tuple[int, ...]]:
+    hid, I, D = cfg.hidden_size, cfg.intermediate_size, cfg.head_dim
+    H, Hk = cfg.num_attention_heads, cfg.num_key_value_heads
+    shapes = [(cfg.vocab_size, hid)]
+    for _ in range(cfg.num_hidden_layers):
+        shapes += [(hid,), (H * D, hid), (Hk * D, hid), (Hk * D, hid), (hid, H * D)]
+        if cfg.qk_norm:
+            shapes += [(D,), (D,)]
+        shapes += [(hid,), (I, hid), (I, hid), (hid, I)]
+    shapes.append((hid,))
+    return shapes
+
+
+@dataclass
+class Layout:
+    names: list
+    shapes: list
+    offsets: list
+    numels: list
+    decay: list
+    total: int
+
+
+def model_layout(cfg: ModelConfig) -> Layout:
+    n = _L.ctdk_model_num_tensors(C.byref(cfg))
+    if n < 0:
+        raise lib.CtdkError(-1, lib.last_error())
+    off = (C.c_int64 * n)()
+    num = (C.c_int64 * n)()
+    dec = (C.c_int * n)()
+    total = C.c_int64()
+    lib.check(_L.ctdk_model_layout(C.byref(cfg), off, num, dec, C.byref(total)))
+    names, shapes = param_names(cfg), param_shapes(cfg)
+    assert len(names) == n and all(int(np.prod(s)) == num[i] for i, s in enumerate(shapes))
+    return Layout(names, shapes, list(off), list(num), list(dec), total.value)
+
+
+def _stream_ptr() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+_L.ctdk_model_num_tensors.restype = C.c_int64
+_L.ctdk_model_num_tensors.argtypes = [C.POINTER(ModelConfig)]
+_L.ctdk_model_layout.restype = C.c_int
+_L.ctdk_model_layout.argtypes = [C.POINTER(ModelConfig), C.POINTER(C.c_int64), C.POINTER(C.c_int64),
+                                 C.POINTER(C.c_int), C.POINTER(C.c_int64)]
+_L.ctdk_engine_workspace_bytes.restype = C.c_int64
+_L.ctdk_engine_workspace_bytes.argtypes = [C.POINTER(ModelConfig), C.c_int64, C.c_int64]
+_L.ctdk_engine_create.restype = C.c_int
+_L.ctdk_engine_create.argtypes = [C.POINTER(ModelConfig), C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64,
+                                  C.c_int64, C.c_int64, C.POINTER(C.c_void_p)]
+_L.ctdk_engine_destroy.restype = C.c_int
+_L.ctdk_engine_destroy.argtypes = [C.c_void_p]
+_L.ctdk_engine_forward_backward.restype = C.c_int
+_L.ctdk_engine_forward_backward.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
+                                            C.c_int64, C.c_int64, C.c_int, C.c_void_p, C.c_void_p]
+_L.ctdk_engine_forward_loss.restype = C.c_int
+_L.ctdk_engine_forward_loss.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64,
+                                        C.c_void_p, C.c_void_p]
+LAYER_CALLBACK = C.CFUNCTYPE(None, C.c_int, C.c_void_p)
+_L.ctdk_engine_set_layer_callback.restype = C.c_int
+_L.ctdk_engine_set_layer_callback.argtypes = [C.c_void_p, LAYER_CALLBACK, C.c_void_p]
+
+
+class TrainEngine:
+    """One rank's training state: parameter / gradient arenas, ZeRO-1 shard of AdamW m/v,
+    workspace, and the step. `group` is a torch.distributed process group (None = 1 GPU)."""
+
+    def __init__(self, cfg: ModelConfig, batch: int, seq: int, device="cuda:0", group=None,
+                 lr=1e-4, beta1=0.9, beta2=0.999, eps=1e-8, weight_decay=0.01, clip=1.0, train=True):
+        self.cfg, self.B, self.T = cfg, batch, seq
+        self.device = torch.device(device)
+        self.group = group
+        if group is not None:
+            import torch.distributed as dist
+            self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        else:
+            self.world, self.rank = 1, 0
+        self.layout = model_layout(cfg)
+        # arena padded so that it splits evenly over ranks in 64-float units
+        unit = 64 * self.world
+        self.total = (self.layout.total + unit - 1) // unit * unit
+        self.shard = self.total // self.world
+        self.params = torch.zeros(self.total, dtype=torch.float32, device=self.device)
+        self.grads = torch.zeros(self.total, dtype=torch.float32, device=self.device) if train else None
+        ws = _L.ctdk_engine_workspace_bytes(C.byref(cfg), batch, seq)
+        if ws < 0:
+            raise lib.CtdkError(-1, lib.last_error())
+        self.workspace = torch.empty(ws, dtype=torch.uint8, device=self.device)
+        self._h = C.c_void_p()
+        lib.check(_L.ctdk_engine_create(C.byref(cfg), self.params.data_ptr(),
+                                        self.grads.data_ptr() if train else None,
+                                        self.workspace.data_ptr(), ws, batch, seq, C.byref(self._h)))
+        self.loss_sums = torch.zeros(2, dtype=torch.float32, device=self.device)
+        self.hp = dict(lr=lr, beta1=beta1, beta2=beta2, eps=eps, weight_decay=weight_decay, clip=clip)
+        self.step_count = 0
+        self._cb = None
+        if train:
+            self.m = torch.zeros(self.shard, dtype=torch.float32, device=self.device)
+            self.v = torch.zeros(self.shard, dtype=torch.float32, device=self.device)
+            self._scalars = torch.zeros(4, dtype=torch.float32, device=self.device)  # sumsq, scale, norm
+            self._build_segments()
+
+    def __del__(self):
+        h = getattr(self, "_h", None)
+        if h:
+            _L.ctdk_engine_destroy(h)
+            self._h = None
+
+    # ---- parameters -------------------------------------------------------------------
+    def named_parameters(self) -> dict:
+        lo = self.layout
+        return {n: self.params[o:o + k].view(s) for n, s, o, k in zip(lo.names, lo.shapes, lo.offsets, lo.numels)}
+
+    def named_grads(self) -> dict:
+        lo = self.layout
+        return {n: self.grads[o:o + k].view(s) for n, s, o, k in zip(lo.names, lo.shapes, lo.offsets, lo.numels)}
+
+    def load_parameters(self, tensors: dict) -> None:
+        views = self.named_parameters()
+        for n, v in views.items():
+            src = tensors[n]
+            src = torch.from_numpy(np.ascontiguousarray(src)) if isinstance(src, np.ndarray) else src
+            if tuple(src.shape) != tuple(v.shape):
+                raise RuntimeError(f"load_parameters: shape mismatch for {n}")
+            v.copy_(src.to(torch.float32))
+
+    def init_parameters(self, seed=1234, std=0.02) -> None:
+        """Random-init N(0, std) for embedding / linear weights, 1.0 for every norm weight."""
+        gen = torch.Generator(device=self.device)
+        gen.manual_seed(seed)
+        self.params.zero_()
+        for (n, v), dec in zip(self.named_parameters().items(), self.layout.decay):
+            if dec:
+                v.normal_(0.0, std, generator=gen)
+            else:
+                v.fill_(1.0)
+
+    def _build_segments(self) -> None:
+        """Per-shard weight-decay segments: decay group gets weight_decay, norm weights 0
+        (the two ParamGroups of tools/ctd_train/main.cpp:304-311). Padding counts as no-decay."""
+        lo_, hi_ = self.rank * self.shard, (self.rank + 1) * self.shard
+        ends, wds = [], []
+        lo = self.layout
+        pos = lo_
+        for o, k, d in zip(lo.offsets, lo.numels, lo.decay):
+            padded_end = o + (k + 63) // 64 * 64
+            if padded_end <= lo_ or o >= hi_:
+                continue
+            end = min(padded_end, hi_)
+            wd = self.hp["weight_decay"] if d else 0.0
+            if ends and wds[-1] == wd:
+                ends[-1] = end - lo_
+            else:
+                ends.append(end - lo_)
+                wds.append(wd)
+            pos = end
+        if pos < hi_:
+            ends.append(hi_ - lo_)
+            wds.append(0.0)
+        if not ends:
+            ends, wds = [self.shard], [0.0]
+        ends[-1] = self.shard
+        self.seg_end = torch.tensor(ends, dtype=torch.int64, device=self.device)
+        self.seg_wd = torch.tensor(wds, dtype=torch.float32, device=self.device)
+
+    # ---- step -------------------------------------------------------------------------
+    def set_layer_callback(self, fn) -> None:
+        self._cb = LAYER_CALLBACK(lambda layer, _u: fn(layer)) if fn else LAYER_CALLBACK(0)
+        lib.check(_L.ctdk_engine_set_layer_callback(self._h, self._cb, None))
+
+    def forward_backward(self, ids, targets, loss_mask, row_weight, accumulate=False) -> None:
+        B, T = ids.shape
+        lib.check(_L.ctdk_engine_forward_backward(
+            self._h, ids.data_ptr(), targets.data_ptr(), loss_mask.data_ptr(), row_weight.data_ptr(),
+            B, T, int(accumulate), self.loss_sums.data_ptr(), _stream_ptr()))
+
+    def forward_loss(self, ids, targets, loss_mask) -> None:
+        B, T = ids.shape
+        lib.check(_L.ctdk_engine_forward_loss(self._h, ids.data_ptr(), targets.data_ptr(),
+                                              loss_mask.data_ptr(), B, T, self.loss_sums.data_ptr(),
+                                              _stream_ptr()))
+
+    def optimizer_step(self, lr=None) -> None:
+        """reduce-scatter(grads) -> sum of squares (+ all-reduce) -> clip scale -> fused AdamW on
+        this rank's shard -> all-gather(params). No host synchronisation."""
+        hp = self.hp
+        lr = hp["lr"] if lr is None else lr
+        s = _stream_ptr()
+        lo_, hi_ = self.rank * self.shard, (self.rank + 1) * self.shard
+        if self.world > 1:
+            import torch.distributed as dist
+            gshard = self.grads[lo_:hi_]
+            dist.reduce_scatter_tensor(gshard, self.grads, op=dist.ReduceOp.SUM, group=self.group)
+        else:
+            gshard = self.grads
+        sc = self._scalars
+        sc.zero_()
+        lib.call("ctdk_sumsq", gshard.data_ptr(), self.shard, sc.data_ptr(), s)
+        if self.world > 1:
+            import torch.distributed as dist
+            dist.all_reduce(sc[0:1], group=self.group)
+            dist.all_reduce(self.loss_sums, group=self.group)
+        lib.call("ctdk_clip_scale", sc.data_ptr(), hp["clip"], 1e-6, sc[1:].data_ptr(), sc[2:].data_ptr(), s)
+        self.step_count += 1
+        t = np.float32(self.step_count)
+        bc1 = np.float32(1.0) - np.power(np.float32(hp["beta1"]), t, dtype=np.float32)
+        bc2 = np.float32(1.0) - np.power(np.float32(hp["beta2"]), t, dtype=np.float32)
+        ap = lib.AdamWParams(lr, hp["beta1"], hp["beta2"], hp["eps"], 0.0, float(bc1), float(bc2))
+        pshard = self.params[lo_:hi_]
+        lib.call("ctdk_adamw", pshard.data_ptr(), gshard.data_ptr(), self.m.data_ptr(), self.v.data_ptr(),
+                 self.shard, C.byref(ap), sc[1:].data_ptr(), self.seg_end.data_ptr(), self.seg_wd.data_ptr(),
+                 self.seg_end.numel(), s)
+        if self.world > 1:
+            import torch.distributed as dist
+            dist.all_gather_into_tensor(self.params, pshard, group=self.group)
+
+    def train_step(self, ids, targets, loss_mask, row_weight, lr=None) -> None:
+        """One optimizer step on this rank's rows (already weighted per micro-batch)."""
+        self.loss_sums.zero_()
+        self.forward_backward(ids, targets, loss_mask, row_weight, accumulate=False)
+        self.optimizer_step(lr)
+
+    def read_metrics(self) -> dict:
+        """Synchronises and returns the logged loss (mask-weighted mean, main.cpp:365-380) and
+        the pre-clip gradient norm of the last step."""
+        ls = self.loss_sums.tolist()
+        sc = self._scalars.tolist()
+        return dict(loss=ls[0] / ls[1] if ls[1] > 0 else 0.0, mask_sum=ls[1], grad_norm=sc[2], clip_scale=sc[1])
+
+
+def row_weights(loss_mask: torch.Tensor, micro_batch: int, accum_total: int) -> torch.Tensor:
+    """w[i] = mask_i / (A * sum(mask of i's micro-batch)): the factor the reference applies
+    through mul_scalar(loss, 1/A) and the masked-CE backward (main.cpp:346-361, loss.cu:388-411).
+    loss_mask is [rows, T] with rows a multiple of micro_batch; A counts ALL micro-batches of
+    the step (over every rank). Micro-batches with an empty mask get weight 0 (main.cpp:357)."""
+    rows, T = loss_mask.shape
+    m = loss_mask.view(rows // micro_batch, micro_batch * T)
+    sm = m.sum(dim=1, keepdim=True)
+    w = torch.where(sm > 0, m / (sm * accum_total), torch.zeros_like(m))
+    return w.view(rows, T).contiguous()

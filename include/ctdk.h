@@ -1,0 +1,256 @@
+/* ctdk — C-ABI of the sm_100a kernels behind emberlm's decoder training step.
+ *
+ * Every entry point takes raw device pointers and sizes, enqueues work on `stream`
+ * (a cudaStream_t passed as void*; NULL = the legacy default stream, which is what the
+ * reference runs on) and returns 0 or a negative CTDK_E* status. Unless stated, entry
+ * points never allocate, never synchronise and never throw; ctdk_last_error() returns
+ * the message of the calling thread's last failure. Tensors are fp32, row-major and
+ * contiguous unless a leading dimension is given, exactly as the reference's ops demand
+ * (e.g. src/ops/elementwise.cu:71-81 in the reference).
+ *
+ * Each declaration cites the reference interface (file:line inside KyleCr4ne/emberlm)
+ * whose arithmetic it replaces.
+ */
+#ifndef CTDK_H_
+#define CTDK_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define CTDK_OK 0
+#define CTDK_EINVAL (-1)   /* bad argument (shape, alignment, null pointer) */
+#define CTDK_ELAUNCH (-2)  /* CUDA reported an error at launch / encode time */
+#define CTDK_ETIMEOUT (-3) /* a bounded device-side wait ran out (status word set) */
+#define CTDK_ENOMEM (-4)   /* an allocating entry point could not allocate */
+
+const char* ctdk_last_error(void);
+/* Reads (and clears) the device status word written by bounded waits; synchronises
+ * `stream`. Returns 0 or CTDK_ETIMEOUT; where[0..3] (optional) receives the raw words. */
+int ctdk_device_status(void* stream, int* where);
+int ctdk_sm_count(void);
+
+/* ------------------------------------------------------------------------------------
+ * GEMM  —  C[M,N] = op(A)·op(B) (+ epilogue), TF32 tensor cores (tcgen05, TMEM fp32
+ * accumulators, TMA-fed), optional 3xTF32 split for near-fp32 results.
+ * Replaces cublasSgemm in ops::matmul_impl (src/ops/matmul.cpp:13-49) and the two
+ * backward GEMMs of MatmulBackward (src/ops/matmul.cpp:99-118).
+ *   transa==0: A is [M,K] with leading dimension lda;  transa!=0: A is [K,M].
+ *   transb==0: B is [K,N] with leading dimension ldb;  transb!=0: B is [N,K].
+ * Shapes whose leading dimensions are not multiples of 4 floats, or pointers not
+ * 16-byte aligned, take a plain fp32 SIMT kernel (exact fp32, any shape).
+ * ------------------------------------------------------------------------------------ */
+#define CTDK_GEMM_TF32 0
+#define CTDK_GEMM_3XTF32 1
+#define CTDK_GEMM_FP32_SIMT 2 /* force the SIMT kernel (exact fp32) */
+
+#define CTDK_EPI_STORE 0      /* C = acc */
+#define CTDK_EPI_ACCUMULATE 1 /* C += acc (gradient accumulation over micro-batches) */
+#define CTDK_EPI_RESIDUAL 2   /* C = acc + aux, aux is [M,N] with leading dimension ldc */
+
+int ctdk_gemm(const float* A, const float* B, float* C, int64_t M, int64_t N, int64_t K,
+              int64_t lda, int64_t ldb, int64_t ldc, int transa, int transb, int precision,
+              int epilogue, const float* aux, void* stream);
+
+/* Batched variant with full-matrix strides, as cublasSgemmStridedBatched in
+ * ops::bmm_impl (src/ops/matmul.cpp:51-93). */
+int ctdk_bmm(const float* A, const float* B, float* C, int64_t batch, int64_t M, int64_t N,
+             int64_t K, int transa, int transb, int precision, void* stream);
+
+/* ------------------------------------------------------------------------------------
+ * RMSNorm — y = x * rsqrt(mean(x^2)+eps) * w per row of length H.
+ * Replaces rms_norm_kernel_f32 / rms_norm_backward_kernel_f32 (src/ops/norm.cu:18-106).
+ * rstd (optional, [rows]) receives the per-row scale. The backward writes dx and
+ * dw (+)= sum_rows dy*x*rstd; `dw_scratch` must hold ctdk_rmsnorm_bwd_scratch_floats(H)
+ * floats; accumulate_dw != 0 adds into dw instead of overwriting it. If add_to_dx != 0,
+ * dx += result (the residual-stream gradient is kept in one buffer).
+ * ------------------------------------------------------------------------------------ */
+int ctdk_rmsnorm_fwd(const float* x, const float* w, float* y, float* rstd, int64_t rows,
+                     int H, float eps, void* stream);
+int64_t ctdk_rmsnorm_bwd_scratch_floats(int H);
+int ctdk_rmsnorm_bwd(const float* dy, const float* x, const float* w, float* dx, float* dw,
+                     float* dw_scratch, int64_t rows, int H, float eps, int accumulate_dw,
+                     int add_to_dx, void* stream);
+
+/* ------------------------------------------------------------------------------------
+ * RoPE — non-interleaved rotation of pairs (i, i+D/2) of x[B,T,H,D] by
+ * (position_start+t)*freq_i, freq_i = theta^(-2i/D) with the llama3 wavelength scaling.
+ * Replaces rope_kernel_f32 (src/ops/rope.cu:17-56); RopeScaling fields as in
+ * include/ctd/ops/rope.h:9-22 (scaling_factor <= 1 disables scaling). sin_sign = +1
+ * forward, -1 for the transpose (backward). x_out may alias x_in. `row_stride` is the
+ * distance in floats between consecutive (b,t) rows (H*D when contiguous).
+ * ------------------------------------------------------------------------------------ */
+typedef struct {
+  float theta;
+  float scaling_factor;
+  float low_freq_wavelen;
+  float high_freq_wavelen;
+} ctdk_rope_params;
+
+int ctdk_rope(const float* x_in, float* x_out, int64_t B, int64_t T, int H, int D,
+              int64_t row_stride, int position_start, const ctdk_rope_params* p,
+              float sin_sign, void* stream);
+
+/* (cos, sin) table for positions position_start .. position_start+T-1:
+ * table[t][i] = {cosf(a), sinf(a)}, a = float(position_start+t) * freq_i, i < D/2
+ * (T*D floats). The fused kernels below read it instead of recomputing powf/sin/cos per
+ * element as rope_kernel_f32 does (src/ops/rope.cu:32-50). */
+int ctdk_rope_table(float* table, int64_t T, int D, int position_start,
+                    const ctdk_rope_params* p, void* stream);
+
+/* Fused per-head RMSNorm (optional, Qwen3 QK-Norm: include/ctd/nn/attention.h:115-118)
+ * followed by RoPE (attention.h:120-121) on the q and k slices of a packed
+ * qkv[B*T, (H+2*Hk)*D] buffer, written to qkv_out (v is copied; qkv_out may alias qkv when
+ * no norm weights are given). When wq/wk are NULL only RoPE is applied. rstd_q [B*T*H] and
+ * rstd_k [B*T*Hk] are saved for the backward. D must be 64 or 128.
+ * The backward takes d(qkv_out) in dqkv and overwrites its q and k slices with d(qkv)
+ * (v is left as is); dwq, dwk (+)= the norm-weight gradients. `scratch` must hold
+ * ctdk_qk_norm_rope_bwd_scratch_floats(D) floats when norm weights are given. */
+int ctdk_qk_norm_rope_fwd(const float* qkv, float* qkv_out, const float* wq, const float* wk,
+                          float* rstd_q, float* rstd_k, const float* rope_table, int64_t B,
+                          int64_t T, int H, int Hk, int D, float eps, void* stream);
+int64_t ctdk_qk_norm_rope_bwd_scratch_floats(int D);
+int ctdk_qk_norm_rope_bwd(float* dqkv, const float* qkv_pre, const float* wq, const float* wk,
+                          const float* rstd_q, const float* rstd_k, float* dwq, float* dwk,
+                          float* scratch, const float* rope_table, int64_t B, int64_t T, int H,
+                          int Hk, int D, int accumulate_dw, void* stream);
+
+/* ------------------------------------------------------------------------------------
+ * Elementwise. Replace add/sub/mul/scale/silu/silu_backward kernels
+ * (src/ops/elementwise.cu:15-69) and mul_scalar (src/ops/repeat_kv.cu:45).
+ * ------------------------------------------------------------------------------------ */
+int ctdk_add(const float* a, const float* b, float* out, int64_t n, void* stream);
+int ctdk_sub(const float* a, const float* b, float* out, int64_t n, void* stream);
+int ctdk_mul(const float* a, const float* b, float* out, int64_t n, void* stream);
+int ctdk_scale(const float* x, float alpha, float* out, int64_t n, void* stream);
+int ctdk_silu(const float* x, float* out, int64_t n, void* stream);
+int ctdk_silu_bwd(const float* x, const float* g, float* out, int64_t n, void* stream);
+/* SwiGLU of nn::MLP::forward (include/ctd/nn/mlp.h:16-21): act = silu(g)*u on a packed
+ * gu[rows, 2*I] buffer (gate columns first) -> act[rows, I]; backward writes dgu in the
+ * same packed layout from d(act). */
+int ctdk_swiglu_fwd(const float* gu, float* act, int64_t rows, int I, void* stream);
+int ctdk_swiglu_bwd(const float* gu, const float* dact, float* dgu, int64_t rows, int I,
+                    void* stream);
+
+/* ------------------------------------------------------------------------------------
+ * Embedding. Replaces embedding_kernel_f32 / embedding_backward_kernel_f32
+ * (src/ops/embedding.cu:15-39). ids are int64 as at the reference's ops:: API
+ * (embedding.cu:44). The backward adds dy rows into dW (the caller owns zeroing, so the
+ * tied-embedding gradient can be accumulated in place). Out-of-range ids are skipped and
+ * counted in the device status word.
+ * ------------------------------------------------------------------------------------ */
+int ctdk_embedding_fwd(const int64_t* ids, const float* W, float* out, int64_t rows, int H,
+                       int64_t V, void* stream);
+int ctdk_embedding_bwd(const int64_t* ids, const float* dy, float* dW, int64_t rows, int H,
+                       int64_t V, void* stream);
+
+/* ------------------------------------------------------------------------------------
+ * Masked cross-entropy on a block of logits[n,V] (leading dimension V).
+ * Replaces ce_masked_fwd_kernel_f32 / ce_masked_bwd_kernel_f32 (src/ops/loss.cu:254-329).
+ * row_weight[i] = mask_i * dy / sum(mask) (the factor the reference applies in
+ * CrossEntropyMaskedBackward, loss.cu:388-411). In one pass per row it computes
+ * lse_i, adds mask_i*(lse_i - z_target) to loss_sum[0] and mask_i to loss_sum[1]
+ * (loss_mask[i] is 0/1), and overwrites the logits with
+ * dlogits = row_weight_i * (softmax(z) - onehot(target)); rows of weight 0 are zero-filled
+ * exactly. lse_out (optional) receives lse per row. If dlogits_inplace == 0 the logits are
+ * left untouched (forward only).
+ * ------------------------------------------------------------------------------------ */
+int ctdk_ce_masked(float* logits, const int64_t* targets, const float* loss_mask,
+                   const float* row_weight, float* loss_sum, float* lse_out, int64_t n,
+                   int64_t V, int dlogits_inplace, void* stream);
+
+/* ------------------------------------------------------------------------------------
+ * Causal softmax attention with grouped-query heads on packed projections.
+ * Replaces the bmm -> mul_scalar -> causal mask -> softmax -> bmm chain of
+ * nn::Attention::forward_train (include/ctd/nn/attention.h:123-141) including
+ * repeat_kv_heads and the permutes. q is read at qkv[(b*T+t)*row_stride + h*D], k at
+ * column offset H*D + hk*D, v at (H+Hk)*D + hk*D; query head h uses kv head h/(H/Hk).
+ * out is [B*T, H*D]; lse [B,H,T] holds the log-sum-exp of the scaled scores.
+ * The backward takes dout [B*T,H*D] and writes dqkv in the packed layout.
+ * ------------------------------------------------------------------------------------ */
+int ctdk_attn_fwd(const float* qkv, float* out, float* lse, int64_t B, int64_t T, int H,
+                  int Hk, int D, void* stream);
+int ctdk_attn_bwd(const float* qkv, const float* out, const float* dout, const float* lse,
+                  float* delta, float* dqkv, int64_t B, int64_t T, int H, int Hk, int D,
+                  void* stream);
+
+/* ------------------------------------------------------------------------------------
+ * Optimizer. ctdk_sumsq adds sum(g^2) into out[0] (sum_sq_kernel_f32,
+ * src/core/optim.cu:221-239). ctdk_adamw is one launch over a flat range of parameters:
+ *   g' = g * grad_scale            (clip_grad_norm_'s scale, optim.cu:276-290; read from
+ *                                   device memory so no host sync is needed; NULL = 1)
+ *   m = b1 m + (1-b1) g';  v = b2 v + (1-b2) g'^2
+ *   p = p - lr * ((m/bc1) / (sqrtf(v/bc2) + eps) + wd * p)   (adamw_step_kernel_f32,
+ *                                                              optim.cu:54-73)
+ * Weight decay applies per segment: seg_end[i] is the exclusive end offset (in floats,
+ * relative to p, multiple of 4) of segment i and seg_wd[i] its decay (the reference's two
+ * ParamGroups, tools/ctd_train/main.cpp:304-311). nseg == 0 applies `wd` everywhere.
+ * ------------------------------------------------------------------------------------ */
+typedef struct {
+  float lr, beta1, beta2, eps, wd, bc1, bc2;
+} ctdk_adamw_params;
+
+int ctdk_sumsq(const float* g, int64_t n, float* out, void* stream);
+/* scale_out[0] = norm > max_norm ? max_norm/(norm+eps) : 1, norm_out[0] = norm with
+ * norm = sqrt(sumsq[0]) (clip_grad_norm_, optim.cu:274-279). */
+int ctdk_clip_scale(const float* sumsq, float max_norm, float eps, float* scale_out,
+                    float* norm_out, void* stream);
+int ctdk_adamw(float* p, const float* g, float* m, float* v, int64_t n,
+               const ctdk_adamw_params* hp, const float* grad_scale, const int64_t* seg_end,
+               const float* seg_wd, int nseg, void* stream);
+
+/* ------------------------------------------------------------------------------------
+ * Training-step engine: the fused per-layer forward/backward schedule that replaces the
+ * autograd tape walk of Model::forward_train_masked + Tensor::backward
+ * (include/ctd/nn/model.h:170-206, src/core/autograd.cu:158-237) for the decoder.
+ * The caller owns all device memory: a flat fp32 parameter arena, a gradient arena of the
+ * same layout and a workspace. The arena holds the tensors in Model::collect_parameters
+ * order (src/nn/model.cpp:78-98), each padded to a multiple of 64 floats, so q/k/v and
+ * gate/up weights are adjacent and run as one GEMM each.
+ * ------------------------------------------------------------------------------------ */
+typedef struct {
+  int vocab_size, hidden_size, intermediate_size, num_hidden_layers;
+  int num_attention_heads, num_key_value_heads, head_dim;
+  float rms_norm_eps, rope_theta;
+  int qk_norm; /* Qwen3 per-head RMSNorm on q and k before RoPE */
+  float rope_scaling_factor, rope_scaling_low_freq_factor, rope_scaling_high_freq_factor;
+  int rope_scaling_original_max_pos;
+  int gradient_checkpointing; /* keep only layer inputs; recompute inside the backward */
+  int precision;              /* CTDK_GEMM_TF32 or CTDK_GEMM_3XTF32 */
+} ctdk_model_config;          /* fields as LlamaConfig, include/ctd/nn/model.h:19-37 */
+
+/* Number of parameter tensors, and their arena layout: offsets[i], numels[i] (floats),
+ * decay[i] (1 = weight-decay group) in collect_parameters order; *total = arena floats. */
+int64_t ctdk_model_num_tensors(const ctdk_model_config* cfg);
+int ctdk_model_layout(const ctdk_model_config* cfg, int64_t* offsets, int64_t* numels,
+                      int* decay, int64_t* total);
+int64_t ctdk_engine_workspace_bytes(const ctdk_model_config* cfg, int64_t B, int64_t T);
+/* Host-side object only (no device allocation). B, T are the largest batch and sequence
+ * (positions per row, i.e. seq_len-1) the workspace was sized for. */
+int ctdk_engine_create(const ctdk_model_config* cfg, float* params, float* grads,
+                       void* workspace, int64_t workspace_bytes, int64_t B, int64_t T,
+                       void** engine);
+int ctdk_engine_destroy(void* engine);
+/* One micro-batch (or several concatenated along B): forward, masked CE and backward.
+ * ids/targets int64 [B,T], loss_mask fp32 [B,T] (0/1), row_weight fp32 [B,T] =
+ * mask * dy / sum(mask of the row's micro-batch). accumulate == 0 overwrites the gradient
+ * arena, != 0 adds to it. loss_sums (device float[2]) += {sum mask*row_loss, sum mask}. */
+int ctdk_engine_forward_backward(void* engine, const int64_t* ids, const int64_t* targets,
+                                 const float* loss_mask, const float* row_weight, int64_t B,
+                                 int64_t T, int accumulate, float* loss_sums, void* stream);
+/* Forward and loss only (the no-grad validation pass, tools/ctd_train/main.cpp:191-206). */
+int ctdk_engine_forward_loss(void* engine, const int64_t* ids, const int64_t* targets,
+                             const float* loss_mask, int64_t B, int64_t T, float* loss_sums,
+                             void* stream);
+/* Optional host callback invoked right after the backward kernels of layer `layer` have been
+ * enqueued (layer == num_hidden_layers: final norm + LM head; -1: embedding, i.e. all done),
+ * so the caller can start reducing that layer's gradients while earlier layers still run. */
+typedef void (*ctdk_layer_callback)(int layer, void* user);
+int ctdk_engine_set_layer_callback(void* engine, ctdk_layer_callback cb, void* user);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* CTDK_H_ */
