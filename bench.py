@@ -1,0 +1,367 @@
+#!/usr/bin/env python
+"""Benchmark of the decoder training step (forward + backward + clip + AdamW), data-parallel
+over N GPUs of one node. Prints ONE JSON line on rank 0.
+
+  python bench.py --gpus 1 --steps 10 --warmup 3
+  python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 \
+      --master-port P bench.py --gpus N --steps K --warmup W
+  python bench.py --impl reference ...     # the reference's own CUDA build of the same step
+
+Workload: the SmolLM2-360M-shaped decoder on a global batch of 32 rows x 1024 tokens (the step
+sees T = 1023 positions per row, as the reference's loader shifts inputs/targets), random-init
+fp32 weights, uniform synthetic token ids, ~50 % span loss masks. The batch is the reference's
+8 micro-batches of 4 rows (each normalised by its own mask sum, weighted 1/8); rank r takes
+micro-batches r, r+N, ... and runs them in one fused pass, gradients are reduce-scattered,
+AdamW runs on the rank's ZeRO-1 shard, parameters are all-gathered. Total work is fixed as N
+grows (strong scaling). `value` = positions/s with inputs resident in HBM; `e2e` = the same
+with token / mask rows coming from pinned host memory every step and the loss read back.
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes as C
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+if str(ROOT) not in sys.path:
+    sys.path.insert(0, str(ROOT))
+
+WORKLOADS = {
+    # name: (preset, global rows, seq_len, micro-batch rows, grad-accum micro-batches, checkpointing)
+    "smollm2_135m_b4x512": ("smollm2_135m", 4, 512, 4, 1, False),
+    "smollm2_360m_b32x1024": ("smollm2_360m", 32, 1024, 4, 8, False),
+    "qwen3_0_6b_b16x2048": ("qwen3_0_6b", 16, 2048, 2, 8, False),
+    "llama3_2_1b_b32x2048": ("llama3_2_1b", 32, 2048, 4, 8, True),
+    "qwen3_1_7b_b64x4096": ("qwen3_1_7b", 64, 4096, 2, 32, True),
+}
+DEFAULT_WORKLOAD = "smollm2_360m_b32x1024"
+HP = dict(lr=1e-4, beta1=0.9, beta2=0.999, eps=1e-8, weight_decay=0.01, clip=1.0)
+METRIC = "train tokens/s (fwd+bwd+AdamW)"
+
+
+def algorithmic_flops_per_step(cfg: dict, rows: int, T: int) -> float:
+    """3 * [2*tok*(P_mat + V*hid) + L*B*H*2*T^2*D]: forward + 2x backward, causal half of the
+    attention square, recomputation and masked-row skipping not counted."""
+    hid, I, D = cfg["hidden_size"], cfg["intermediate_size"], cfg["head_dim"]
+    H, Hk, L, V = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["num_hidden_layers"], cfg["vocab_size"]
+    p_mat = L * (2 * hid * H * D + 2 * hid * Hk * D + 3 * hid * I)
+    tok = rows * T
+    return 3.0 * (2.0 * tok * (p_mat + V * hid) + L * rows * H * 2.0 * T * T * D)
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.proc, self.lines = index, None, []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-lms", "200", "-i", str(self.index)], stdout=subprocess.PIPE,
+                                         stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._pump, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, power, reasons = [], [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1])); mx.append(float(f[2])); power.append(float(f[3]))
+            except ValueError:
+                continue
+            for n, v in zip(names, f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2], "sm_max_mhz": max(mx), "power_w_max": max(power),
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def measured_peaks() -> dict:
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return dict(hbm_gbs=d["hbm_gbs"], bf16_burst=d["bf16_tflops"], bf16_sustained=d["bf16_tflops_sustained"],
+                    source="measured")
+    return dict(hbm_gbs=6650.0, bf16_burst=1590.0, bf16_sustained=1400.0, source="fallback")
+
+
+def synth_rows(vocab: int, rows: int, S: int, seed: int):
+    """int32 token rows and int8 0/1 masks in the reference's bin format: mask[0] = 0, then
+    alternating spans of 16..128 positions, 'assistant' spans = 1 (about half of the positions)."""
+    import numpy as np
+    rng = np.random.default_rng(seed)
+    tok = rng.integers(0, vocab, size=(rows, S), dtype=np.int32)
+    msk = np.zeros((rows, S), dtype=np.int8)
+    for d in range(rows):
+        pos, val = 1, 0
+        while pos < S:
+            ln = int(rng.integers(16, 129))
+            msk[d, pos:pos + ln] = val
+            pos += ln
+            val ^= 1
+        if msk[d].sum() == 0:
+            msk[d, -1] = 1
+    return tok, msk
+
+
+# ----------------------------------------------------------------------------------------------
+def run_ours(args) -> dict:
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+
+    from emberlm_b200 import engine as E, lib
+
+    preset, rows, S, mb, A, ckpt = WORKLOADS[args.workload]
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run")
+    torch.cuda.set_device(local)
+    group = None
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device(f"cuda:{local}"))
+        group = dist.group.WORLD
+    if A % world != 0:
+        raise SystemExit(f"{A} micro-batches do not divide over {world} ranks")
+    T = S - 1
+    my_mbs = list(range(rank, A, world))          # micro-batches dealt round-robin
+    my_rows = len(my_mbs) * mb
+    cfgd = dict(E.PRESETS[preset])
+    cfg = E.make_config(**cfgd, gradient_checkpointing=ckpt)
+    eng = E.TrainEngine(cfg, my_rows, T, device=f"cuda:{local}", group=group, **HP)
+    eng.init_parameters(seed=1234)
+
+    # synthetic documents: a different set of rows per step, same on every rank; a rank keeps the
+    # rows of its own micro-batches
+    n_steps = args.warmup + args.steps
+    L_ = lib.raw()
+    L_.ctdk_launch_count.restype = C.c_longlong
+    L_.ctdk_prof_collect.argtypes = [C.c_int, C.POINTER(C.c_double), C.POINTER(C.c_double), C.POINTER(C.c_longlong)]
+
+    def host_batch(step):
+        tok, msk = synth_rows(cfgd["vocab_size"], rows, S, seed=4321 + step)
+        sel = np.concatenate([np.arange(j * mb, (j + 1) * mb) for j in my_mbs])
+        return tok[sel], msk[sel]
+
+    pinned_tok = [torch.empty((my_rows, S), dtype=torch.int32).pin_memory() for _ in range(2)]
+    pinned_msk = [torch.empty((my_rows, S), dtype=torch.int8).pin_memory() for _ in range(2)]
+    host = [host_batch(s) for s in range(min(n_steps, 4))]
+
+    def to_device(step, slot):
+        """H2D of one step's rows (int32 tokens + int8 masks) and on-device widening to what the
+        engine takes (int64 ids/targets, fp32 mask, per-row weights)."""
+        t, m = host[step % len(host)]
+        pinned_tok[slot].copy_(torch.from_numpy(t))
+        pinned_msk[slot].copy_(torch.from_numpy(m))
+        d_tok = pinned_tok[slot].cuda(non_blocking=True)
+        d_msk = pinned_msk[slot].cuda(non_blocking=True)
+        ids = d_tok[:, :-1].to(torch.int64).contiguous()
+        tgt = d_tok[:, 1:].to(torch.int64).contiguous()
+        mask = d_msk[:, 1:].to(torch.float32).contiguous()
+        w = E.row_weights(mask, mb, A)
+        return ids, tgt, mask, w
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(run_step, steps):
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for s in range(steps):
+            run_step(s)
+        e1.record()
+        barrier()
+        ms = torch.tensor([e0.elapsed_time(e1)], device="cuda")
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return float(ms)
+
+    # ---- device-resident arm ------------------------------------------------------------
+    resident = [to_device(s, s % 2) for s in range(len(host))]
+    torch.cuda.synchronize()
+
+    def step_resident(s):
+        ids, tgt, mask, w = resident[s % len(resident)]
+        eng.train_step(ids, tgt, mask, w)
+
+    for s in range(args.warmup):
+        step_resident(s)
+    barrier()
+    sampler = ClockSampler(local) if rank == 0 else None
+    if sampler:
+        sampler.start()
+    L_.ctdk_prof_enable(1)
+    n0 = L_.ctdk_launch_count()
+    ms_total = timed(step_resident, args.steps)
+    launches = L_.ctdk_launch_count() - n0
+    L_.ctdk_prof_enable(0)
+    clocks = sampler.stop() if sampler else None
+    prof = {}
+    for name, cls in (("gemm", 0), ("attn", 1), ("adamw", 2), ("norm", 3)):
+        a, b, n = C.c_double(), C.c_double(), C.c_longlong()
+        L_.ctdk_prof_collect(cls, C.byref(a), C.byref(b), C.byref(n))
+        prof[name] = (a.value, b.value, n.value)
+    metrics = eng.read_metrics()
+
+    # ---- end-to-end arm: rows from pinned host memory every step, loss read back ------------
+    losses = []
+
+    def step_e2e(s):
+        ids, tgt, mask, w = to_device(s, s % 2)
+        eng.train_step(ids, tgt, mask, w)
+        losses.append(eng.read_metrics()["loss"])      # D2H read of the step's loss / grad norm
+
+    step_e2e(0)
+    ms_e2e = timed(step_e2e, args.steps)
+
+    positions = rows * T
+    value = positions * args.steps / (ms_total / 1e3)
+    e2e_value = positions * args.steps / (ms_e2e / 1e3)
+    peaks = measured_peaks()
+    gemm_ms, gemm_flops, gemm_n = prof["gemm"]
+    tf32_peak = peaks["bf16_sustained"] / 2.0      # TF32 runs at half the bf16 tensor rate
+    achieved = gemm_flops / (gemm_ms / 1e3) / 1e12 if gemm_ms > 0 else 0.0
+    flops_step = algorithmic_flops_per_step(cfgd, rows, T)
+    out = {
+        "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms_total / args.steps, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "tf32 (fp32 storage, fp32 accumulate)",
+        "data": "synthetic", "impl": "ours",
+        "config": {"workload": args.workload, "global_batch": rows, "seq_len": S, "positions_per_step": positions,
+                   "micro_batch": mb, "grad_accum": A, "parallelism": f"dp{world}+zero1",
+                   "gradient_checkpointing": ckpt, "l2": "inputs larger than L2 (activations of several GB per step)",
+                   "algorithmic_tflop_per_step": flops_step / 1e12},
+        "step_tflops_per_gpu": flops_step / (ms_total / args.steps / 1e3) / 1e12 / world,
+        "step_frac_of_tf32_peak": flops_step / (ms_total / args.steps / 1e3) / 1e12 / world / tf32_peak,
+        "loss": metrics["loss"], "grad_norm": metrics["grad_norm"],
+        "e2e": {"value": e2e_value, "unit": "tokens/s", "ms_per_step": ms_e2e / args.steps,
+                "h2d_bytes_per_step": my_rows * S * 5, "d2h_bytes_per_step": 24},
+        "gpu_launches": int(launches),
+        "clocks": clocks,
+        "roofline": {"kernel": "gemm_tf32_kernel (tcgen05)", "bound": "tensor", "achieved": achieved,
+                     "peak": tf32_peak, "unit": "TFLOP/s", "frac": achieved / tf32_peak if tf32_peak else None,
+                     "peak_source": f"{peaks['source']}: bf16_tflops_sustained/2 (TF32 = half the bf16 rate)",
+                     "launches": int(gemm_n), "avg_launch_ms": gemm_ms / gemm_n if gemm_n else None,
+                     "share_of_step": gemm_ms / ms_total, "traffic": None},
+        "kernel_classes": {k: {"ms_per_step": v[0] / args.steps, "launches_per_step": v[2] / args.steps,
+                               "achieved": (v[1] / (v[0] / 1e3) / (1e12 if k in ("gemm", "attn") else 1e9)) if v[0] > 0 else None,
+                               "unit": "TFLOP/s" if k in ("gemm", "attn") else "GB/s"} for k, v in prof.items()},
+    }
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        out["cpu_baseline"] = cpu_baseline(preset)
+    if world > 1:
+        dist.destroy_process_group()
+    return out if rank == 0 else None
+
+
+def cpu_baseline(preset: str) -> dict:
+    """The numpy oracle (a port: the reference has no CPU implementation of the step) timed on the
+    host cores on a bounded sample: one row of 1024 tokens through the full model, fwd+bwd+AdamW."""
+    import numpy as np
+    from oracle import model as om
+    cfg = om.PRESETS[preset]
+    S = 1024
+    params = om.init_params(cfg, seed=1234)
+    tok, msk = om.synth_batch(cfg.vocab_size, 1, S, seed=7)
+    opt = om.AdamWState()
+    t0 = time.perf_counter()
+    om.train_step(params, cfg, [om.make_batch(tok, msk, [0])], opt, HP["lr"], HP["beta1"], HP["beta2"], HP["eps"],
+                  HP["weight_decay"], HP["clip"])
+    dt = time.perf_counter() - t0
+    return {"value": (S - 1) / dt, "unit": "tokens/s", "cores": os.cpu_count(), "kind": "port",
+            "sample": f"1 row x {S} tokens, all {cfg.num_hidden_layers} layers, fwd+bwd+clip+AdamW, numpy/BLAS fp32, {dt:.1f} s"}
+
+
+# ----------------------------------------------------------------------------------------------
+def run_reference(args) -> dict | None:
+    """Times the UNMODIFIED reference (its CUDA build, oracle/_ref/ref_harness) on the same
+    workload: same config, same micro-batch split (b rows x A micro-batches), same optimizer."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return None
+    import numpy as np
+    from oracle import model as om, ref_run
+    preset, rows, S, mb, A, ckpt = WORKLOADS[args.workload]
+    base = {"impl": "reference", "metric": METRIC, "unit": "tokens/s", "higher_is_better": True}
+    if not ref_run.available():
+        return {**base, "unavailable": "oracle/_ref/ref_harness not built (reference sources absent at build time)"}
+    cfg = om.PRESETS[preset]
+    params = om.init_params(cfg, seed=1234)
+    n_steps = args.warmup + args.steps
+    tok, msk = om.synth_batch(cfg.vocab_size, rows * min(n_steps, 4), S, seed=4321)
+    t0 = time.perf_counter()
+    try:
+        r = ref_run.run_reference(cfg, params, tok, msk, mb, A, steps=args.steps, warmup=args.warmup,
+                                  gradient_checkpointing=ckpt, want_grads=False, want_params=False, **HP)
+    except Exception as e:  # noqa: BLE001
+        return {**base, "unavailable": f"reference run failed: {str(e)[:200]}"}
+    ms = sum(r["step_ms"])
+    positions = rows * (S - 1)
+    value = positions * args.steps / (ms / 1e3)
+    return {**base, "value": value, "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": ms / args.steps, "scaling": "strong", "vs_baseline": None,
+            "dtype": "fp32 (cuBLAS SGEMM, default math mode)", "data": "synthetic",
+            "config": {"workload": args.workload, "global_batch": rows, "seq_len": S, "positions_per_step": positions,
+                       "micro_batch": mb, "grad_accum": A, "parallelism": "single GPU (the reference has no DP)",
+                       "gradient_checkpointing": ckpt},
+            "loss": r["loss"][-1], "grad_norm": r["grad_norm"][-1],
+            "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": 0, "kind": "reference",
+                             "sample": "the reference's own CUDA build on one B200 (it has no CPU path); "
+                                       f"{args.steps} steps after {args.warmup} warm-up, wall clock with device sync; "
+                                       f"whole run {time.perf_counter() - t0:.0f} s incl. weight load"},
+            "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--workload", choices=sorted(WORKLOADS), default=DEFAULT_WORKLOAD)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.warmup < 3 and args.impl == "ours":
+        print(f"note: --warmup {args.warmup} < 3; timing rules ask for at least 3", file=sys.stderr)
+    out = run_reference(args) if args.impl == "reference" else run_ours(args)
+    if out is not None:
+        print(json.dumps(out), flush=True)
+
+
+if __name__ == "__main__":
+    main()

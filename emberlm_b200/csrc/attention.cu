@@ -484,6 +484,8 @@ int ctdk_attn_fwd(const float* qkv, float* out, float* lse, int64_t B, int64_t T
   dim3 grid(static_cast<unsigned>((T + BQ - 1) / BQ), static_cast<unsigned>(H),
             static_cast<unsigned>(B));
   const int smem = (BQ + 2 * BKV) * (D + 4) * static_cast<int>(sizeof(float));
+  // causal half of 2 GEMMs: 2 * (2*T*T*D)/2 per (batch, head)
+  void* tok = prof_begin(CTDK_PROF_ATTN, 2.0 * B * H * static_cast<double>(T) * T * D, s);
   if (D == 64) {
     rc = set_smem(attn_fwd_kernel<64>, smem, "ctdk_attn_fwd");
     if (rc != CTDK_OK) return rc;
@@ -495,6 +497,7 @@ int ctdk_attn_fwd(const float* qkv, float* out, float* lse, int64_t B, int64_t T
     attn_fwd_kernel<128><<<grid, 128, smem, s>>>(qkv, out, lse, static_cast<int>(T), H, Hk,
                                                 scale_log2);
   }
+  prof_end(tok, s);
   return check_launch("ctdk_attn_fwd");
 }
 
@@ -514,6 +517,8 @@ int ctdk_attn_bwd(const float* qkv, const float* out, const float* dout, const f
   const int Ti = static_cast<int>(T);
   const float scale = 1.0f / sqrtf(static_cast<float>(D));
 
+  // backward = 2x the forward's algorithmic FLOPs (recomputation is not counted)
+  void* tok = prof_begin(CTDK_PROF_ATTN, 4.0 * B * H * static_cast<double>(T) * T * D, s);
   const int64_t items = B * T * H;
   const int64_t cap = static_cast<int64_t>(sm_count()) * 8;
   const int64_t need = (items + 7) / 8;
@@ -555,6 +560,7 @@ int ctdk_attn_bwd(const float* qkv, const float* out, const float* dout, const f
     attn_bwd_dkv_kernel<128, QT><<<gk, 128, smem_k, s>>>(qkv, dout, lse, delta, dqkv, Ti, H, Hk,
                                                         scale);
   }
+  prof_end(tok, s);
   return check_launch("ctdk_attn_bwd(dkv)");
 }
 

@@ -26,6 +26,11 @@ int* device_status_word();
 // Reads the status word (synchronises the stream); returns 0 or CTDK_ETIMEOUT.
 int read_device_status(cudaStream_t stream);
 
+// Optional CUDA-event timing of one launch on its stream (no-ops unless ctdk_prof_enable(1)):
+// cls is a CTDK_PROF_* class, work its algorithmic FLOPs or bytes.
+void* prof_begin(int cls, double work, cudaStream_t s);
+void prof_end(void* token, cudaStream_t s);
+
 inline int ceil_div(int64_t a, int64_t b) { return static_cast<int>((a + b - 1) / b); }
 
 #define CTDK_REQUIRE(cond, ...)                                   \
@@ -186,16 +191,20 @@ __device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, float (&v)[32]) {
   for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
 }
 
-// Shared-memory matrix descriptor for a 128-byte-swizzled operand tile (tcgen05 format):
-// start address, leading/stride byte offsets in 16-byte units, version 1, layout 2 (SW128).
-__device__ __forceinline__ uint64_t make_sw128_desc(uint32_t smem_addr, uint32_t lbo_bytes,
-                                                    uint32_t sbo_bytes) {
+// Shared-memory matrix descriptor (tcgen05 format): start address, leading/stride byte
+// offsets in 16-byte units, version 1, and the swizzle layout type in bits 61-63:
+//   2 = SWIZZLE_128B          (16-byte chunks XORed with the row index mod 8; K-major tiles)
+//   1 = SWIZZLE_128B_BASE32B  (32-byte chunks XORed with the row index mod 4; the only layout
+//                              the tensor core accepts for MN-major 32-bit operands)
+constexpr uint32_t kLayoutSw128 = 2, kLayoutSw128Base32 = 1;
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr, uint32_t lbo_bytes,
+                                                   uint32_t sbo_bytes, uint32_t layout_type) {
   uint64_t d = 0;
   d |= static_cast<uint64_t>((smem_addr >> 4) & 0x3fffu);
   d |= static_cast<uint64_t>((lbo_bytes >> 4) & 0x3fffu) << 16;
   d |= static_cast<uint64_t>((sbo_bytes >> 4) & 0x3fffu) << 32;
   d |= 1ull << 46;  // descriptor version for sm_100
-  d |= 2ull << 61;  // SWIZZLE_128B
+  d |= static_cast<uint64_t>(layout_type) << 61;
   return d;
 }
 

@@ -113,17 +113,22 @@ int ctdk_gemm(const float* A, const float* B, float* C, int64_t M, int64_t N, in
   CTDK_REQUIRE(A && B, "ctdk_gemm: null operand");
   CTDK_REQUIRE(lda >= (transa ? M : K), "ctdk_gemm: lda too small");
   CTDK_REQUIRE(ldb >= (transb ? K : N), "ctdk_gemm: ldb too small");
+  void* tok = prof_begin(CTDK_PROF_GEMM, 2.0 * static_cast<double>(M) * N * K, s);
   if (precision != CTDK_GEMM_FP32_SIMT) {
     int rc = (precision == CTDK_GEMM_3XTF32)
                  ? gemm_3xtf32(A, B, C, M, N, K, lda, ldb, ldc, transa, transb, epilogue, aux, s)
                  : gemm_tcgen05(A, B, C, M, N, K, lda, ldb, ldc, transa, transb, epilogue, aux,
                                 s);
-    if (rc <= 0) return rc;  // enqueued, or a real error
+    if (rc <= 0) {  // enqueued, or a real error
+      prof_end(tok, s);
+      return rc;
+    }
   }
   dim3 grid(static_cast<unsigned>((N + TS - 1) / TS), static_cast<unsigned>((M + TS - 1) / TS));
   CTDK_REQUIRE(grid.y <= 65535u, "ctdk_gemm: M too large for the SIMT path");
   gemm_simt_kernel<<<grid, 256, 0, s>>>(A, B, C, aux, M, N, K, lda, ldb, ldc, transa, transb,
                                         epilogue);
+  prof_end(tok, s);
   return check_launch("ctdk_gemm(simt)");
 }
 

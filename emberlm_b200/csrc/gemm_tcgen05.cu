@@ -11,8 +11,9 @@
 //            of tile i overlap the main loop of tile i+1.
 // Operands that are contiguous along K are loaded as one box {32 floats, rows}; operands
 // contiguous along M or N (the transposed cases of the reference's matmul, emberlm
-// src/ops/matmul.cpp:25-47,99-118) are loaded as {32 floats of M/N, 32 rows of K} boxes and
-// described to the tensor core as MN-major. M, N and K tails are zero-filled by TMA bounds
+// src/ops/matmul.cpp:25-47,99-118) are loaded as {32 floats of M/N, 32 rows of K} boxes with
+// the 32-byte-atom variant of the 128-byte swizzle and described to the tensor core as
+// MN-major. M, N and K tails are zero-filled by TMA bounds
 // checking; the epilogue predicates stores. Every mbarrier wait is bounded.
 #include <cuda.h>
 #include <cudaTypedefs.h>
@@ -183,14 +184,17 @@ __global__ void __launch_bounds__(kThreads, 1)
           const uint32_t b_addr = a_addr + kATileBytes;
 #pragma unroll
           for (int ks = 0; ks < BK / 8; ++ks) {
-            // K-major: the 8-float k-slice starts 32 bytes further inside the swizzled row;
-            // rows are 128 bytes apart, 8-row groups 1024 bytes apart (SBO).
-            // MN-major: the 8 k-rows of a slice are one 1024-byte group; the 32-float chunks
-            // along M/N are kChunkBytes apart (LBO).
-            const uint64_t adesc = A_MN ? make_sw128_desc(a_addr + ks * 1024, kChunkBytes, 1024)
-                                        : make_sw128_desc(a_addr + ks * 32, 16, 1024);
-            const uint64_t bdesc = B_MN ? make_sw128_desc(b_addr + ks * 1024, kChunkBytes, 1024)
-                                        : make_sw128_desc(b_addr + ks * 32, 16, 1024);
+            // K-major (SWIZZLE_128B): the 8-float k-slice starts 32 bytes further inside the
+            // swizzled row; rows are 128 bytes apart, 8-row groups 1024 bytes apart (SBO).
+            // MN-major (SWIZZLE_128B_BASE32B): a k-slice is 8 rows of 128 bytes = two 4-row
+            // swizzle groups 512 bytes apart (SBO); the 32-float chunks along M/N are
+            // kChunkBytes apart (LBO).
+            const uint64_t adesc =
+                A_MN ? make_smem_desc(a_addr + ks * 1024, kChunkBytes, 512, kLayoutSw128Base32)
+                     : make_smem_desc(a_addr + ks * 32, 16, 1024, kLayoutSw128);
+            const uint64_t bdesc =
+                B_MN ? make_smem_desc(b_addr + ks * 1024, kChunkBytes, 512, kLayoutSw128Base32)
+                     : make_smem_desc(b_addr + ks * 32, 16, 1024, kLayoutSw128);
             umma_tf32(d_tmem, adesc, bdesc, idesc, (kb | ks) != 0 ? 1u : 0u);
           }
           umma_commit(&empty[s]);  // stage is free once these MMAs have read it
@@ -310,9 +314,10 @@ bool tma_rounds_to_tf32() {
 }
 
 // 2-D map over a row-major fp32 matrix: dim0 = contiguous extent `inner`, dim1 = `outer`
-// rows `ld` floats apart; box = {32, box_rows}; 128-byte swizzle; out-of-range reads give 0.
+// rows `ld` floats apart; box = {32, box_rows}; 128-byte rows swizzled in 16-byte chunks
+// (K-major tiles) or 32-byte chunks (MN-major tiles); out-of-range reads give 0.
 int make_map(CUtensorMap* map, const float* base, int64_t inner, int64_t outer, int64_t ld,
-             int box_rows, bool exact_fp32) {
+             int box_rows, bool mn_major, bool exact_fp32) {
   auto enc = encode_fn();
   if (enc == nullptr) return fail(CTDK_ELAUNCH, "cuTensorMapEncodeTiled unavailable");
   cuuint64_t dims[2] = {static_cast<cuuint64_t>(inner), static_cast<cuuint64_t>(outer)};
@@ -323,7 +328,8 @@ int make_map(CUtensorMap* map, const float* base, int64_t inner, int64_t outer, 
                                      ? CU_TENSOR_MAP_DATA_TYPE_TFLOAT32
                                      : CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
   CUresult r = enc(map, dt, 2, const_cast<float*>(base), dims, strides, box, estr,
-                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   mn_major ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS)
     return fail(CTDK_ELAUNCH, "cuTensorMapEncodeTiled failed (%d): inner=%lld outer=%lld ld=%lld",
@@ -394,11 +400,11 @@ int gemm_tcgen05(const float* A, const float* B, float* Cp, int64_t M, int64_t N
 
   CUtensorMap ta, tb;
   int rc;
-  if (a_mn) rc = make_map(&ta, A, M, K, lda, BK, false);
-  else rc = make_map(&ta, A, K, M, lda, BM, false);
+  if (a_mn) rc = make_map(&ta, A, M, K, lda, BK, true, false);
+  else rc = make_map(&ta, A, K, M, lda, BM, false, false);
   if (rc != CTDK_OK) return rc;
-  if (b_mn) rc = make_map(&tb, B, N, K, ldb, BK, false);
-  else rc = make_map(&tb, B, K, N, ldb, bn, false);
+  if (b_mn) rc = make_map(&tb, B, N, K, ldb, BK, true, false);
+  else rc = make_map(&tb, B, K, N, ldb, bn, false, false);
   if (rc != CTDK_OK) return rc;
 
   GemmArgs args;

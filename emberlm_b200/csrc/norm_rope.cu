@@ -483,6 +483,7 @@ int ctdk_rmsnorm_fwd(const float* x, const float* w, float* y, float* rstd, int6
   const int64_t cap = static_cast<int64_t>(sm_count()) * 8;
   const int grid = static_cast<int>(rows < cap ? rows : cap);
   const bool vec = (H % 4 == 0) && aligned16(x) && aligned16(w) && aligned16(y) && H <= 4096;
+  void* tok = prof_begin(CTDK_PROF_NORM, 8.0 * static_cast<double>(rows) * H, s);
   if (vec) {
     const int H4 = H / 4;
     int threads = ((H4 + 31) / 32) * 32;
@@ -496,6 +497,7 @@ int ctdk_rmsnorm_fwd(const float* x, const float* w, float* y, float* rstd, int6
   } else {
     rmsnorm_fwd_generic_kernel<<<grid, 256, 0, s>>>(x, w, y, rstd, rows, H, eps);
   }
+  prof_end(tok, s);
   return check_launch("ctdk_rmsnorm_fwd");
 }
 

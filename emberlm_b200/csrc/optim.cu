@@ -180,6 +180,7 @@ int ctdk_adamw(float* p, const float* g, float* m, float* v, int64_t n,
   CTDK_REQUIRE(nseg == 0 || (seg_end && seg_wd), "ctdk_adamw: null segment table");
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const int64_t cap = static_cast<int64_t>(sm_count()) * 8;
+  void* tok = prof_begin(CTDK_PROF_ADAMW, 28.0 * static_cast<double>(n), s);
   if (aligned16(p) && aligned16(g) && aligned16(m) && aligned16(v)) {
     const int64_t need = (n / 4 + 255) / 256 + 1;
     const size_t smem = static_cast<size_t>(nseg) * (sizeof(int64_t) + sizeof(float));
@@ -190,6 +191,7 @@ int ctdk_adamw(float* p, const float* g, float* m, float* v, int64_t n,
     adamw_scalar_kernel<<<static_cast<int>(need < cap ? need : cap), 256, 0, s>>>(
         p, g, m, v, n, *hp, grad_scale, seg_end, seg_wd, nseg);
   }
+  prof_end(tok, s);
   return check_launch("ctdk_adamw");
 }
 

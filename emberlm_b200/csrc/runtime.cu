@@ -1,7 +1,9 @@
 // Error reporting, device properties and the device status word of the ctdk library.
+#include <atomic>
 #include <cstdarg>
 #include <cstdio>
 #include <mutex>
+#include <vector>
 
 #include "common.cuh"
 
@@ -27,7 +29,50 @@ int fail(int code, const char* fmt, ...) {
   return code;
 }
 
+std::atomic<long long> g_launches{0};
+
+// ---- optional per-class kernel timing with CUDA events on the launching stream ----
+struct ProfRec {
+  cudaEvent_t a, b;
+  int cls;
+  double work;
+};
+std::mutex g_prof_mu;
+bool g_prof_on = false;
+std::vector<ProfRec> g_prof;
+std::vector<cudaEvent_t> g_event_pool;
+
+cudaEvent_t take_event() {
+  if (!g_event_pool.empty()) {
+    cudaEvent_t e = g_event_pool.back();
+    g_event_pool.pop_back();
+    return e;
+  }
+  cudaEvent_t e = nullptr;
+  cudaEventCreate(&e);
+  return e;
+}
+
+bool prof_enabled() { return g_prof_on; }
+
+void* prof_begin(int cls, double work, cudaStream_t s) {
+  if (!g_prof_on) return nullptr;
+  std::lock_guard<std::mutex> lk(g_prof_mu);
+  ProfRec r{take_event(), take_event(), cls, work};
+  cudaEventRecord(r.a, s);
+  g_prof.push_back(r);
+  return reinterpret_cast<void*>(g_prof.size());
+}
+
+void prof_end(void* token, cudaStream_t s) {
+  if (token == nullptr) return;
+  std::lock_guard<std::mutex> lk(g_prof_mu);
+  const size_t i = reinterpret_cast<size_t>(token) - 1;
+  if (i < g_prof.size()) cudaEventRecord(g_prof[i].b, s);
+}
+
 int check_launch(const char* what) {
+  g_launches.fetch_add(1, std::memory_order_relaxed);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return fail(CTDK_ELAUNCH, "%s: %s", what, cudaGetErrorString(e));
   return CTDK_OK;
@@ -79,6 +124,41 @@ extern "C" {
 const char* ctdk_last_error(void) { return ctdk::g_err; }
 
 int ctdk_sm_count(void) { return ctdk::sm_count(); }
+
+long long ctdk_launch_count(void) { return ctdk::g_launches.load(); }
+
+int ctdk_prof_enable(int on) {
+  std::lock_guard<std::mutex> lk(ctdk::g_prof_mu);
+  ctdk::g_prof_on = on != 0;
+  return CTDK_OK;
+}
+
+int ctdk_prof_collect(int cls, double* total_ms, double* total_work, long long* launches) {
+  cudaDeviceSynchronize();
+  std::lock_guard<std::mutex> lk(ctdk::g_prof_mu);
+  double ms = 0.0, work = 0.0;
+  long long n = 0;
+  std::vector<ctdk::ProfRec> keep;
+  for (auto& r : ctdk::g_prof) {
+    if (r.cls != cls) {
+      keep.push_back(r);
+      continue;
+    }
+    float t = 0.0f;
+    if (cudaEventElapsedTime(&t, r.a, r.b) == cudaSuccess) {
+      ms += t;
+      work += r.work;
+      ++n;
+    }
+    ctdk::g_event_pool.push_back(r.a);
+    ctdk::g_event_pool.push_back(r.b);
+  }
+  ctdk::g_prof.swap(keep);
+  if (total_ms) *total_ms = ms;
+  if (total_work) *total_work = work;
+  if (launches) *launches = n;
+  return CTDK_OK;
+}
 
 int ctdk_device_status(void* stream, int* where) {
   int* p = ctdk::device_status_word();

@@ -31,6 +31,18 @@ const char* ctdk_last_error(void);
  * `stream`. Returns 0 or CTDK_ETIMEOUT; where[0..3] (optional) receives the raw words. */
 int ctdk_device_status(void* stream, int* where);
 int ctdk_sm_count(void);
+/* Number of kernel launches this library has enqueued in this process. */
+long long ctdk_launch_count(void);
+/* Optional live timing: while enabled, every launch of a profiled class is bracketed by CUDA
+ * events on its own stream. ctdk_prof_collect synchronises the device and returns (and clears)
+ * the summed duration in ms, the summed algorithmic work (FLOPs for CTDK_PROF_GEMM, bytes for
+ * the others) and the number of launches of class `cls`. */
+#define CTDK_PROF_GEMM 0
+#define CTDK_PROF_ATTN 1
+#define CTDK_PROF_ADAMW 2
+#define CTDK_PROF_NORM 3
+int ctdk_prof_enable(int on);
+int ctdk_prof_collect(int cls, double* total_ms, double* total_work, long long* launches);
 
 /* ------------------------------------------------------------------------------------
  * GEMM  —  C[M,N] = op(A)·op(B) (+ epilogue), TF32 tensor cores (tcgen05, TMEM fp32

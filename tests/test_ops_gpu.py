@@ -41,8 +41,10 @@ def _status_clean():
     assert rc == 0, lib.last_error()
 
 
-def relmax(got, ref):
-    return float(np.abs(got.astype(np.float64) - ref).max() / max(np.abs(ref).max(), 1e-30))
+def relmax(got, ref, floor=1e-30):
+    """max|got-ref| / max(max|ref|, floor); `floor` is the magnitude of the operands when the
+    exact answer may be (near) zero."""
+    return float(np.abs(got.astype(np.float64) - ref).max() / max(np.abs(ref).max(), floor))
 
 
 # ---------------------------------------------------------------------------------------
@@ -248,9 +250,10 @@ def test_attention_forward_backward(K, B, T, H, Hk, D):
     rref = np.concatenate([rdq, rdk, rdv], axis=2).reshape(B * T, -1)
     dqkv = host(K.attention_backward(dev(qkv), out, dev(dout), lse, B, T, H, Hk, D))
     HD, KD = H * D, Hk * D
-    assert relmax(dqkv[:, :HD], rref[:, :HD]) < 6e-3
-    assert relmax(dqkv[:, HD:HD + KD], rref[:, HD:HD + KD]) < 6e-3
-    assert relmax(dqkv[:, HD + KD:], rref[:, HD + KD:]) < 6e-3
+    # T == 1 has dq = dk = 0 exactly; the floor keeps the TF32 rounding of dP there in scale
+    assert relmax(dqkv[:, :HD], rref[:, :HD], 0.1) < 6e-3
+    assert relmax(dqkv[:, HD:HD + KD], rref[:, HD:HD + KD], 0.1) < 6e-3
+    assert relmax(dqkv[:, HD + KD:], rref[:, HD + KD:], 0.1) < 6e-3
 
 
 def test_attention_is_causal(K):
