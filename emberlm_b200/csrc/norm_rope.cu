@@ -550,6 +550,94 @@ int ctdk_rmsnorm_bwd(const float* dy, const float* x, const float* w, float* dx,
   return check_launch("ctdk_rmsnorm_bwd(finalize)");
 }
 
+// ---------------------------------------------------------------------------------------
+// RMSNorm backward without any caller- or library-allocated scratch.
+//
+// Some hosts of this library cannot hand it scratch memory and cannot let it allocate
+// either: a trainer that reserved the whole of HBM for its own arena at start-up (a
+// cudaMalloc from inside a library call would simply fail, or would force the arena to
+// shrink), and step loops that must not contain cudaMalloc/cudaFree because those calls
+// synchronise the device and stall every stream (the very cost the reference pays per op).
+// For them the per-CTA dw partial rows live in a fixed array inside the library image.
+// It costs kStaticRows * kStaticMaxH * 4 bytes = 4 MiB of device memory on every GPU that
+// loads the library, for the life of the process.
+// ---------------------------------------------------------------------------------------
+namespace ctdk {
+namespace {
+constexpr int kStaticRows = 256;   // per-CTA partial rows (upper bound of the grid)
+constexpr int kStaticMaxH = 4096;  // widest row the static variant accepts
+static __device__ __align__(256) float g_rmsnorm_static_scratch[kStaticRows * kStaticMaxH];
+
+// Device address of the array, resolved once per device. In host code the array's name is
+// only a handle for cudaGetSymbolAddress, never a pointer a kernel may be given.
+float* g_static_scratch_ptr[64] = {nullptr};
+
+int static_scratch(float** out) {
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess || dev < 0 || dev >= 64)
+    return fail(CTDK_ELAUNCH, "ctdk_rmsnorm_bwd_static: no current device");
+  if (g_static_scratch_ptr[dev] == nullptr) {
+    float* p = nullptr;
+    e = cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_rmsnorm_static_scratch);
+    if (e != cudaSuccess || p == nullptr)
+      return fail(CTDK_ELAUNCH, "ctdk_rmsnorm_bwd_static: cudaGetSymbolAddress failed: %s",
+                  cudaGetErrorString(e));
+    g_static_scratch_ptr[dev] = p;
+  }
+  *out = g_static_scratch_ptr[dev];
+  return CTDK_OK;
+}
+}  // namespace
+}  // namespace ctdk
+
+int ctdk_rmsnorm_bwd_static(const float* dy, const float* x, const float* w, float* dx,
+                            float* dw, int64_t rows, int H, float eps, int accumulate_dw,
+                            int add_to_dx, void* stream) {
+  CTDK_REQUIRE(rows >= 0 && H > 0, "ctdk_rmsnorm_bwd_static: bad shape");
+  CTDK_REQUIRE(H <= kStaticMaxH,
+               "ctdk_rmsnorm_bwd_static: H = %d exceeds the built-in scratch (max %d); use "
+               "ctdk_rmsnorm_bwd with caller-provided scratch",
+               H, kStaticMaxH);
+  CTDK_REQUIRE(dw != nullptr, "ctdk_rmsnorm_bwd_static: null dw");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (rows == 0) {
+    if (!accumulate_dw) cudaMemsetAsync(dw, 0, sizeof(float) * H, s);
+    return CTDK_OK;
+  }
+  CTDK_REQUIRE(dy && x && w && dx, "ctdk_rmsnorm_bwd_static: null pointer");
+  float* scratch = nullptr;
+  int rc = static_scratch(&scratch);  // first call on a device resolves the symbol address
+  if (rc != CTDK_OK) return rc;
+  int64_t cap = static_cast<int64_t>(sm_count()) * 2;
+  if (cap > kStaticRows) cap = kStaticRows;
+  const int grid = static_cast<int>(rows < cap ? rows : cap);
+  // Nothing in the array has to start at zero: each of the `grid` CTAs overwrites its whole
+  // partial row (the generic kernel zeroes its row itself) and the finalize pass reads only
+  // those rows, so contents left by an earlier call are never observed.
+  const bool vec =
+      (H % 4 == 0) && aligned16(dy) && aligned16(x) && aligned16(w) && aligned16(dx);
+  if (vec) {
+    const int H4 = H / 4;
+    int threads = ((H4 + 31) / 32) * 32;
+    if (threads > 256) threads = 256;
+    const int nv = (H4 + threads - 1) / threads;
+    if (nv == 1)
+      launch_rmsnorm_bwd<1>(dy, x, w, dx, scratch, rows, H, eps, add_to_dx, threads, grid, s);
+    else if (nv == 2)
+      launch_rmsnorm_bwd<2>(dy, x, w, dx, scratch, rows, H, eps, add_to_dx, threads, grid, s);
+    else
+      launch_rmsnorm_bwd<4>(dy, x, w, dx, scratch, rows, H, eps, add_to_dx, threads, grid, s);
+  } else {
+    rmsnorm_bwd_generic_kernel<<<grid, 256, 0, s>>>(dy, x, w, dx, scratch, rows, H, eps,
+                                                    add_to_dx);
+  }
+  rc = check_launch("ctdk_rmsnorm_bwd_static");
+  if (rc != CTDK_OK) return rc;
+  dw_finalize_kernel<<<ceil_div(H, 128), 128, 0, s>>>(scratch, dw, grid, H, accumulate_dw);
+  return check_launch("ctdk_rmsnorm_bwd_static(finalize)");
+}
+
 int ctdk_rope_table(float* table, int64_t T, int D, int position_start,
                     const ctdk_rope_params* p, void* stream) {
   CTDK_REQUIRE(table && p, "ctdk_rope_table: null pointer");

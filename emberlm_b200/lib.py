@@ -54,6 +54,7 @@ _SIGS = {
     "ctdk_bmm": [_p, _p, _p, _l, _l, _l, _l, _i, _i, _i, _p],
     "ctdk_rmsnorm_fwd": [_p, _p, _p, _p, _l, _i, _f, _p],
     "ctdk_rmsnorm_bwd": [_p, _p, _p, _p, _p, _p, _l, _i, _f, _i, _i, _p],
+    "ctdk_rmsnorm_bwd_static": [_p, _p, _p, _p, _p, _l, _i, _f, _i, _i, _p],
     "ctdk_rope": [_p, _p, _l, _l, _i, _i, _l, _i, C.POINTER(RopeParams), _f, _p],
     "ctdk_rope_table": [_p, _l, _i, _i, C.POINTER(RopeParams), _p],
     "ctdk_qk_norm_rope_fwd": [_p, _p, _p, _p, _p, _p, _p, _l, _l, _i, _i, _i, _f, _p],
@@ -83,6 +84,13 @@ for _name, _args in _SIGS.items():
 _lib.ctdk_last_error.restype = C.c_char_p
 _lib.ctdk_last_error.argtypes = []
 _lib.ctdk_sm_count.restype = C.c_int
+_lib.ctdk_launch_count.restype = C.c_longlong
+_lib.ctdk_launch_count.argtypes = []
+_lib.ctdk_prof_enable.restype = C.c_int
+_lib.ctdk_prof_enable.argtypes = [C.c_int]
+_lib.ctdk_prof_collect.restype = C.c_int
+_lib.ctdk_prof_collect.argtypes = [C.c_int, C.POINTER(C.c_double), C.POINTER(C.c_double),
+                                   C.POINTER(C.c_longlong)]
 _lib.ctdk_rmsnorm_bwd_scratch_floats.restype = C.c_int64
 _lib.ctdk_rmsnorm_bwd_scratch_floats.argtypes = [C.c_int]
 _lib.ctdk_qk_norm_rope_bwd_scratch_floats.restype = C.c_int64

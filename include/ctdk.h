@@ -86,6 +86,21 @@ int ctdk_rmsnorm_bwd(const float* dy, const float* x, const float* w, float* dx,
                      float* dw_scratch, int64_t rows, int H, float eps, int accumulate_dw,
                      int add_to_dx, void* stream);
 
+/* Same result as ctdk_rmsnorm_bwd, for callers that can neither pass scratch nor let the
+ * library allocate: hosts that gave all of HBM to their own arena at start-up, and step
+ * loops that must stay free of cudaMalloc/cudaFree because those stall every stream.
+ * (No counterpart in the reference, whose ops allocate on every call.)
+ * The dw partial rows live in a 4 MiB array built into the library (256 rows x 4096 floats),
+ * resident on every GPU that loads it until the process exits. H above 4096 is rejected
+ * with CTDK_EINVAL. The entry point calls no cudaMalloc, cudaFree or allocating library
+ * routine. The first call on each device looks up the array's device address (with that
+ * device current); make that first call outside any stream capture. All calls share the one
+ * array: two calls whose kernels can overlap on the GPU (different streams, no ordering
+ * between them) race on it — keep them on one stream or order them with events. */
+int ctdk_rmsnorm_bwd_static(const float* dy, const float* x, const float* w, float* dx,
+                            float* dw, int64_t rows, int H, float eps, int accumulate_dw,
+                            int add_to_dx, void* stream);
+
 /* ------------------------------------------------------------------------------------
  * RoPE — non-interleaved rotation of pairs (i, i+D/2) of x[B,T,H,D] by
  * (position_start+t)*freq_i, freq_i = theta^(-2i/D) with the llama3 wavelength scaling.
