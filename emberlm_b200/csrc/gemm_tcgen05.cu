@@ -49,6 +49,7 @@ struct GemmArgs {
   int M, N, K;
   int epilogue;
   int vec_ok;  // C (and aux) rows are 16-byte aligned and N%4==0
+  int splits;  // K is cut into `splits` ranges; >1: partial tiles are added to C with atomics
   int* status;
 };
 
@@ -92,6 +93,7 @@ __global__ void __launch_bounds__(kThreads, 1)
   const int n_blocks = (args.N + BN - 1) / BN;
   const int num_tiles = m_blocks * n_blocks;
   const int k_blocks = (args.K + BK - 1) / BK;
+  const int num_units = num_tiles * args.splits;  // unit u: tile u % num_tiles, k-range u / num_tiles
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < C::kStages; ++s) {
@@ -122,11 +124,14 @@ __global__ void __launch_bounds__(kThreads, 1)
       int s = 0;
       uint32_t ph = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      for (int unit = blockIdx.x; unit < num_units && ok; unit += gridDim.x) {
         int mb, nb;
-        tile_coords(tile, m_blocks, n_blocks, mb, nb);
+        tile_coords(unit % num_tiles, m_blocks, n_blocks, mb, nb);
         const int m0 = mb * BM, n0 = nb * BN;
-        for (int kb = 0; kb < k_blocks; ++kb) {
+        const int split = unit / num_tiles;
+        const int kb0 = static_cast<int>(static_cast<int64_t>(split) * k_blocks / args.splits);
+        const int kb1 = static_cast<int>(static_cast<int64_t>(split + 1) * k_blocks / args.splits);
+        for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait_bounded(&empty[s], ph ^ 1u, args.status, 1)) {
             ok = false;
             break;
@@ -165,7 +170,10 @@ __global__ void __launch_bounds__(kThreads, 1)
       uint32_t ph = 0;
       bool ok = true;
       int it = 0;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++it) {
+      for (int unit = blockIdx.x; unit < num_units && ok; unit += gridDim.x, ++it) {
+        const int split = unit / num_tiles;
+        const int kb0 = static_cast<int>(static_cast<int64_t>(split) * k_blocks / args.splits);
+        const int kb1 = static_cast<int>(static_cast<int64_t>(split + 1) * k_blocks / args.splits);
         const int acc = it & 1;
         const uint32_t acc_ph = (static_cast<uint32_t>(it) >> 1) & 1u;
         if (!mbar_wait_bounded(&tempty[acc], acc_ph ^ 1u, args.status, 2)) {
@@ -174,7 +182,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BN);
-        for (int kb = 0; kb < k_blocks; ++kb) {
+        for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait_bounded(&full[s], ph, args.status, 3)) {
             ok = false;
             break;
@@ -195,7 +203,7 @@ __global__ void __launch_bounds__(kThreads, 1)
             const uint64_t bdesc =
                 B_MN ? make_smem_desc(b_addr + ks * 1024, kChunkBytes, 512, kLayoutSw128Base32)
                      : make_smem_desc(b_addr + ks * 32, 16, 1024, kLayoutSw128);
-            umma_tf32(d_tmem, adesc, bdesc, idesc, (kb | ks) != 0 ? 1u : 0u);
+            umma_tf32(d_tmem, adesc, bdesc, idesc, (kb != kb0 || ks != 0) ? 1u : 0u);
           }
           umma_commit(&empty[s]);  // stage is free once these MMAs have read it
           if (++s == C::kStages) {
@@ -216,9 +224,11 @@ __global__ void __launch_bounds__(kThreads, 1)
     const int row_in_tile = q * 32 + lane;
     int it = 0;
     bool ok = true;
-    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++it) {
+    for (int unit = blockIdx.x; unit < num_units && ok; unit += gridDim.x, ++it) {
       int mb, nb;
-      tile_coords(tile, m_blocks, n_blocks, mb, nb);
+      tile_coords(unit % num_tiles, m_blocks, n_blocks, mb, nb);
+      const bool first_split = unit < num_tiles;
+      const bool atomic = args.splits > 1;
       const int acc = it & 1;
       const uint32_t acc_ph = (static_cast<uint32_t>(it) >> 1) & 1u;
       if (!mbar_wait_bounded(&tfull[acc], acc_ph, args.status, 5)) {
@@ -240,6 +250,31 @@ __global__ void __launch_bounds__(kThreads, 1)
         tmem_ld_32x32(t_row + static_cast<uint32_t>(ch * 32), v);
         if (!row_ok) {
           // rows past M hold zero-filled garbage: nothing to store
+        } else if (atomic) {
+          // split-K: C was zeroed (STORE / RESIDUAL) or holds the running sum (ACCUMULATE);
+          // every k-range adds its partial tile, the first one also adds the residual.
+          const bool add_aux = first_split && args.epilogue == CTDK_EPI_RESIDUAL;
+          if (args.vec_ok && col0 + 32 <= args.N) {
+            float4* c4 = reinterpret_cast<float4*>(crow + col0);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              float4 r = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+              if (add_aux) {
+                const float4 x = reinterpret_cast<const float4*>(xrow + col0)[j];
+                r.x += x.x;
+                r.y += x.y;
+                r.z += x.z;
+                r.w += x.w;
+              }
+              atomicAdd(&c4[j], r);
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              const int col = col0 + j;
+              if (col < args.N) atomicAdd(&crow[col], v[j] + (add_aux ? xrow[col] : 0.0f));
+            }
+          }
         } else if (args.vec_ok && col0 + 32 <= args.N) {
           float4* c4 = reinterpret_cast<float4*>(crow + col0);
           if (args.epilogue == CTDK_EPI_STORE) {
@@ -355,7 +390,7 @@ int launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmArgs& args,
     attr_set[dev] = true;
   }
   const int m_blocks = (args.M + BM - 1) / BM, n_blocks = (args.N + BN - 1) / BN;
-  const int tiles = m_blocks * n_blocks;
+  const int tiles = m_blocks * n_blocks * args.splits;
   const int sms = sm_count();
   const int grid = tiles < sms ? tiles : sms;
   kern<<<grid, kThreads, C::kSmemBytes, stream>>>(ta, tb, args);
@@ -385,17 +420,36 @@ int gemm_tcgen05(const float* A, const float* B, float* Cp, int64_t M, int64_t N
 
   const bool a_mn = transa != 0;  // A stored [K,M]: contiguous along M
   const bool b_mn = transb == 0;  // B stored [K,N]: contiguous along N
-  int bn = 256;
-  if (N <= 64) bn = 64;
-  else if (N <= 128) bn = 128;
-  else {
-    // Tensor-core time of a tile grows with its width, so compare waves x width and keep
-    // the wide tile on ties (fewer A re-reads).
-    const int64_t m_blocks = (M + BM - 1) / BM;
-    const int sms = sm_count();
-    const int64_t cost256 = ((m_blocks * ((N + 255) / 256) + sms - 1) / sms) * 256;
-    const int64_t cost128 = ((m_blocks * ((N + 127) / 128) + sms - 1) / sms) * 128;
-    bn = cost128 < cost256 ? 128 : 256;
+  // Tile width and K split: estimated time = rounds of the persistent grid x k-blocks per
+  // unit x relative cost of a k-block (a 128-wide tile does half the work of a 256-wide one
+  // but moves 2/3 of the operand bytes, hence the 0.6). Splitting K only pays when the output
+  // tiles alone cannot fill the SMs (weight gradients: few tiles, K = all tokens).
+  const int sms = sm_count();
+  const int64_t m_blocks = (M + BM - 1) / BM;
+  const int64_t k_blocks = (K + BK - 1) / BK;
+  int bn = 64, splits = 1;
+  if (N > 64) {
+    double best = 1e300;
+    const int widths[2] = {256, 128};
+    for (int wi = 0; wi < 2; ++wi) {
+      const int w = widths[wi];
+      if (w == 256 && N <= 128) continue;
+      const int64_t tiles = m_blocks * ((N + w - 1) / w);
+      const int max_splits = static_cast<int>(k_blocks / 16 < 1 ? 1 : (k_blocks / 16 > 32 ? 32 : k_blocks / 16));
+      for (int sp = 1; sp <= max_splits; ++sp) {
+        if (sp > 1 && tiles >= 2 * sms) break;
+        const int64_t units = tiles * sp;
+        const double rounds = static_cast<double>((units + sms - 1) / sms);
+        const double kb = static_cast<double>((k_blocks + sp - 1) / sp);
+        // + a fixed per-unit cost (epilogue / atomics) in k-block equivalents
+        const double t = rounds * (kb + (sp > 1 ? 12.0 : 6.0)) * (w == 256 ? 1.0 : 0.6);
+        if (t < best * 0.97) {
+          best = t;
+          bn = w;
+          splits = sp;
+        }
+      }
+    }
   }
 
   CUtensorMap ta, tb;
@@ -416,8 +470,15 @@ int gemm_tcgen05(const float* A, const float* B, float* Cp, int64_t M, int64_t N
   args.K = static_cast<int>(K);
   args.epilogue = epilogue;
   args.vec_ok = (a16(Cp) && (ldc & 3) == 0 && (aux == nullptr || a16(aux))) ? 1 : 0;
+  args.splits = splits;
   args.status = device_status_word();
   if (args.status == nullptr) return fail(CTDK_ELAUNCH, "gemm: no status word");
+  if (splits > 1 && epilogue != CTDK_EPI_ACCUMULATE) {
+    cudaError_t e = cudaMemset2DAsync(Cp, static_cast<size_t>(ldc) * sizeof(float), 0,
+                                      static_cast<size_t>(N) * sizeof(float),
+                                      static_cast<size_t>(M), stream);
+    if (e != cudaSuccess) return fail(CTDK_ELAUNCH, "gemm: memset failed: %s", cudaGetErrorString(e));
+  }
 
   switch (bn) {
     case 64: return dispatch_major<64>(a_mn, b_mn, ta, tb, args, stream);

@@ -173,7 +173,8 @@ def ints(shape, seed, lim=3):
 
 
 GEMM_SHAPES = [(128, 256, 32), (128, 128, 64), (2044, 576, 576), (300, 960, 1536), (1, 192, 576),
-               (257, 1600, 960), (130, 64, 96), (64, 8, 8), (515, 320, 100), (200, 1000, 36)]
+               (257, 1600, 960), (130, 64, 96), (64, 8, 8), (515, 320, 100), (200, 1000, 36),
+               (192, 576, 3000), (576, 200, 2044), (960, 960, 8192)]   # few tiles, long K: split-K
 
 
 @pytest.mark.parametrize("M,N,K_", GEMM_SHAPES)
@@ -208,6 +209,15 @@ def test_gemm_epilogues_and_fallbacks(K):
     assert np.array_equal(host(c), (ref + base).astype(F32))
     c2 = K.matmul(dev(a), dev(b), False, True, epilogue=lib.EPI_RESIDUAL, aux=dev(base))
     assert np.array_equal(host(c2), (ref + base).astype(F32))
+    # split-K shapes (few output tiles, long K) with every epilogue
+    a5, b5, base5 = ints((4000, 192), 40), ints((4000, 320), 41), ints((192, 320), 42)
+    ref5 = a5.T.astype(np.float64) @ b5
+    assert np.array_equal(host(K.matmul(dev(a5), dev(b5), True, False)), ref5.astype(F32))
+    c5 = dev(base5.copy())
+    K.matmul(dev(a5), dev(b5), True, False, out=c5, epilogue=lib.EPI_ACCUMULATE)
+    assert np.array_equal(host(c5), (ref5 + base5).astype(F32))
+    c6 = K.matmul(dev(a5), dev(b5), True, False, epilogue=lib.EPI_RESIDUAL, aux=dev(base5))
+    assert np.array_equal(host(c6), (ref5 + base5).astype(F32))
     # SIMT path: odd leading dimensions, exact fp32 (tests/test_matmul.cpp tolerance 1e-4)
     a3, b3 = rnd((5, 7), 27), rnd((7, 6), 28)
     np.testing.assert_allclose(host(K.matmul(dev(a3), dev(b3))), a3 @ b3, atol=1e-5)
