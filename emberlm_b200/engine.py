@@ -119,6 +119,55 @@ def model_layout(cfg: ModelConfig) -> Layout:
     return Layout(names, shapes, list(off), list(num), list(dec), total.value)
 
 
+def padded_total(layout_total: int, world: int) -> int:
+    """Arena length padded so that it splits evenly over `world` ranks in 64-float units."""
+    unit = 64 * world
+    return (layout_total + unit - 1) // unit * unit
+
+
+def shard_bounds(total_padded: int, world: int, rank: int) -> tuple[int, int]:
+    """ZeRO-1 ownership: rank r owns the contiguous slice r of parameters, gradients, m and v."""
+    shard = total_padded // world
+    return rank * shard, (rank + 1) * shard
+
+
+def deal_micro_batches(accum: int, world: int, rank: int) -> list[int]:
+    """The step's `accum` micro-batches are dealt round-robin: rank r runs r, r+world, ..."""
+    if accum % world:
+        raise ValueError(f"{accum} micro-batches do not divide over {world} ranks")
+    return list(range(rank, accum, world))
+
+
+def build_segments(layout: Layout, weight_decay: float, lo: int, hi: int):
+    """Weight-decay segments of the arena slice [lo, hi): decay group gets weight_decay, norm
+    weights 0 (the two ParamGroups of tools/ctd_train/main.cpp:304-311); padding counts as
+    no-decay. Returns (exclusive end offsets relative to lo, decay per segment)."""
+    ends, wds = [], []
+    pos = lo
+    for o, k, d in zip(layout.offsets, layout.numels, layout.decay):
+        padded_end = o + (k + 63) // 64 * 64
+        if padded_end <= lo or o >= hi:
+            continue
+        end = min(padded_end, hi)
+        wd = weight_decay if d else 0.0
+        if ends and wds[-1] == wd:
+            ends[-1] = end - lo
+        else:
+            ends.append(end - lo)
+            wds.append(wd)
+        pos = end
+    if pos < hi:
+        if ends and wds[-1] == 0.0:
+            ends[-1] = hi - lo
+        else:
+            ends.append(hi - lo)
+            wds.append(0.0)
+    if not ends:
+        ends, wds = [hi - lo], [0.0]
+    ends[-1] = hi - lo
+    return ends, wds
+
+
 def _stream_ptr() -> int:
     return torch.cuda.current_stream().cuda_stream
 
@@ -162,8 +211,7 @@ class TrainEngine:
             self.world, self.rank = 1, 0
         self.layout = model_layout(cfg)
         # arena padded so that it splits evenly over ranks in 64-float units
-        unit = 64 * self.world
-        self.total = (self.layout.total + unit - 1) // unit * unit
+        self.total = padded_total(self.layout.total, self.world)
         self.shard = self.total // self.world
         self.params = torch.zeros(self.total, dtype=torch.float32, device=self.device)
         self.grads = torch.zeros(self.total, dtype=torch.float32, device=self.device) if train else None
@@ -221,30 +269,8 @@ class TrainEngine:
                 v.fill_(1.0)
 
     def _build_segments(self) -> None:
-        """Per-shard weight-decay segments: decay group gets weight_decay, norm weights 0
-        (the two ParamGroups of tools/ctd_train/main.cpp:304-311). Padding counts as no-decay."""
-        lo_, hi_ = self.rank * self.shard, (self.rank + 1) * self.shard
-        ends, wds = [], []
-        lo = self.layout
-        pos = lo_
-        for o, k, d in zip(lo.offsets, lo.numels, lo.decay):
-            padded_end = o + (k + 63) // 64 * 64
-            if padded_end <= lo_ or o >= hi_:
-                continue
-            end = min(padded_end, hi_)
-            wd = self.hp["weight_decay"] if d else 0.0
-            if ends and wds[-1] == wd:
-                ends[-1] = end - lo_
-            else:
-                ends.append(end - lo_)
-                wds.append(wd)
-            pos = end
-        if pos < hi_:
-            ends.append(hi_ - lo_)
-            wds.append(0.0)
-        if not ends:
-            ends, wds = [self.shard], [0.0]
-        ends[-1] = self.shard
+        ends, wds = build_segments(self.layout, self.hp["weight_decay"], self.rank * self.shard,
+                                   (self.rank + 1) * self.shard)
         self.seg_end = torch.tensor(ends, dtype=torch.int64, device=self.device)
         self.seg_wd = torch.tensor(wds, dtype=torch.float32, device=self.device)
 

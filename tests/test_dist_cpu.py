@@ -1,0 +1,131 @@
+"""Data-parallel host logic on CPU with gloo, world_size 2: micro-batch dealing, per-row loss
+weights, ZeRO-1 shard ownership and the per-shard weight-decay segments. The numpy oracle does
+the arithmetic (no GPU); the result of the two-rank step must equal the single-process step of
+tools/ctd_train/main.cpp:346-373 as restated in oracle.model.train_step."""
+import os
+import socket
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from oracle import model as om
+from oracle import ops as oo
+
+HP = dict(lr=1e-3, beta1=0.9, beta2=0.999, eps=1e-8, weight_decay=0.1, clip=0.5)
+KW = dict(vocab_size=96, hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=2,
+          num_key_value_heads=1, head_dim=64, rms_norm_eps=1e-5, rope_theta=10000.0)
+A, MB, S = 4, 2, 24
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _flatten(layout, tensors, total):
+    flat = np.zeros(total, np.float32)
+    for n, o, k in zip(layout.names, layout.offsets, layout.numels):
+        flat[o:o + k] = tensors[n].reshape(-1)
+    return flat
+
+
+def _worker(rank, world, port, out):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from emberlm_b200 import engine as E
+    ocfg, ecfg = om.LlamaConfig(**KW), E.make_config(**KW)
+    layout = E.model_layout(ecfg)
+    total = E.padded_total(layout.total, world)
+    lo, hi = E.shard_bounds(total, world, rank)
+    params = om.init_params(ocfg, seed=3, std=0.05)
+    tok, msk = om.synth_batch(ocfg.vocab_size, A * MB, S, seed=4)
+    # this rank's micro-batches, fused into one pass with per-row weights
+    mine = E.deal_micro_batches(A, world, rank)
+    rows = [r for j in mine for r in range(j * MB, (j + 1) * MB)]
+    ids, tgt, m = om.make_batch(tok, msk, rows)
+    w = E.row_weights(torch.from_numpy(m), MB, A).numpy()
+    grads = None
+    for j in range(len(mine)):  # the oracle has no per-row weights: weight = dy/sum(mask) per micro-batch
+        sl = slice(j * MB, (j + 1) * MB)
+        _, _, g = om.forward_backward(params, ocfg, ids[sl], tgt[sl], m[sl], dy=1.0 / A, acc=np.float64)
+        grads = g if grads is None else {k: grads[k] + g[k] for k in g}
+        # the weights the engine would get are exactly dy/sum(mask) on the masked positions
+        assert np.allclose(w[sl][m[sl] > 0], (1.0 / A) / m[sl].sum())
+    gflat = torch.from_numpy(_flatten(layout, grads, total))
+    dist.all_reduce(gflat)                       # gloo has no reduce_scatter: sum, then keep own slice
+    gshard = gflat[lo:hi].numpy()
+    ss = torch.tensor([float((gshard.astype(np.float64) ** 2).sum())], dtype=torch.float64)
+    dist.all_reduce(ss)
+    norm = np.float32(np.sqrt(ss.item()))
+    scale = np.float32(HP["clip"]) / (norm + np.float32(1e-6)) if norm > HP["clip"] else np.float32(1.0)
+    pflat = _flatten(layout, params, total)
+    ends, wds = E.build_segments(layout, HP["weight_decay"], lo, hi)
+    new = pflat[lo:hi].copy()
+    start = 0
+    for end, wd in zip(ends, wds):
+        p, _, _ = oo.adamw_step(pflat[lo + start:lo + end], (gshard[start:end] * scale).astype(np.float32),
+                                np.zeros(end - start, np.float32), np.zeros(end - start, np.float32), 1,
+                                HP["lr"], HP["beta1"], HP["beta2"], HP["eps"], wd)
+        new[start:end] = p
+        start = end
+    gathered = [torch.zeros(hi - lo) for _ in range(world)]
+    dist.all_gather(gathered, torch.from_numpy(new))
+    if rank == 0:
+        np.save(out, np.concatenate([g.numpy() for g in gathered]))
+        np.save(out + ".norm.npy", np.array([norm]))
+    dist.destroy_process_group()
+
+
+def test_two_rank_zero1_step_equals_single_process_step(tmp_path):
+    from emberlm_b200 import engine as E
+    out = str(tmp_path / "params.npy")
+    mp.spawn(_worker, args=(2, _free_port(), out), nprocs=2, join=True)
+    got = np.load(out)
+    ocfg, ecfg = om.LlamaConfig(**KW), E.make_config(**KW)
+    layout = E.model_layout(ecfg)
+    params = om.init_params(ocfg, seed=3, std=0.05)
+    tok, msk = om.synth_batch(ocfg.vocab_size, A * MB, S, seed=4)
+    mbs = [om.make_batch(tok, msk, list(range(j * MB, (j + 1) * MB))) for j in range(A)]
+    _, norm, _ = om.train_step(params, ocfg, mbs, om.AdamWState(), HP["lr"], HP["beta1"], HP["beta2"], HP["eps"],
+                               HP["weight_decay"], HP["clip"], acc=np.float64)
+    assert abs(float(np.load(out + ".norm.npy")[0]) - norm) <= 1e-5 * norm
+    for n, o, k in zip(layout.names, layout.offsets, layout.numels):
+        ref = params[n].reshape(-1)
+        assert np.abs(got[o:o + k] - ref).max() <= 2e-5 * max(np.abs(ref).max(), 1e-12), n
+
+
+def test_shard_segments_cover_every_tensor_once():
+    from emberlm_b200 import engine as E
+    cfg = E.make_config(**E.PRESETS["qwen3_0_6b"])
+    layout = E.model_layout(cfg)
+    for world in (1, 2, 4, 8):
+        total = E.padded_total(layout.total, world)
+        assert total % (64 * world) == 0 and total >= layout.total
+        wd = np.full(total, -1.0)
+        for r in range(world):
+            lo, hi = E.shard_bounds(total, world, r)
+            ends, wds = E.build_segments(layout, 0.01, lo, hi)
+            assert ends[-1] == hi - lo and all(e % 4 == 0 for e in ends) and ends == sorted(ends)
+            start = 0
+            for e, w in zip(ends, wds):
+                wd[lo + start:lo + e] = w
+                start = e
+        assert (wd >= 0).all()
+        for o, k, d in zip(layout.offsets, layout.numels, layout.decay):
+            assert (wd[o:o + k] == (0.01 if d else 0.0)).all()
+
+
+def test_dealing_and_row_weights():
+    from emberlm_b200 import engine as E
+    assert E.deal_micro_batches(8, 4, 1) == [1, 5]
+    assert sorted(sum((E.deal_micro_batches(8, 8, r) for r in range(8)), [])) == list(range(8))
+    with pytest.raises(ValueError):
+        E.deal_micro_batches(8, 3, 0)
+    m = torch.tensor([[0, 1, 1, 0], [0, 0, 1, 0], [0, 0, 0, 0], [0, 0, 0, 0]], dtype=torch.float32)
+    w = E.row_weights(m, 2, 4)                    # micro-batch 0: 3 ones; micro-batch 1: empty mask
+    assert torch.allclose(w[:2][m[:2] > 0], torch.tensor(1.0 / (4 * 3)))
+    assert float(w[2:].abs().sum()) == 0.0 and float(w[:2][m[:2] == 0].abs().sum()) == 0.0
