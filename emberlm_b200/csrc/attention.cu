@@ -15,6 +15,12 @@
 #include "common.cuh"
 
 namespace ctdk {
+
+// tcgen05 kernels (attention_tc.cu); return 1 when a shape is not eligible.
+int attn_fwd_tcgen05(const float* qkv, float* out, float* lse, int64_t B, int64_t T, int H, int Hk,
+                     int D, cudaStream_t stream);
+bool attn_use_legacy();
+
 namespace {
 
 constexpr int BQ = 64;   // query rows per CTA (4 warps x 16)
@@ -486,6 +492,13 @@ int ctdk_attn_fwd(const float* qkv, float* out, float* lse, int64_t B, int64_t T
   const int smem = (BQ + 2 * BKV) * (D + 4) * static_cast<int>(sizeof(float));
   // causal half of 2 GEMMs: 2 * (2*T*T*D)/2 per (batch, head)
   void* tok = prof_begin(CTDK_PROF_ATTN, 2.0 * B * H * static_cast<double>(T) * T * D, s);
+  if (!attn_use_legacy()) {
+    rc = attn_fwd_tcgen05(qkv, out, lse, B, T, H, Hk, D, s);
+    if (rc <= 0) {
+      prof_end(tok, s);
+      return rc;
+    }
+  }
   if (D == 64) {
     rc = set_smem(attn_fwd_kernel<64>, smem, "ctdk_attn_fwd");
     if (rc != CTDK_OK) return rc;

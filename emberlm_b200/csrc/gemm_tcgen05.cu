@@ -373,6 +373,33 @@ int make_map(CUtensorMap* map, const float* base, int64_t inner, int64_t outer, 
   return CTDK_OK;
 }
 
+}  // namespace
+
+int encode_tensor_map(CUtensorMap* map, const float* base, int rank, const uint64_t* dims,
+                      const uint64_t* strides_bytes, const uint32_t* box, bool atom32) {
+  auto enc = encode_fn();
+  if (enc == nullptr) return fail(CTDK_ELAUNCH, "cuTensorMapEncodeTiled unavailable");
+  cuuint64_t d[5], st[4];
+  cuuint32_t bx[5], es[5];
+  for (int i = 0; i < rank; ++i) {
+    d[i] = dims[i];
+    bx[i] = box[i];
+    es[i] = 1;
+    if (i + 1 < rank) st[i] = strides_bytes[i];
+  }
+  const CUtensorMapDataType dt =
+      tma_rounds_to_tf32() ? CU_TENSOR_MAP_DATA_TYPE_TFLOAT32 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
+  CUresult r = enc(map, dt, rank, const_cast<float*>(base), d, st, bx, es,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   atom32 ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
+                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS)
+    return fail(CTDK_ELAUNCH, "cuTensorMapEncodeTiled failed (%d), rank %d", static_cast<int>(r), rank);
+  return CTDK_OK;
+}
+
+namespace {
+
 template <int BN, bool A_MN, bool B_MN>
 int launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmArgs& args,
            cudaStream_t stream) {
