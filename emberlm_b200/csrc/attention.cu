@@ -19,6 +19,10 @@ namespace ctdk {
 // tcgen05 kernels (attention_tc.cu); return 1 when a shape is not eligible.
 int attn_fwd_tcgen05(const float* qkv, float* out, float* lse, int64_t B, int64_t T, int H, int Hk,
                      int D, cudaStream_t stream);
+int attn_bwd_dq_tcgen05(const float* qkv, const float* dout, const float* lse, const float* delta,
+                        float* dqkv, int64_t B, int64_t T, int H, int Hk, int D, cudaStream_t stream);
+int attn_bwd_dkv_tcgen05(const float* qkv, const float* dout, const float* lse, const float* delta,
+                         float* dqkv, int64_t B, int64_t T, int H, int Hk, int D, cudaStream_t stream);
 bool attn_use_legacy();
 
 namespace {
@@ -545,33 +549,45 @@ int ctdk_attn_bwd(const float* qkv, const float* out, const float* dout, const f
   dim3 gk(static_cast<unsigned>((T + BKV - 1) / BKV), static_cast<unsigned>(Hk),
           static_cast<unsigned>(B));
   const int smem_q = (2 * BQ + 2 * BKV) * (D + 4) * static_cast<int>(sizeof(float));
+  // tcgen05 kernels first; each returns 1 when it does not take the shape.
+  int dq_done = 1, dkv_done = 1;
+  if (!attn_use_legacy()) {
+    dq_done = attn_bwd_dq_tcgen05(qkv, dout, lse, delta, dqkv, B, T, H, Hk, D, s);
+    if (dq_done < 0) return dq_done;
+    dkv_done = attn_bwd_dkv_tcgen05(qkv, dout, lse, delta, dqkv, B, T, H, Hk, D, s);
+    if (dkv_done < 0) return dkv_done;
+  }
   if (D == 64) {
     constexpr int QT = 64;
     const int smem_k = ((2 * BKV + 2 * QT) * (64 + 4) + 2 * QT) * static_cast<int>(sizeof(float));
-    rc = set_smem(attn_bwd_dq_kernel<64>, smem_q, "ctdk_attn_bwd");
-    if (rc != CTDK_OK) return rc;
-    rc = set_smem(attn_bwd_dkv_kernel<64, QT>, smem_k, "ctdk_attn_bwd");
-    if (rc != CTDK_OK) return rc;
-    attn_bwd_dq_kernel<64><<<gq, 128, smem_q, s>>>(qkv, dout, lse, delta, dqkv, Ti, H, Hk,
-                                                  scale);
-    rc = check_launch("ctdk_attn_bwd(dq)");
-    if (rc != CTDK_OK) return rc;
-    attn_bwd_dkv_kernel<64, QT><<<gk, 128, smem_k, s>>>(qkv, dout, lse, delta, dqkv, Ti, H, Hk,
-                                                       scale);
+    if (dq_done == 1) {
+      rc = set_smem(attn_bwd_dq_kernel<64>, smem_q, "ctdk_attn_bwd");
+      if (rc != CTDK_OK) return rc;
+      attn_bwd_dq_kernel<64><<<gq, 128, smem_q, s>>>(qkv, dout, lse, delta, dqkv, Ti, H, Hk, scale);
+      rc = check_launch("ctdk_attn_bwd(dq)");
+      if (rc != CTDK_OK) return rc;
+    }
+    if (dkv_done == 1) {
+      rc = set_smem(attn_bwd_dkv_kernel<64, QT>, smem_k, "ctdk_attn_bwd");
+      if (rc != CTDK_OK) return rc;
+      attn_bwd_dkv_kernel<64, QT><<<gk, 128, smem_k, s>>>(qkv, dout, lse, delta, dqkv, Ti, H, Hk, scale);
+    }
   } else {
     constexpr int QT = 32;
     const int smem_k =
         ((2 * BKV + 2 * QT) * (128 + 4) + 2 * QT) * static_cast<int>(sizeof(float));
-    rc = set_smem(attn_bwd_dq_kernel<128>, smem_q, "ctdk_attn_bwd");
-    if (rc != CTDK_OK) return rc;
-    rc = set_smem(attn_bwd_dkv_kernel<128, QT>, smem_k, "ctdk_attn_bwd");
-    if (rc != CTDK_OK) return rc;
-    attn_bwd_dq_kernel<128><<<gq, 128, smem_q, s>>>(qkv, dout, lse, delta, dqkv, Ti, H, Hk,
-                                                   scale);
-    rc = check_launch("ctdk_attn_bwd(dq)");
-    if (rc != CTDK_OK) return rc;
-    attn_bwd_dkv_kernel<128, QT><<<gk, 128, smem_k, s>>>(qkv, dout, lse, delta, dqkv, Ti, H, Hk,
-                                                        scale);
+    if (dq_done == 1) {
+      rc = set_smem(attn_bwd_dq_kernel<128>, smem_q, "ctdk_attn_bwd");
+      if (rc != CTDK_OK) return rc;
+      attn_bwd_dq_kernel<128><<<gq, 128, smem_q, s>>>(qkv, dout, lse, delta, dqkv, Ti, H, Hk, scale);
+      rc = check_launch("ctdk_attn_bwd(dq)");
+      if (rc != CTDK_OK) return rc;
+    }
+    if (dkv_done == 1) {
+      rc = set_smem(attn_bwd_dkv_kernel<128, QT>, smem_k, "ctdk_attn_bwd");
+      if (rc != CTDK_OK) return rc;
+      attn_bwd_dkv_kernel<128, QT><<<gk, 128, smem_k, s>>>(qkv, dout, lse, delta, dqkv, Ti, H, Hk, scale);
+    }
   }
   prof_end(tok, s);
   return check_launch("ctdk_attn_bwd(dkv)");

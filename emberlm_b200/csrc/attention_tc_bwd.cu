@@ -1,0 +1,607 @@
+// Causal grouped-query attention backward on the tcgen05 tensor cores.
+//
+// Two kernels, as in the mma.sync version (attention.cu), after delta = rowsum(dO*O):
+//   dQ kernel   one CTA per (128-query tile, head, batch), loop over key tiles:
+//               S = Q K^T and dP = dO V^T into tensor memory, the compute warps turn them into
+//               dS = P*(dP - delta)*scale in place (P = exp(S*scale - lse)), then
+//               dQ += dS K with dS read from tensor memory and K as an MN-major operand;
+//               dQ accumulates in tensor memory over all key tiles and is read once.
+//   dK/dV kernel one CTA per (128-key tile, kv head, batch), loop over the query heads of the
+//               group and the query tiles at or after the key tile (keys are the M dimension):
+//               S^T = K Q^T, dP^T = V dO^T, P^T and dS^T in place, dV += P^T dO, dK += dS^T Q;
+//               dK and dV accumulate in tensor memory, so the group sum (the reference's
+//               repeat_kv_sum, emberlm src/ops/repeat_kv.cu:29-43) needs no atomics.
+// Operands that are needed both K-major and MN-major (K in the dQ kernel; Q and dO in the dK/dV
+// kernel) are loaded twice by TMA, once per swizzle layout. Every mbarrier wait is bounded.
+#include <cfloat>
+
+#include "common.cuh"
+
+namespace ctdk {
+namespace {
+
+constexpr int TM = 128;  // rows of the CTA tile = tensor-memory lanes
+constexpr float kLog2ef = 1.4426950408889634f;
+
+__device__ __forceinline__ uint32_t idesc_b(bool b_mn, int n) {
+  return (1u << 4) | (2u << 7) | (2u << 10) | (static_cast<uint32_t>(b_mn) << 16) |
+         (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(TM >> 4) << 24);
+}
+__device__ __forceinline__ uint32_t tf32_bits(float x) {
+  uint32_t r;
+  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
+  return r;
+}
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+struct BwdArgs {
+  const float* lse;
+  const float* delta;
+  float* dqkv;
+  int T, H, Hk;
+  float scale;
+  int* status;
+};
+
+// ----------------------------------------------------------------------------------------
+// dQ kernel. TKB keys per tile, NB score buffers / K,V stages.
+// ----------------------------------------------------------------------------------------
+template <int D, int TKB, int NB>
+struct DqCfg {
+  static constexpr int kRowTile = TM * D * 4;    // Q or dO
+  static constexpr int kKeyTile = TKB * D * 4;   // K (either layout) or V
+  static constexpr int kSmem = 2 * kRowTile + NB * 3 * kKeyTile + 1024 + 256;
+  static constexpr int kCols = NB * 2 * TKB + D;
+  static constexpr uint32_t kTmemCols = kCols <= 256 ? 256 : 512;
+};
+
+template <int D, int TKB, int NB>
+__global__ void __launch_bounds__(320, 1)
+    attn_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tm_q,    // qkv, box 128 rows, K-major
+                          const __grid_constant__ CUtensorMap tm_do,   // dout, box 128 rows, K-major
+                          const __grid_constant__ CUtensorMap tm_kk,   // qkv, box TKB rows, K-major
+                          const __grid_constant__ CUtensorMap tm_km,   // qkv, box TKB rows, MN-major
+                          const BwdArgs args) {
+  using C = DqCfg<D, TKB, NB>;
+  constexpr int NC = D / 32;
+  constexpr int kRowChunk = TM * 128, kKeyChunk = TKB * 128;
+  extern __shared__ unsigned char smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  unsigned char* smem = smem_raw + ((1024u - (raw & 1023u)) & 1023u);
+  unsigned char* q_s = smem;
+  unsigned char* do_s = q_s + C::kRowTile;
+  unsigned char* kk_s = do_s + C::kRowTile;          // [NB]
+  unsigned char* km_s = kk_s + NB * C::kKeyTile;     // [NB]
+  unsigned char* v_s = km_s + NB * C::kKeyTile;      // [NB]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(v_s + NB * C::kKeyTile);
+  uint64_t* q_full = bars;          // 1 (Q and dO)
+  uint64_t* kv_full = bars + 1;     // [2] K (K-major) and V
+  uint64_t* kv_empty = bars + 3;    // [2]
+  uint64_t* km_full = bars + 5;     // [2] K (MN-major)
+  uint64_t* km_empty = bars + 7;    // [2]
+  uint64_t* sdp_full = bars + 9;    // [2]
+  uint64_t* ds_ready = bars + 11;   // [2] 256 arrivals
+  uint64_t* dq_full = bars + 13;    // 1
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 14);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int qi = gridDim.x - 1 - blockIdx.x;
+  const int h = blockIdx.y, b = blockIdx.z;
+  const int hk = h / (args.H / args.Hk);
+  const int q0 = qi * TM;
+  const int last_key = min(q0 + TM, args.T) - 1;
+  const int n_tiles = last_key / TKB + 1;
+  const int col_q = h * D, col_k = (args.H + hk) * D, col_v = (args.H + args.Hk + hk) * D;
+
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&kv_full[i], 1);
+      mbar_init(&kv_empty[i], 1);
+      mbar_init(&km_full[i], 1);
+      mbar_init(&km_empty[i], 1);
+      mbar_init(&sdp_full[i], 1);
+      mbar_init(&ds_ready[i], 256);
+    }
+    mbar_init(dq_full, 1);
+    mbar_fence_init();
+    tma_prefetch_desc(&tm_q);
+    tma_prefetch_desc(&tm_do);
+    tma_prefetch_desc(&tm_kk);
+    tma_prefetch_desc(&tm_km);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, C::kTmemCols);
+    tmem_relinquish();
+    tc_fence_before();
+  }
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  auto tm_s = [&](int i) { return tmem_base + static_cast<uint32_t>(i * 2 * TKB); };          // S, later dS
+  auto tm_dp = [&](int i) { return tmem_base + static_cast<uint32_t>(i * 2 * TKB + TKB); };   // dP
+  const uint32_t tm_dq = tmem_base + static_cast<uint32_t>(NB * 2 * TKB);
+
+  if (warp == 0) {
+    if (lane == 0) {
+      mbar_expect_tx(q_full, 2 * C::kRowTile);
+#pragma unroll
+      for (int c = 0; c < NC; ++c) {
+        tma_load_3d(q_s + c * kRowChunk, &tm_q, q_full, col_q + 32 * c, q0, b);
+        tma_load_3d(do_s + c * kRowChunk, &tm_do, q_full, col_q + 32 * c, q0, b);
+      }
+      for (int j = 0; j < n_tiles; ++j) {
+        const int s = j % NB;
+        const uint32_t ph = static_cast<uint32_t>(j / NB) & 1u;
+        if (!mbar_wait_bounded(&kv_empty[s], ph ^ 1u, args.status, 41)) break;
+        mbar_expect_tx(&kv_full[s], 2 * C::kKeyTile);
+#pragma unroll
+        for (int c = 0; c < NC; ++c) {
+          tma_load_3d(kk_s + s * C::kKeyTile + c * kKeyChunk, &tm_kk, &kv_full[s], col_k + 32 * c, j * TKB, b);
+          tma_load_3d(v_s + s * C::kKeyTile + c * kKeyChunk, &tm_kk, &kv_full[s], col_v + 32 * c, j * TKB, b);
+        }
+        if (!mbar_wait_bounded(&km_empty[s], ph ^ 1u, args.status, 42)) break;
+        mbar_expect_tx(&km_full[s], C::kKeyTile);
+#pragma unroll
+        for (int c = 0; c < NC; ++c)
+          tma_load_3d(km_s + s * C::kKeyTile + c * kKeyChunk, &tm_km, &km_full[s], col_k + 32 * c, j * TKB, b);
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const uint32_t idesc_s = idesc_b(false, TKB);
+      const uint32_t idesc_dq = idesc_b(true, D);
+      bool ok = mbar_wait_bounded(q_full, 0, args.status, 43);
+      tc_fence_after();
+      const uint32_t q_addr = smem_u32(q_s), do_addr = smem_u32(do_s);
+      auto issue_sdp = [&](int j) {
+        const int s = j % NB;
+        if (!mbar_wait_bounded(&kv_full[s], static_cast<uint32_t>(j / NB) & 1u, args.status, 44)) return false;
+        tc_fence_after();
+        const uint32_t k_addr = smem_u32(kk_s + s * C::kKeyTile), v_addr = smem_u32(v_s + s * C::kKeyTile);
+#pragma unroll
+        for (int ks = 0; ks < D / 8; ++ks) {
+          const uint32_t ao = static_cast<uint32_t>((ks >> 2) * kRowChunk + (ks & 3) * 32);
+          const uint32_t bo = static_cast<uint32_t>((ks >> 2) * kKeyChunk + (ks & 3) * 32);
+          umma_tf32(tm_s(s), make_smem_desc(q_addr + ao, 16, 1024, kLayoutSw128),
+                    make_smem_desc(k_addr + bo, 16, 1024, kLayoutSw128), idesc_s, ks != 0 ? 1u : 0u);
+        }
+#pragma unroll
+        for (int ks = 0; ks < D / 8; ++ks) {
+          const uint32_t ao = static_cast<uint32_t>((ks >> 2) * kRowChunk + (ks & 3) * 32);
+          const uint32_t bo = static_cast<uint32_t>((ks >> 2) * kKeyChunk + (ks & 3) * 32);
+          umma_tf32(tm_dp(s), make_smem_desc(do_addr + ao, 16, 1024, kLayoutSw128),
+                    make_smem_desc(v_addr + bo, 16, 1024, kLayoutSw128), idesc_s, ks != 0 ? 1u : 0u);
+        }
+        umma_commit(&kv_empty[s]);
+        umma_commit(&sdp_full[s]);
+        return true;
+      };
+      auto issue_dq = [&](int jj) {
+        const int s = jj % NB;
+        const uint32_t ph = static_cast<uint32_t>(jj / NB) & 1u;
+        if (!mbar_wait_bounded(&ds_ready[s], ph, args.status, 45)) return false;
+        if (!mbar_wait_bounded(&km_full[s], ph, args.status, 46)) return false;
+        tc_fence_after();
+        const uint32_t k_addr = smem_u32(km_s + s * C::kKeyTile);
+#pragma unroll
+        for (int ks = 0; ks < TKB / 8; ++ks)
+          umma_tf32_ta(tm_dq, tm_s(s) + static_cast<uint32_t>(ks * 8),
+                       make_smem_desc(k_addr + ks * 1024, kKeyChunk, 512, kLayoutSw128Base32), idesc_dq,
+                       (jj != 0 || ks != 0) ? 1u : 0u);
+        umma_commit(&km_empty[s]);
+        return true;
+      };
+      for (int j = 0; j <= n_tiles && ok; ++j) {
+        if (NB == 2 && j < n_tiles) ok = issue_sdp(j);
+        if (ok && j >= 1) ok = issue_dq(j - 1);
+        if (NB == 1 && ok && j < n_tiles) ok = issue_sdp(j);
+      }
+      umma_commit(dq_full);
+    }
+    __syncwarp();
+  } else {
+    // 8 compute warps: warp pair (w, w+4) shares a lane quarter, each takes half of the keys.
+    const int cw = warp - 2;
+    const int qd = warp & 3, half = cw >> 2;
+    const int row = q0 + qd * 32 + lane;
+    const uint32_t lane_off = static_cast<uint32_t>(qd * 32) << 16;
+    const int64_t lbase = (static_cast<int64_t>(b) * args.H + h) * args.T;
+    const bool row_ok = row < args.T;
+    const float lse2 = row_ok ? args.lse[lbase + row] * kLog2ef : FLT_MAX;
+    const float dl = row_ok ? args.delta[lbase + row] : 0.0f;
+    const float sc2 = args.scale * kLog2ef;
+    constexpr int HC = TKB / 2;  // columns per thread and tile
+    bool ok = true;
+    for (int j = 0; j < n_tiles && ok; ++j) {
+      const int s = j % NB;
+      if (!mbar_wait_bounded(&sdp_full[s], static_cast<uint32_t>(j / NB) & 1u, args.status, 47)) { ok = false; break; }
+      tc_fence_after();
+      const int key0 = j * TKB + half * HC;
+#pragma unroll
+      for (int c = 0; c < HC / 32; ++c) {
+        float sv[32], dv[32];
+        uint32_t ob[32];
+        tmem_ld_32x32(tm_s(s) + lane_off + half * HC + c * 32, sv);
+        tmem_ld_32x32(tm_dp(s) + lane_off + half * HC + c * 32, dv);
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const float p = (key0 + c * 32 + i > row) ? 0.0f : ex2(sv[i] * sc2 - lse2);
+          ob[i] = tf32_bits(p * (dv[i] - dl) * args.scale);
+        }
+        tmem_st_32x32(tm_s(s) + lane_off + half * HC + c * 32, ob);
+      }
+      tmem_wait_st();
+      tc_fence_before();
+      mbar_arrive(&ds_ready[s]);
+    }
+    if (ok && mbar_wait_bounded(dq_full, 0, args.status, 48)) {
+      tc_fence_after();
+      const int64_t RS = static_cast<int64_t>(args.H + 2 * args.Hk) * D;
+      float* dst = args.dqkv + (static_cast<int64_t>(b) * args.T + row) * RS + static_cast<int64_t>(h) * D;
+#pragma unroll
+      for (int c = 0; c < D / 64; ++c) {
+        float v[32];
+        const int col = half * (D / 2) + c * 32;
+        tmem_ld_32x32(tm_dq + lane_off + col, v);
+        if (row_ok) {
+#pragma unroll
+          for (int i = 0; i < 8; ++i)
+            reinterpret_cast<float4*>(dst + col)[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+        }
+        __syncwarp();
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, C::kTmemCols);
+  }
+}
+
+int map3(CUtensorMap* m, const float* base, int64_t inner, int64_t T, int64_t B, int rows, bool atom32) {
+  const uint64_t dims[3] = {static_cast<uint64_t>(inner), static_cast<uint64_t>(T), static_cast<uint64_t>(B)};
+  const uint64_t strides[2] = {static_cast<uint64_t>(inner) * 4, static_cast<uint64_t>(T) * inner * 4};
+  const uint32_t box[3] = {32u, static_cast<uint32_t>(rows), 1u};
+  return encode_tensor_map(m, base, 3, dims, strides, box, atom32);
+}
+
+template <int D, int TKB, int NB>
+int launch_dq(const float* qkv, const float* dout, const BwdArgs& a, int64_t B, cudaStream_t s) {
+  using C = DqCfg<D, TKB, NB>;
+  const int RS = (a.H + 2 * a.Hk) * D;
+  CUtensorMap tq, tdo, tkk, tkm;
+  int rc = map3(&tq, qkv, RS, a.T, B, TM, false);
+  if (rc == CTDK_OK) rc = map3(&tdo, dout, static_cast<int64_t>(a.H) * D, a.T, B, TM, false);
+  if (rc == CTDK_OK) rc = map3(&tkk, qkv, RS, a.T, B, TKB, false);
+  if (rc == CTDK_OK) rc = map3(&tkm, qkv, RS, a.T, B, TKB, true);
+  if (rc != CTDK_OK) return rc;
+  auto* kern = attn_bwd_dq_tc_kernel<D, TKB, NB>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmem);
+  if (e != cudaSuccess) return fail(CTDK_ELAUNCH, "attn_bwd dq(tcgen05): shared memory opt-in failed: %s", cudaGetErrorString(e));
+  dim3 grid(static_cast<unsigned>((a.T + TM - 1) / TM), static_cast<unsigned>(a.H), static_cast<unsigned>(B));
+  kern<<<grid, 320, C::kSmem, s>>>(tq, tdo, tkk, tkm, a);
+  return check_launch("ctdk_attn_bwd(dq, tcgen05)");
+}
+
+}  // namespace
+
+// dQ part of the backward. Returns CTDK_OK, a negative status, or 1 when not eligible.
+int attn_bwd_dq_tcgen05(const float* qkv, const float* dout, const float* lse, const float* delta, float* dqkv,
+                        int64_t B, int64_t T, int H, int Hk, int D, cudaStream_t stream) {
+  if ((reinterpret_cast<uintptr_t>(qkv) & 15u) || (reinterpret_cast<uintptr_t>(dout) & 15u) ||
+      (reinterpret_cast<uintptr_t>(dqkv) & 15u))
+    return 1;
+  BwdArgs a;
+  a.lse = lse;
+  a.delta = delta;
+  a.dqkv = dqkv;
+  a.T = static_cast<int>(T);
+  a.H = H;
+  a.Hk = Hk;
+  a.scale = 1.0f / sqrtf(static_cast<float>(D));
+  a.status = device_status_word();
+  if (a.status == nullptr) return fail(CTDK_ELAUNCH, "attn_bwd(tcgen05): no status word");
+  return D == 64 ? launch_dq<64, 64, 2>(qkv, dout, a, B, stream) : launch_dq<128, 64, 1>(qkv, dout, a, B, stream);
+}
+
+// ----------------------------------------------------------------------------------------
+// dK/dV kernel. Keys are the M dimension (tensor-memory lanes). TQB queries per step, NB stages.
+// ----------------------------------------------------------------------------------------
+namespace {
+
+template <int D, int TQB, int NB>
+struct DkvCfg {
+  static constexpr int kKeyTile = TM * D * 4;    // K or V, resident
+  static constexpr int kQTile = TQB * D * 4;     // Q or dO in one layout
+  static constexpr int kSmem = 2 * kKeyTile + NB * 4 * kQTile + 1024 /*align*/ + 1024 /*lse, delta*/ + 256;
+  static constexpr int kCols = NB * 2 * TQB + 2 * D;
+  static constexpr uint32_t kTmemCols = kCols <= 256 ? 256 : 512;
+  static constexpr int kComputeWarps = 4 * (TQB / 32);
+  static constexpr int kThreads = 64 + 32 * kComputeWarps;
+};
+
+template <int D, int TQB, int NB>
+__global__ void __launch_bounds__(DkvCfg<D, TQB, NB>::kThreads, 1)
+    attn_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tm_kv,   // qkv, box 128 rows, K-major
+                           const __grid_constant__ CUtensorMap tm_qk,   // qkv, box TQB rows, K-major
+                           const __grid_constant__ CUtensorMap tm_dok,  // dout, box TQB rows, K-major
+                           const __grid_constant__ CUtensorMap tm_qm,   // qkv, box TQB rows, MN-major
+                           const __grid_constant__ CUtensorMap tm_dom,  // dout, box TQB rows, MN-major
+                           const BwdArgs args) {
+  using C = DkvCfg<D, TQB, NB>;
+  constexpr int NC = D / 32;
+  constexpr int kKeyChunk = TM * 128, kQChunk = TQB * 128;
+  constexpr int NCW = C::kComputeWarps * 32;
+  extern __shared__ unsigned char smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  unsigned char* smem = smem_raw + ((1024u - (raw & 1023u)) & 1023u);
+  unsigned char* k_s = smem;
+  unsigned char* v_s = k_s + C::kKeyTile;
+  unsigned char* qk_s = v_s + C::kKeyTile;            // [NB] Q  K-major
+  unsigned char* dok_s = qk_s + NB * C::kQTile;       // [NB] dO K-major
+  unsigned char* qm_s = dok_s + NB * C::kQTile;       // [NB] Q  MN-major
+  unsigned char* dom_s = qm_s + NB * C::kQTile;       // [NB] dO MN-major
+  float* s_lse = reinterpret_cast<float*>(dom_s + NB * C::kQTile);   // [2][TQB]
+  float* s_del = s_lse + 2 * TQB;                                    // [2][TQB]  (NB <= 2)
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 2 * C::kKeyTile + NB * 4 * C::kQTile + 1024);
+  uint64_t* kv_full = bars;         // 1
+  uint64_t* qk_full = bars + 1;     // [2]
+  uint64_t* qk_empty = bars + 3;    // [2]
+  uint64_t* qm_full = bars + 5;     // [2]
+  uint64_t* qm_empty = bars + 7;    // [2]
+  uint64_t* sdp_full = bars + 9;    // [2]
+  uint64_t* pds_ready = bars + 11;  // [2] NCW arrivals
+  uint64_t* done_bar = bars + 13;   // 1
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 14);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int kj = blockIdx.x;  // key tile; low tiles have the most query tiles and start first
+  const int hk = blockIdx.y, b = blockIdx.z;
+  const int G = args.H / args.Hk;
+  const int k0 = kj * TM;
+  const int n_qt = (args.T + TQB - 1) / TQB;
+  const int first_qt = k0 / TQB;
+  const int per_head = n_qt - first_qt;
+  const int n_units = G * per_head;
+  const int col_k = (args.H + hk) * D, col_v = (args.H + args.Hk + hk) * D;
+
+  if (threadIdx.x == 0) {
+    mbar_init(kv_full, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&qk_full[i], 1);
+      mbar_init(&qk_empty[i], 1);
+      mbar_init(&qm_full[i], 1);
+      mbar_init(&qm_empty[i], 1);
+      mbar_init(&sdp_full[i], 1);
+      mbar_init(&pds_ready[i], NCW);
+    }
+    mbar_init(done_bar, 1);
+    mbar_fence_init();
+    tma_prefetch_desc(&tm_kv);
+    tma_prefetch_desc(&tm_qk);
+    tma_prefetch_desc(&tm_dok);
+    tma_prefetch_desc(&tm_qm);
+    tma_prefetch_desc(&tm_dom);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, C::kTmemCols);
+    tmem_relinquish();
+    tc_fence_before();
+  }
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  auto tm_s = [&](int i) { return tmem_base + static_cast<uint32_t>(i * 2 * TQB); };         // S^T, then P^T
+  auto tm_dp = [&](int i) { return tmem_base + static_cast<uint32_t>(i * 2 * TQB + TQB); };  // dP^T, then dS^T
+  const uint32_t tm_dv = tmem_base + static_cast<uint32_t>(NB * 2 * TQB);
+  const uint32_t tm_dk = tm_dv + static_cast<uint32_t>(D);
+
+  if (warp == 0) {
+    if (lane == 0) {
+      mbar_expect_tx(kv_full, 2 * C::kKeyTile);
+#pragma unroll
+      for (int c = 0; c < NC; ++c) {
+        tma_load_3d(k_s + c * kKeyChunk, &tm_kv, kv_full, col_k + 32 * c, k0, b);
+        tma_load_3d(v_s + c * kKeyChunk, &tm_kv, kv_full, col_v + 32 * c, k0, b);
+      }
+      for (int u = 0; u < n_units; ++u) {
+        const int s = u % NB;
+        const uint32_t ph = static_cast<uint32_t>(u / NB) & 1u;
+        const int g = u / per_head;
+        const int qrow = (first_qt + (u - g * per_head)) * TQB;
+        const int col_q = (hk * G + g) * D;
+        if (!mbar_wait_bounded(&qk_empty[s], ph ^ 1u, args.status, 51)) break;
+        mbar_expect_tx(&qk_full[s], 2 * C::kQTile);
+#pragma unroll
+        for (int c = 0; c < NC; ++c) {
+          tma_load_3d(qk_s + s * C::kQTile + c * kQChunk, &tm_qk, &qk_full[s], col_q + 32 * c, qrow, b);
+          tma_load_3d(dok_s + s * C::kQTile + c * kQChunk, &tm_dok, &qk_full[s], col_q + 32 * c, qrow, b);
+        }
+        if (!mbar_wait_bounded(&qm_empty[s], ph ^ 1u, args.status, 52)) break;
+        mbar_expect_tx(&qm_full[s], 2 * C::kQTile);
+#pragma unroll
+        for (int c = 0; c < NC; ++c) {
+          tma_load_3d(qm_s + s * C::kQTile + c * kQChunk, &tm_qm, &qm_full[s], col_q + 32 * c, qrow, b);
+          tma_load_3d(dom_s + s * C::kQTile + c * kQChunk, &tm_dom, &qm_full[s], col_q + 32 * c, qrow, b);
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const uint32_t idesc_s = idesc_b(false, TQB);
+      const uint32_t idesc_d = idesc_b(true, D);
+      bool ok = mbar_wait_bounded(kv_full, 0, args.status, 53);
+      tc_fence_after();
+      const uint32_t k_addr = smem_u32(k_s), v_addr = smem_u32(v_s);
+      auto issue_sdp = [&](int u) {
+        const int s = u % NB;
+        if (!mbar_wait_bounded(&qk_full[s], static_cast<uint32_t>(u / NB) & 1u, args.status, 54)) return false;
+        tc_fence_after();
+        const uint32_t q_addr = smem_u32(qk_s + s * C::kQTile), do_addr = smem_u32(dok_s + s * C::kQTile);
+#pragma unroll
+        for (int ks = 0; ks < D / 8; ++ks) {
+          const uint32_t ao = static_cast<uint32_t>((ks >> 2) * kKeyChunk + (ks & 3) * 32);
+          const uint32_t bo = static_cast<uint32_t>((ks >> 2) * kQChunk + (ks & 3) * 32);
+          umma_tf32(tm_s(s), make_smem_desc(k_addr + ao, 16, 1024, kLayoutSw128),
+                    make_smem_desc(q_addr + bo, 16, 1024, kLayoutSw128), idesc_s, ks != 0 ? 1u : 0u);
+        }
+#pragma unroll
+        for (int ks = 0; ks < D / 8; ++ks) {
+          const uint32_t ao = static_cast<uint32_t>((ks >> 2) * kKeyChunk + (ks & 3) * 32);
+          const uint32_t bo = static_cast<uint32_t>((ks >> 2) * kQChunk + (ks & 3) * 32);
+          umma_tf32(tm_dp(s), make_smem_desc(v_addr + ao, 16, 1024, kLayoutSw128),
+                    make_smem_desc(do_addr + bo, 16, 1024, kLayoutSw128), idesc_s, ks != 0 ? 1u : 0u);
+        }
+        umma_commit(&qk_empty[s]);
+        umma_commit(&sdp_full[s]);
+        return true;
+      };
+      auto issue_dvdk = [&](int u) {
+        const int s = u % NB;
+        const uint32_t ph = static_cast<uint32_t>(u / NB) & 1u;
+        if (!mbar_wait_bounded(&pds_ready[s], ph, args.status, 55)) return false;
+        if (!mbar_wait_bounded(&qm_full[s], ph, args.status, 56)) return false;
+        tc_fence_after();
+        const uint32_t q_addr = smem_u32(qm_s + s * C::kQTile), do_addr = smem_u32(dom_s + s * C::kQTile);
+#pragma unroll
+        for (int ks = 0; ks < TQB / 8; ++ks)
+          umma_tf32_ta(tm_dv, tm_s(s) + static_cast<uint32_t>(ks * 8),
+                       make_smem_desc(do_addr + ks * 1024, kQChunk, 512, kLayoutSw128Base32), idesc_d,
+                       (u != 0 || ks != 0) ? 1u : 0u);
+#pragma unroll
+        for (int ks = 0; ks < TQB / 8; ++ks)
+          umma_tf32_ta(tm_dk, tm_dp(s) + static_cast<uint32_t>(ks * 8),
+                       make_smem_desc(q_addr + ks * 1024, kQChunk, 512, kLayoutSw128Base32), idesc_d,
+                       (u != 0 || ks != 0) ? 1u : 0u);
+        umma_commit(&qm_empty[s]);
+        return true;
+      };
+      for (int u = 0; u <= n_units && ok; ++u) {
+        if (NB == 2 && u < n_units) ok = issue_sdp(u);
+        if (ok && u >= 1) ok = issue_dvdk(u - 1);
+        if (NB == 1 && ok && u < n_units) ok = issue_sdp(u);
+      }
+      umma_commit(done_bar);
+    }
+    __syncwarp();
+  } else {
+    const int cw = warp - 2;
+    const int qd = warp & 3, half = cw >> 2;
+    const int ctid = cw * 32 + lane;  // 0 .. NCW-1
+    const int key = k0 + qd * 32 + lane;
+    const uint32_t lane_off = static_cast<uint32_t>(qd * 32) << 16;
+    const float sc2 = args.scale * kLog2ef;
+    bool ok = true;
+    for (int u = 0; u < n_units && ok; ++u) {
+      const int s = u % NB;
+      const int g = u / per_head;
+      const int q0 = (first_qt + (u - g * per_head)) * TQB;
+      const int64_t lbase = (static_cast<int64_t>(b) * args.H + hk * G + g) * args.T;
+      float* bl = s_lse + (u & 1) * TQB;
+      float* bd = s_del + (u & 1) * TQB;
+      for (int t = ctid; t < 2 * TQB; t += NCW) {
+        const int q = q0 + (t < TQB ? t : t - TQB);
+        if (t < TQB) bl[t] = q < args.T ? args.lse[lbase + q] * kLog2ef : FLT_MAX;
+        else bd[t - TQB] = q < args.T ? args.delta[lbase + q] : 0.0f;
+      }
+      asm volatile("bar.sync 1, %0;" ::"r"(NCW) : "memory");
+      if (!mbar_wait_bounded(&sdp_full[s], static_cast<uint32_t>(u / NB) & 1u, args.status, 57)) { ok = false; break; }
+      tc_fence_after();
+      float sv[32], dv[32];
+      uint32_t pb[32], db[32];
+      tmem_ld_32x32(tm_s(s) + lane_off + half * 32, sv);
+      tmem_ld_32x32(tm_dp(s) + lane_off + half * 32, dv);
+#pragma unroll
+      for (int i = 0; i < 32; ++i) {
+        const int ql = half * 32 + i;
+        const float p = (key > q0 + ql) ? 0.0f : ex2(sv[i] * sc2 - bl[ql]);
+        pb[i] = tf32_bits(p);
+        db[i] = tf32_bits(p * (dv[i] - bd[ql]) * args.scale);
+      }
+      tmem_st_32x32(tm_s(s) + lane_off + half * 32, pb);
+      tmem_st_32x32(tm_dp(s) + lane_off + half * 32, db);
+      tmem_wait_st();
+      tc_fence_before();
+      mbar_arrive(&pds_ready[s]);
+    }
+    if (ok && mbar_wait_bounded(done_bar, 0, args.status, 58)) {
+      tc_fence_after();
+      const int64_t RS = static_cast<int64_t>(args.H + 2 * args.Hk) * D;
+      float* row = args.dqkv + (static_cast<int64_t>(b) * args.T + key) * RS;
+      constexpr int kChunks = 2 * D / 32;               // dV chunks then dK chunks
+      constexpr int kPerWarpSet = kChunks / (C::kComputeWarps / 4);
+      for (int c = half * kPerWarpSet; c < (half + 1) * kPerWarpSet; ++c) {
+        float v[32];
+        tmem_ld_32x32(tm_dv + lane_off + c * 32, v);   // dK follows dV in tensor memory
+        const bool is_dv = c < D / 32;
+        float* dst = row + (is_dv ? col_v + c * 32 : col_k + (c - D / 32) * 32);
+        if (key < args.T) {
+#pragma unroll
+          for (int i = 0; i < 8; ++i)
+            reinterpret_cast<float4*>(dst)[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+        }
+        __syncwarp();
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, C::kTmemCols);
+  }
+}
+
+template <int D, int TQB, int NB>
+int launch_dkv(const float* qkv, const float* dout, const BwdArgs& a, int64_t B, cudaStream_t s) {
+  using C = DkvCfg<D, TQB, NB>;
+  const int RS = (a.H + 2 * a.Hk) * D;
+  const int64_t HD = static_cast<int64_t>(a.H) * D;
+  CUtensorMap tkv, tqk, tdok, tqm, tdom;
+  int rc = map3(&tkv, qkv, RS, a.T, B, TM, false);
+  if (rc == CTDK_OK) rc = map3(&tqk, qkv, RS, a.T, B, TQB, false);
+  if (rc == CTDK_OK) rc = map3(&tdok, dout, HD, a.T, B, TQB, false);
+  if (rc == CTDK_OK) rc = map3(&tqm, qkv, RS, a.T, B, TQB, true);
+  if (rc == CTDK_OK) rc = map3(&tdom, dout, HD, a.T, B, TQB, true);
+  if (rc != CTDK_OK) return rc;
+  auto* kern = attn_bwd_dkv_tc_kernel<D, TQB, NB>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmem);
+  if (e != cudaSuccess) return fail(CTDK_ELAUNCH, "attn_bwd dkv(tcgen05): shared memory opt-in failed: %s", cudaGetErrorString(e));
+  dim3 grid(static_cast<unsigned>((a.T + TM - 1) / TM), static_cast<unsigned>(a.Hk), static_cast<unsigned>(B));
+  kern<<<grid, C::kThreads, C::kSmem, s>>>(tkv, tqk, tdok, tqm, tdom, a);
+  return check_launch("ctdk_attn_bwd(dkv, tcgen05)");
+}
+
+}  // namespace
+
+// dK/dV part of the backward. Returns CTDK_OK, a negative status, or 1 when not eligible.
+int attn_bwd_dkv_tcgen05(const float* qkv, const float* dout, const float* lse, const float* delta, float* dqkv,
+                         int64_t B, int64_t T, int H, int Hk, int D, cudaStream_t stream) {
+  if ((reinterpret_cast<uintptr_t>(qkv) & 15u) || (reinterpret_cast<uintptr_t>(dout) & 15u) ||
+      (reinterpret_cast<uintptr_t>(dqkv) & 15u))
+    return 1;
+  BwdArgs a;
+  a.lse = lse;
+  a.delta = delta;
+  a.dqkv = dqkv;
+  a.T = static_cast<int>(T);
+  a.H = H;
+  a.Hk = Hk;
+  a.scale = 1.0f / sqrtf(static_cast<float>(D));
+  a.status = device_status_word();
+  if (a.status == nullptr) return fail(CTDK_ELAUNCH, "attn_bwd(tcgen05): no status word");
+  return D == 64 ? launch_dkv<64, 64, 2>(qkv, dout, a, B, stream) : launch_dkv<128, 32, 1>(qkv, dout, a, B, stream);
+}
+
+}  // namespace ctdk
