@@ -13,7 +13,8 @@
 namespace ctdk {
 namespace {
 
-constexpr int kMaxPartialRows = 512;
+constexpr int kMaxPartialRows = 512;    // QK-Norm backward
+constexpr int kNormPartialRows = 2048;  // RMSNorm backward: up to 8 CTAs per SM keep HBM busy
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
@@ -225,6 +226,26 @@ __global__ void __launch_bounds__(128) dw_finalize_kernel(const float* __restric
   dw[c] = accumulate ? dw[c] + acc : acc;
 }
 
+// Same column sum for many partial rows: 256 threads = 8 row groups x 32 columns per CTA.
+__global__ void __launch_bounds__(256) dw_finalize_wide_kernel(const float* __restrict__ partial,
+                                                               float* __restrict__ dw, int nparts,
+                                                               int H, int accumulate) {
+  __shared__ float red[8][33];
+  const int cl = threadIdx.x & 31, rg = threadIdx.x >> 5;
+  const int c = blockIdx.x * 32 + cl;
+  float acc = 0.0f;
+  if (c < H)
+    for (int p = rg; p < nparts; p += 8) acc += partial[static_cast<int64_t>(p) * H + c];
+  red[rg][cl] = acc;
+  __syncthreads();
+  if (rg == 0 && c < H) {
+    float t = 0.0f;
+#pragma unroll
+    for (int r = 0; r < 8; ++r) t += red[r][cl];
+    dw[c] = accumulate ? dw[c] + t : t;
+  }
+}
+
 // partial rows are [2][D] (q-norm then k-norm); dwq/dwk (+)= column sums.
 __global__ void __launch_bounds__(128) qk_dw_finalize_kernel(const float* __restrict__ partial,
                                                              float* __restrict__ dwq,
@@ -300,9 +321,30 @@ __global__ void __launch_bounds__(256)
 }
 
 // ---------------------------------------------------------------------------------------
-// Fused QK-Norm + RoPE over a packed qkv row: one warp per (row, head) item. Each lane
-// owns NP rotation pairs (i, i+D/2), i = lane + 32*j: D = 64*NP.
+// Fused QK-Norm + RoPE over the packed qkv buffer. A group of D/8 threads owns one (row, head)
+// slot: thread j of the group holds the float4 at [4j, 4j+3] and its rotation partners at
+// [D/2+4j, D/2+4j+3], so every access is 128 bits and a warp covers 4 (D=64) or 2 (D=128)
+// heads per iteration. NP = D/64.
 // ---------------------------------------------------------------------------------------
+template <int NP>
+__device__ __forceinline__ float group_sum(float v) {
+#pragma unroll
+  for (int o = 4 * NP; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+__device__ __forceinline__ void rot4(float4& a, float4& b, const float4 cs0, const float4 cs1,
+                                     float sin_sign) {
+  // cs0 = (c0,s0,c1,s1), cs1 = (c2,s2,c3,s3)
+  float4 ra, rb;
+  ra.x = a.x * cs0.x - b.x * cs0.y * sin_sign;  rb.x = a.x * cs0.y * sin_sign + b.x * cs0.x;
+  ra.y = a.y * cs0.z - b.y * cs0.w * sin_sign;  rb.y = a.y * cs0.w * sin_sign + b.y * cs0.z;
+  ra.z = a.z * cs1.x - b.z * cs1.y * sin_sign;  rb.z = a.z * cs1.y * sin_sign + b.z * cs1.x;
+  ra.w = a.w * cs1.z - b.w * cs1.w * sin_sign;  rb.w = a.w * cs1.w * sin_sign + b.w * cs1.z;
+  a = ra;
+  b = rb;
+}
+
 template <int NP>
 __global__ void __launch_bounds__(256)
     qk_norm_rope_fwd_kernel(const float* __restrict__ qkv, float* __restrict__ out,
@@ -310,60 +352,58 @@ __global__ void __launch_bounds__(256)
                             float* __restrict__ rstd_q, float* __restrict__ rstd_k,
                             const float2* __restrict__ table, int64_t rows, int64_t T, int H,
                             int Hk, float eps) {
-  constexpr int D = 64 * NP, Dh = 32 * NP;
-  const int lane = threadIdx.x & 31;
-  const int64_t warp0 = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
-  const int64_t nwarps = (static_cast<int64_t>(gridDim.x) * blockDim.x) >> 5;
+  constexpr int D = 64 * NP, Dh = 32 * NP, TPH = 8 * NP;  // threads per head slot
   const int HT = H + 2 * Hk;
   const int64_t items = rows * HT;
+  const int j = threadIdx.x % TPH;
+  const int64_t g0 = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) / TPH;
+  const int64_t ng = (static_cast<int64_t>(gridDim.x) * blockDim.x) / TPH;
   const bool copy_v = (out != qkv);
-  for (int64_t it = warp0; it < items; it += nwarps) {
-    const int64_t row = it / HT;
-    const int h = static_cast<int>(it - row * HT);
-    const float* xr = qkv + it * D;
-    float* yr = out + it * D;
-    if (h >= H + Hk) {  // v head: plain copy
-      if (copy_v) {
-#pragma unroll
-        for (int j = 0; j < 2 * NP; ++j) yr[lane + 32 * j] = xr[lane + 32 * j];
+  const bool has_norm = (wq != nullptr);
+  const int64_t iters = (items + ng - 1) / ng;  // every lane runs the same number of shuffles
+  for (int64_t k = 0; k < iters; ++k) {
+    const int64_t it = g0 + k * ng;
+    const bool live = it < items;
+    const int64_t row = live ? it / HT : 0;
+    const int h = live ? static_cast<int>(it - row * HT) : 0;
+    const bool is_v = h >= H + Hk, is_q = h < H;
+    float4 a = make_float4(0.f, 0.f, 0.f, 0.f), b = a;
+    if (live) {
+      a = *reinterpret_cast<const float4*>(qkv + it * D + 4 * j);
+      b = *reinterpret_cast<const float4*>(qkv + it * D + Dh + 4 * j);
+    }
+    if (has_norm) {
+      float ss = a.x * a.x + a.y * a.y + a.z * a.z + a.w * a.w + b.x * b.x + b.y * b.y +
+                 b.z * b.z + b.w * b.w;
+      ss = group_sum<NP>(ss);
+      if (live && !is_v) {
+        const float s = rsqrtf(ss / static_cast<float>(D) + eps);
+        if (j == 0) {
+          if (is_q) rstd_q[row * H + h] = s;
+          else rstd_k[row * Hk + (h - H)] = s;
+        }
+        const float* w = is_q ? wq : wk;
+        const float4 wa = *reinterpret_cast<const float4*>(w + 4 * j);
+        const float4 wb = *reinterpret_cast<const float4*>(w + Dh + 4 * j);
+        a.x = a.x * s * wa.x;  a.y = a.y * s * wa.y;  a.z = a.z * s * wa.z;  a.w = a.w * s * wa.w;
+        b.x = b.x * s * wb.x;  b.y = b.y * s * wb.y;  b.z = b.z * s * wb.z;  b.w = b.w * s * wb.w;
       }
+    }
+    if (!live) continue;
+    if (!is_v) {
+      const int64_t t = row % T;
+      const float4* tb = reinterpret_cast<const float4*>(table + t * Dh + 4 * j);
+      rot4(a, b, tb[0], tb[1], 1.0f);
+    } else if (!copy_v) {
       continue;
     }
-    const bool is_q = h < H;
-    const float* w = is_q ? wq : wk;
-    float a[NP], b[NP];
-    float ss = 0.0f;
-#pragma unroll
-    for (int j = 0; j < NP; ++j) {
-      a[j] = xr[lane + 32 * j];
-      b[j] = xr[lane + 32 * j + Dh];
-      ss += a[j] * a[j] + b[j] * b[j];
-    }
-    if (w != nullptr) {
-      ss = warp_sum(ss);
-      const float s = rsqrtf(ss / static_cast<float>(D) + eps);
-      if (lane == 0) {
-        if (is_q) rstd_q[row * H + h] = s;
-        else rstd_k[row * Hk + (h - H)] = s;
-      }
-#pragma unroll
-      for (int j = 0; j < NP; ++j) {
-        a[j] = a[j] * s * w[lane + 32 * j];
-        b[j] = b[j] * s * w[lane + 32 * j + Dh];
-      }
-    }
-    const int64_t t = row % T;
-#pragma unroll
-    for (int j = 0; j < NP; ++j) {
-      const float2 cs = table[t * Dh + lane + 32 * j];
-      yr[lane + 32 * j] = a[j] * cs.x - b[j] * cs.y;
-      yr[lane + 32 * j + Dh] = a[j] * cs.y + b[j] * cs.x;
-    }
+    *reinterpret_cast<float4*>(out + it * D + 4 * j) = a;
+    *reinterpret_cast<float4*>(out + it * D + Dh + 4 * j) = b;
   }
 }
 
 // Backward, in place on dqkv: un-rotate (R(-theta)), then the RMSNorm backward per head.
-// dw partials: per-warp registers -> smem -> partial[blockIdx.x][2][D].
+// dw partials: registers -> shared-memory atomics -> partial[blockIdx.x][2][D].
 template <int NP>
 __global__ void __launch_bounds__(256)
     qk_norm_rope_bwd_kernel(float* __restrict__ dqkv, const float* __restrict__ qkv_pre,
@@ -371,85 +411,81 @@ __global__ void __launch_bounds__(256)
                             const float* __restrict__ rstd_q, const float* __restrict__ rstd_k,
                             float* __restrict__ partial, const float2* __restrict__ table,
                             int64_t rows, int64_t T, int H, int Hk) {
-  constexpr int D = 64 * NP, Dh = 32 * NP;
-  __shared__ float sdw[8][2][D];
-  const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
-  const int64_t warp0 = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
-  const int64_t nwarps = (static_cast<int64_t>(gridDim.x) * blockDim.x) >> 5;
+  constexpr int D = 64 * NP, Dh = 32 * NP, TPH = 8 * NP;
+  __shared__ float sdw[2][D];
   const int HT = H + 2 * Hk, HQK = H + Hk;
   const int64_t items = rows * HQK;
+  const int j = threadIdx.x % TPH;
+  const int64_t g0 = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) / TPH;
+  const int64_t ng = (static_cast<int64_t>(gridDim.x) * blockDim.x) / TPH;
   const bool has_norm = (wq != nullptr);
-  float dwa[2][NP], dwb[2][NP];
-#pragma unroll
-  for (int j = 0; j < NP; ++j) {
-    dwa[0][j] = dwa[1][j] = dwb[0][j] = dwb[1][j] = 0.0f;
-  }
-  for (int64_t it = warp0; it < items; it += nwarps) {
-    const int64_t row = it / HQK;
-    const int h = static_cast<int>(it - row * HQK);
+  for (int i = threadIdx.x; i < 2 * D; i += blockDim.x) sdw[i / D][i % D] = 0.0f;
+  __syncthreads();
+  float4 dwa[2], dwb[2];
+  dwa[0] = dwa[1] = dwb[0] = dwb[1] = make_float4(0.f, 0.f, 0.f, 0.f);
+  const int64_t iters = (items + ng - 1) / ng;
+  for (int64_t k = 0; k < iters; ++k) {
+    const int64_t it = g0 + k * ng;
+    const bool live = it < items;
+    const int64_t row = live ? it / HQK : 0;
+    const int h = live ? static_cast<int>(it - row * HQK) : 0;
     const bool is_q = h < H;
-    float* gr = dqkv + (row * HT + h) * D;
-    const int64_t t = row % T;
-    float ga[NP], gb[NP];
-#pragma unroll
-    for (int j = 0; j < NP; ++j) {
-      const float2 cs = table[t * Dh + lane + 32 * j];
-      const float a = gr[lane + 32 * j], b = gr[lane + 32 * j + Dh];
-      ga[j] = a * cs.x + b * cs.y;   // rotation by -angle
-      gb[j] = -a * cs.y + b * cs.x;
+    const int64_t off = (row * HT + h) * D;
+    float4 ga = make_float4(0.f, 0.f, 0.f, 0.f), gb = ga;
+    if (live) {
+      ga = *reinterpret_cast<const float4*>(dqkv + off + 4 * j);
+      gb = *reinterpret_cast<const float4*>(dqkv + off + Dh + 4 * j);
+      const int64_t t = row % T;
+      const float4* tb = reinterpret_cast<const float4*>(table + t * Dh + 4 * j);
+      rot4(ga, gb, tb[0], tb[1], -1.0f);
     }
     if (has_norm) {
-      const float* w = is_q ? wq : wk;
-      const float* xr = qkv_pre + (row * HT + h) * D;
-      const float s = is_q ? rstd_q[row * H + h] : rstd_k[row * Hk + (h - H)];
-      float xa[NP], xb[NP], wa[NP], wb[NP];
-      float c = 0.0f;
-#pragma unroll
-      for (int j = 0; j < NP; ++j) {
-        xa[j] = xr[lane + 32 * j];
-        xb[j] = xr[lane + 32 * j + Dh];
-        wa[j] = w[lane + 32 * j];
-        wb[j] = w[lane + 32 * j + Dh];
-        c += ga[j] * wa[j] * xa[j] + gb[j] * wb[j] * xb[j];
+      float4 xa = make_float4(0.f, 0.f, 0.f, 0.f), xb = xa, wa = xa, wb = xa;
+      float s = 0.0f;
+      if (live) {
+        const float* w = is_q ? wq : wk;
+        xa = *reinterpret_cast<const float4*>(qkv_pre + off + 4 * j);
+        xb = *reinterpret_cast<const float4*>(qkv_pre + off + Dh + 4 * j);
+        wa = *reinterpret_cast<const float4*>(w + 4 * j);
+        wb = *reinterpret_cast<const float4*>(w + Dh + 4 * j);
+        s = is_q ? rstd_q[row * H + h] : rstd_k[row * Hk + (h - H)];
       }
-      c = warp_sum(c);
-      const float k = s * s * c / static_cast<float>(D);
+      float c = ga.x * wa.x * xa.x + ga.y * wa.y * xa.y + ga.z * wa.z * xa.z + ga.w * wa.w * xa.w +
+                gb.x * wb.x * xb.x + gb.y * wb.y * xb.y + gb.z * wb.z * xb.z + gb.w * wb.w * xb.w;
+      c = group_sum<NP>(c);
+      const float kk = s * s * c / static_cast<float>(D);
       const int sel = is_q ? 0 : 1;
-#pragma unroll
-      for (int j = 0; j < NP; ++j) {
-        const float da = ga[j] * xa[j] * s, db = gb[j] * xb[j] * s;
-        if (sel == 0) {
-          dwa[0][j] += da;
-          dwb[0][j] += db;
-        } else {
-          dwa[1][j] += da;
-          dwb[1][j] += db;
-        }
-        ga[j] = s * (ga[j] * wa[j] - xa[j] * k);
-        gb[j] = s * (gb[j] * wb[j] - xb[j] * k);
+      if (live) {
+        dwa[sel].x += ga.x * xa.x * s;  dwa[sel].y += ga.y * xa.y * s;
+        dwa[sel].z += ga.z * xa.z * s;  dwa[sel].w += ga.w * xa.w * s;
+        dwb[sel].x += gb.x * xb.x * s;  dwb[sel].y += gb.y * xb.y * s;
+        dwb[sel].z += gb.z * xb.z * s;  dwb[sel].w += gb.w * xb.w * s;
       }
+      ga.x = s * (ga.x * wa.x - xa.x * kk);  ga.y = s * (ga.y * wa.y - xa.y * kk);
+      ga.z = s * (ga.z * wa.z - xa.z * kk);  ga.w = s * (ga.w * wa.w - xa.w * kk);
+      gb.x = s * (gb.x * wb.x - xb.x * kk);  gb.y = s * (gb.y * wb.y - xb.y * kk);
+      gb.z = s * (gb.z * wb.z - xb.z * kk);  gb.w = s * (gb.w * wb.w - xb.w * kk);
     }
-#pragma unroll
-    for (int j = 0; j < NP; ++j) {
-      gr[lane + 32 * j] = ga[j];
-      gr[lane + 32 * j + Dh] = gb[j];
+    if (live) {
+      *reinterpret_cast<float4*>(dqkv + off + 4 * j) = ga;
+      *reinterpret_cast<float4*>(dqkv + off + Dh + 4 * j) = gb;
     }
   }
   if (has_norm) {
 #pragma unroll
-    for (int sel = 0; sel < 2; ++sel)
-#pragma unroll
-      for (int j = 0; j < NP; ++j) {
-        sdw[wid][sel][lane + 32 * j] = dwa[sel][j];
-        sdw[wid][sel][lane + 32 * j + Dh] = dwb[sel][j];
-      }
-    __syncthreads();
-    const int nw = blockDim.x >> 5;
-    for (int i = threadIdx.x; i < 2 * D; i += blockDim.x) {
-      float acc = 0.0f;
-      for (int ww = 0; ww < nw; ++ww) acc += sdw[ww][i / D][i % D];
-      partial[static_cast<int64_t>(blockIdx.x) * 2 * D + i] = acc;
+    for (int sel = 0; sel < 2; ++sel) {
+      atomicAdd(&sdw[sel][4 * j + 0], dwa[sel].x);
+      atomicAdd(&sdw[sel][4 * j + 1], dwa[sel].y);
+      atomicAdd(&sdw[sel][4 * j + 2], dwa[sel].z);
+      atomicAdd(&sdw[sel][4 * j + 3], dwa[sel].w);
+      atomicAdd(&sdw[sel][Dh + 4 * j + 0], dwb[sel].x);
+      atomicAdd(&sdw[sel][Dh + 4 * j + 1], dwb[sel].y);
+      atomicAdd(&sdw[sel][Dh + 4 * j + 2], dwb[sel].z);
+      atomicAdd(&sdw[sel][Dh + 4 * j + 3], dwb[sel].w);
     }
+    __syncthreads();
+    for (int i = threadIdx.x; i < 2 * D; i += blockDim.x)
+      partial[static_cast<int64_t>(blockIdx.x) * 2 * D + i] = sdw[i / D][i % D];
   }
 }
 
@@ -502,7 +538,7 @@ int ctdk_rmsnorm_fwd(const float* x, const float* w, float* y, float* rstd, int6
 }
 
 int64_t ctdk_rmsnorm_bwd_scratch_floats(int H) {
-  return static_cast<int64_t>(kMaxPartialRows) * (H > 0 ? H : 0);
+  return static_cast<int64_t>(kNormPartialRows) * (H > 0 ? H : 0);
 }
 
 int ctdk_rmsnorm_bwd(const float* dy, const float* x, const float* w, float* dx, float* dw,
@@ -516,8 +552,8 @@ int ctdk_rmsnorm_bwd(const float* dy, const float* x, const float* w, float* dx,
     return CTDK_OK;
   }
   CTDK_REQUIRE(dy && x && w && dx, "ctdk_rmsnorm_bwd: null pointer");
-  int64_t cap = static_cast<int64_t>(sm_count()) * 2;
-  if (cap > kMaxPartialRows) cap = kMaxPartialRows;
+  int64_t cap = static_cast<int64_t>(sm_count()) * 8;
+  if (cap > kNormPartialRows) cap = kNormPartialRows;
   const int grid = static_cast<int>(rows < cap ? rows : cap);
   const bool vec = (H % 4 == 0) && aligned16(dy) && aligned16(x) && aligned16(w) &&
                    aligned16(dx) && aligned16(dw_scratch) && H <= 4096;
@@ -546,7 +582,7 @@ int ctdk_rmsnorm_bwd(const float* dy, const float* x, const float* w, float* dx,
   }
   int rc = check_launch("ctdk_rmsnorm_bwd");
   if (rc != CTDK_OK) return rc;
-  dw_finalize_kernel<<<ceil_div(H, 128), 128, 0, s>>>(dw_scratch, dw, grid, H, accumulate_dw);
+  dw_finalize_wide_kernel<<<ceil_div(H, 32), 256, 0, s>>>(dw_scratch, dw, grid, H, accumulate_dw);
   return check_launch("ctdk_rmsnorm_bwd(finalize)");
 }
 
@@ -674,13 +710,17 @@ int ctdk_qk_norm_rope_fwd(const float* qkv, float* qkv_out, const float* wq, con
   const int64_t rows = B * T;
   if (rows == 0) return CTDK_OK;
   CTDK_REQUIRE(qkv && qkv_out && rope_table, "ctdk_qk_norm_rope_fwd: null pointer");
+  CTDK_REQUIRE(aligned16(qkv) && aligned16(qkv_out) && aligned16(rope_table) && aligned16(wq) &&
+                   aligned16(wk),
+               "ctdk_qk_norm_rope_fwd: pointers must be 16-byte aligned");
   CTDK_REQUIRE((wq == nullptr) == (wk == nullptr), "ctdk_qk_norm_rope_fwd: wq/wk mismatch");
   CTDK_REQUIRE(wq == nullptr || (rstd_q && rstd_k), "ctdk_qk_norm_rope_fwd: rstd required");
   CTDK_REQUIRE(wq == nullptr || qkv_out != qkv,
                "ctdk_qk_norm_rope_fwd: QK-Norm needs an out-of-place result");
   const int64_t items = rows * (H + 2 * Hk);
   const int64_t cap = static_cast<int64_t>(sm_count()) * 8;
-  const int64_t need = (items + 7) / 8;
+  const int per_cta = 256 / (D / 8);  // head slots per CTA and iteration
+  const int64_t need = (items + per_cta - 1) / per_cta;
   const int grid = static_cast<int>(need < cap ? need : cap);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const float2* tb = reinterpret_cast<const float2*>(rope_table);
@@ -715,12 +755,16 @@ int ctdk_qk_norm_rope_bwd(float* dqkv, const float* qkv_pre, const float* wq, co
     return CTDK_OK;
   }
   CTDK_REQUIRE(dqkv && rope_table, "ctdk_qk_norm_rope_bwd: null pointer");
+  CTDK_REQUIRE(aligned16(dqkv) && aligned16(rope_table) && aligned16(qkv_pre) && aligned16(wq) &&
+                   aligned16(wk),
+               "ctdk_qk_norm_rope_bwd: pointers must be 16-byte aligned");
   CTDK_REQUIRE(!has_norm || (qkv_pre && rstd_q && rstd_k && dwq && dwk && scratch),
                "ctdk_qk_norm_rope_bwd: QK-Norm needs qkv_pre, rstd, dw and scratch");
   const int64_t items = rows * (H + Hk);
-  int64_t cap = static_cast<int64_t>(sm_count()) * 2;
+  int64_t cap = static_cast<int64_t>(sm_count()) * 3;
   if (cap > kMaxPartialRows) cap = kMaxPartialRows;
-  const int64_t need = (items + 7) / 8;
+  const int per_cta = 256 / (D / 8);
+  const int64_t need = (items + per_cta - 1) / per_cta;
   const int grid = static_cast<int>(need < cap ? need : cap);
   const float2* tb = reinterpret_cast<const float2*>(rope_table);
   if (D == 64)

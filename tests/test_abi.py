@@ -31,7 +31,7 @@ def test_bad_arguments_return_einval_with_message():
 
 def test_scratch_size_queries():
     L = lib.raw()
-    assert L.ctdk_rmsnorm_bwd_scratch_floats(960) == 512 * 960
+    assert L.ctdk_rmsnorm_bwd_scratch_floats(960) == 2048 * 960
     assert L.ctdk_qk_norm_rope_bwd_scratch_floats(128) == 512 * 2 * 128
 
 
