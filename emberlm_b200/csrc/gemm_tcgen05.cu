@@ -435,6 +435,10 @@ int dispatch_major(bool a_mn, bool b_mn, const CUtensorMap& ta, const CUtensorMa
 
 }  // namespace
 
+int gemm_tcgen05_2cta(const CUtensorMap& ta, const CUtensorMap& tb, bool a_mn, bool b_mn, float* C,
+                      const float* aux, int64_t ldc, int M, int N, int K, int epilogue, int vec_ok, int splits,
+                      int* status, cudaStream_t stream);
+
 // Returns CTDK_OK after enqueueing, or 1 when the shape/alignment is not eligible for the
 // tensor-core path (the caller then uses the SIMT kernel).
 int gemm_tcgen05(const float* A, const float* B, float* Cp, int64_t M, int64_t N, int64_t K,
@@ -479,14 +483,64 @@ int gemm_tcgen05(const float* A, const float* B, float* Cp, int64_t M, int64_t N
     }
   }
 
+  // Paired-CTA kernel (256 x 256 tile per CTA pair, half of B per CTA): same cost model, a pair
+  // round does the work of two 256-wide rounds in about 1.7x the time of one.
+  static const bool pair_off = [] {
+    const char* e = std::getenv("CTDK_GEMM_1CTA");
+    return e != nullptr && e[0] == '1';
+  }();
+  bool use_pair = false;
+  if (!pair_off && M >= 256 && N >= 256) {
+    double best1 = 1e300;
+    {
+      const int64_t tiles = m_blocks * ((N + bn - 1) / bn);
+      const double rounds = static_cast<double>((tiles * splits + sms - 1) / sms);
+      best1 = rounds * (static_cast<double>((k_blocks + splits - 1) / splits) + (splits > 1 ? 12.0 : 6.0)) *
+              (bn == 256 ? 1.0 : (bn == 128 ? 0.6 : 0.4));
+    }
+    const int pairs = sms / 2;
+    const int64_t tiles2 = ((M + 255) / 256) * ((N + 255) / 256);
+    const int max_splits = static_cast<int>(k_blocks / 16 < 1 ? 1 : (k_blocks / 16 > 32 ? 32 : k_blocks / 16));
+    double bestp = 1e300;
+    int sp_best = 1;
+    for (int sp = 1; sp <= max_splits; ++sp) {
+      if (sp > 1 && tiles2 >= 2 * pairs) break;
+      const double rounds = static_cast<double>((tiles2 * sp + pairs - 1) / pairs);
+      const double t = rounds * (static_cast<double>((k_blocks + sp - 1) / sp) + (sp > 1 ? 12.0 : 6.0)) * 1.7;
+      if (t < bestp * 0.97) {
+        bestp = t;
+        sp_best = sp;
+      }
+    }
+    // compare per-SM-round costs: a one-CTA round covers `sms` tiles, a pair round `pairs` tiles
+    if (bestp < best1 * 2.0 * 0.98) {
+      use_pair = true;
+      splits = sp_best;
+      bn = 256;
+    }
+  }
+
   CUtensorMap ta, tb;
   int rc;
   if (a_mn) rc = make_map(&ta, A, M, K, lda, BK, true, false);
   else rc = make_map(&ta, A, K, M, lda, BM, false, false);
   if (rc != CTDK_OK) return rc;
   if (b_mn) rc = make_map(&tb, B, N, K, ldb, BK, true, false);
-  else rc = make_map(&tb, B, K, N, ldb, bn, false, false);
+  else rc = make_map(&tb, B, K, N, ldb, use_pair ? 128 : bn, false, false);
   if (rc != CTDK_OK) return rc;
+
+  if (use_pair) {
+    int* st = device_status_word();
+    if (st == nullptr) return fail(CTDK_ELAUNCH, "gemm: no status word");
+    const int vec = (a16(Cp) && (ldc & 3) == 0 && (aux == nullptr || a16(aux))) ? 1 : 0;
+    if (splits > 1 && epilogue != CTDK_EPI_ACCUMULATE) {
+      cudaError_t e = cudaMemset2DAsync(Cp, static_cast<size_t>(ldc) * sizeof(float), 0,
+                                        static_cast<size_t>(N) * sizeof(float), static_cast<size_t>(M), stream);
+      if (e != cudaSuccess) return fail(CTDK_ELAUNCH, "gemm: memset failed: %s", cudaGetErrorString(e));
+    }
+    return gemm_tcgen05_2cta(ta, tb, a_mn, b_mn, Cp, aux, ldc, static_cast<int>(M), static_cast<int>(N),
+                             static_cast<int>(K), epilogue, vec, splits, st, stream);
+  }
 
   GemmArgs args;
   args.C = Cp;

@@ -1,0 +1,370 @@
+// TF32 GEMM with paired CTAs (tcgen05 cta_group::2): a cluster of two CTAs on one TPC computes a
+// 256 x 256 output tile. Each CTA loads its own 128 rows of A and only HALF of the B tile
+// (128 of the 256 columns) per k-block; the tensor cores of both SMs read both halves. Per FLOP
+// this moves one third fewer operand bytes through L2 and shared memory than the one-CTA
+// 128 x 256 tile of gemm_tcgen05.cu, which is what bounds that kernel with 4-byte operands.
+//
+// Roles per CTA (6 warps): TMA producer, MMA warp, 4 epilogue warps. Only the even CTA of the
+// pair (the leader) issues MMAs; both CTAs' TMA loads report their bytes to the leader's
+// "full" barrier; the leader releases stages and publishes finished accumulators to both CTAs
+// with a multicast tcgen05.commit; both CTAs' epilogue warps report to the leader's
+// "accumulator free" barrier. Loads are plain per-CTA TMA loads. All waits are bounded.
+#include <cuda.h>
+
+#include "common.cuh"
+
+namespace ctdk {
+namespace {
+
+constexpr int BM2 = 128;                 // rows of A per CTA (pair: 256)
+constexpr int BN2 = 256;                 // tile width (each CTA loads 128 columns of B)
+constexpr int BK2 = 32;
+constexpr int kATile = BM2 * BK2 * 4;    // 16 KB
+constexpr int kBHalf = (BN2 / 2) * BK2 * 4;  // 16 KB
+constexpr int kStage2 = kATile + kBHalf;
+constexpr int kStages2 = 6;
+constexpr int kChunk2 = 32 * BK2 * 4;    // one {32 x 32} box of an MN-major operand
+constexpr int kSmem2 = kStages2 * kStage2 + 1024 + 256;
+constexpr uint32_t kPeerMask = 0xFEFFFFFFu;  // clears the CTA-rank bit of a shared::cluster address
+constexpr int kGroupM2 = 8;
+
+struct Gemm2Args {
+  float* C;
+  const float* aux;
+  int64_t ldc;
+  int M, N, K;
+  int epilogue;
+  int vec_ok;
+  int splits;  // K ranges per tile; >1: partial tiles are added to C with atomics
+  int* status;
+};
+
+__device__ __forceinline__ uint32_t cluster_rank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_alloc2(uint32_t* slot, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(slot)), "r"(ncols)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish2() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc2(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+// Load into this CTA's shared memory; the bytes are counted on the LEADER CTA's barrier.
+__device__ __forceinline__ void tma_load_2d_pair(void* smem_dst, const CUtensorMap* m, uint64_t* bar, int c0,
+                                                 int c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_u32(smem_dst)),
+      "l"(reinterpret_cast<uint64_t>(m)), "r"(smem_u32(bar) & kPeerMask), "r"(c0), "r"(c1)
+      : "memory");
+}
+__device__ __forceinline__ void umma_tf32_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                               uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::2.kind::tf32 [%0], %1, %2, %3, p;\n"
+      "}\n" ::"r"(tmem_d),
+      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// One arrival on the barrier at this offset in BOTH CTAs of the pair once prior MMAs retire.
+__device__ __forceinline__ void umma_commit_pair(uint64_t* bar) {
+  asm volatile(
+      "{\n"
+      ".reg .b16 m;\n"
+      "mov.b16 m, 3;\n"
+      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], m;\n"
+      "}\n" ::"r"(smem_u32(bar))
+      : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_leader(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(smem_u32(bar) & kPeerMask)
+               : "memory");
+}
+
+__device__ __forceinline__ void tile_coords2(int tile, int m_blocks, int n_blocks, int& mb, int& nb) {
+  const int per_group = kGroupM2 * n_blocks;
+  const int g = tile / per_group;
+  const int first_m = g * kGroupM2;
+  const int gm = min(kGroupM2, m_blocks - first_m);
+  const int local = tile - g * per_group;
+  mb = first_m + local % gm;
+  nb = local / gm;
+}
+
+template <bool A_MN, bool B_MN>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
+    gemm_tf32_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                          const Gemm2Args args) {
+  extern __shared__ unsigned char smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  unsigned char* smem = smem_raw + ((1024u - (raw & 1023u)) & 1023u);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStages2 * kStage2);
+  uint64_t* full = bars;                   // [kStages2]  used in the leader only
+  uint64_t* empty = bars + kStages2;       // [kStages2]  one per CTA, signalled by multicast commit
+  uint64_t* tfull = bars + 2 * kStages2;   // [2]         one per CTA, multicast commit
+  uint64_t* tempty = tfull + 2;            // [2]         leader only, 8 arrivals (4 warps x 2 CTAs)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 2);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_rank();
+  const bool leader = rank == 0;
+  const int m_blocks = (args.M + 2 * BM2 - 1) / (2 * BM2);
+  const int n_blocks = (args.N + BN2 - 1) / BN2;
+  const int num_tiles = m_blocks * n_blocks;
+  const int k_blocks = (args.K + BK2 - 1) / BK2;
+  const int num_units = num_tiles * args.splits;  // unit u: tile u % num_tiles, k-range u / num_tiles
+  const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages2; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&tfull[a], 1);
+      mbar_init(&tempty[a], 8);
+    }
+    mbar_fence_init();
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmB);
+  }
+  if (warp == 1) {
+    tmem_alloc2(tmem_slot, 512);
+    tmem_relinquish2();
+    tc_fence_before();
+  }
+  __syncthreads();
+  cluster_sync_all();  // both CTAs' barriers are initialised before any remote signal
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ---------------- TMA producer (both CTAs) ----------------
+    if (lane == 0) {
+      int s = 0;
+      uint32_t ph = 0;
+      bool ok = true;
+      for (int unit = pair; unit < num_units && ok; unit += n_pairs) {
+        int mb, nb;
+        tile_coords2(unit % num_tiles, m_blocks, n_blocks, mb, nb);
+        const int m0 = mb * 2 * BM2 + static_cast<int>(rank) * BM2;
+        const int n0 = nb * BN2 + static_cast<int>(rank) * (BN2 / 2);
+        const int split = unit / num_tiles;
+        const int kb0 = static_cast<int>(static_cast<int64_t>(split) * k_blocks / args.splits);
+        const int kb1 = static_cast<int>(static_cast<int64_t>(split + 1) * k_blocks / args.splits);
+        for (int kb = kb0; kb < kb1; ++kb) {
+          if (!mbar_wait_bounded(&empty[s], ph ^ 1u, args.status, 61)) {
+            ok = false;
+            break;
+          }
+          unsigned char* a_dst = smem + s * kStage2;
+          unsigned char* b_dst = a_dst + kATile;
+          if (leader) mbar_expect_tx(&full[s], 2 * kStage2);  // bytes of both CTAs
+          const int k0 = kb * BK2;
+          if (A_MN) {
+#pragma unroll
+            for (int c = 0; c < BM2 / 32; ++c)
+              tma_load_2d_pair(a_dst + c * kChunk2, &tmA, &full[s], m0 + 32 * c, k0);
+          } else {
+            tma_load_2d_pair(a_dst, &tmA, &full[s], k0, m0);
+          }
+          if (B_MN) {
+#pragma unroll
+            for (int c = 0; c < BN2 / 64; ++c)
+              tma_load_2d_pair(b_dst + c * kChunk2, &tmB, &full[s], n0 + 32 * c, k0);
+          } else {
+            tma_load_2d_pair(b_dst, &tmB, &full[s], k0, n0);
+          }
+          if (++s == kStages2) {
+            s = 0;
+            ph ^= 1u;
+          }
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ---------------- MMA issuer (leader CTA only) ----------------
+    if (leader && lane == 0) {
+      // M = 256 (both CTAs), N = 256
+      const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | (static_cast<uint32_t>(A_MN) << 15) |
+                             (static_cast<uint32_t>(B_MN) << 16) | (static_cast<uint32_t>(BN2 >> 3) << 17) |
+                             (static_cast<uint32_t>(256 >> 4) << 24);
+      int s = 0;
+      uint32_t ph = 0;
+      bool ok = true;
+      int it = 0;
+      for (int unit = pair; unit < num_units && ok; unit += n_pairs, ++it) {
+        const int split = unit / num_tiles;
+        const int kb0 = static_cast<int>(static_cast<int64_t>(split) * k_blocks / args.splits);
+        const int kb1 = static_cast<int>(static_cast<int64_t>(split + 1) * k_blocks / args.splits);
+        const int acc = it & 1;
+        const uint32_t acc_ph = (static_cast<uint32_t>(it) >> 1) & 1u;
+        if (!mbar_wait_bounded(&tempty[acc], acc_ph ^ 1u, args.status, 62)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BN2);
+        for (int kb = kb0; kb < kb1; ++kb) {
+          if (!mbar_wait_bounded(&full[s], ph, args.status, 63)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t a_addr = smem_u32(smem + s * kStage2);
+          const uint32_t b_addr = a_addr + kATile;
+#pragma unroll
+          for (int ks = 0; ks < BK2 / 8; ++ks) {
+            const uint64_t adesc = A_MN ? make_smem_desc(a_addr + ks * 1024, kChunk2, 512, kLayoutSw128Base32)
+                                        : make_smem_desc(a_addr + ks * 32, 16, 1024, kLayoutSw128);
+            const uint64_t bdesc = B_MN ? make_smem_desc(b_addr + ks * 1024, kChunk2, 512, kLayoutSw128Base32)
+                                        : make_smem_desc(b_addr + ks * 32, 16, 1024, kLayoutSw128);
+            umma_tf32_pair(d_tmem, adesc, bdesc, idesc, (kb != kb0 || ks != 0) ? 1u : 0u);
+          }
+          umma_commit_pair(&empty[s]);
+          if (++s == kStages2) {
+            s = 0;
+            ph ^= 1u;
+          }
+        }
+        if (ok) umma_commit_pair(&tfull[acc]);
+      }
+    }
+    __syncwarp();
+  } else {
+    // ---------------- epilogue (both CTAs, own 128 rows, all 256 columns) ----------------
+    const int q = warp & 3;
+    const int row_in_tile = static_cast<int>(rank) * BM2 + q * 32 + lane;
+    int it = 0;
+    bool ok = true;
+    for (int unit = pair; unit < num_units && ok; unit += n_pairs, ++it) {
+      int mb, nb;
+      tile_coords2(unit % num_tiles, m_blocks, n_blocks, mb, nb);
+      const bool first_split = unit < num_tiles;
+      const bool atomic = args.splits > 1;
+      const int acc = it & 1;
+      const uint32_t acc_ph = (static_cast<uint32_t>(it) >> 1) & 1u;
+      if (!mbar_wait_bounded(&tfull[acc], acc_ph, args.status, 64)) {
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      const int64_t grow = static_cast<int64_t>(mb) * 2 * BM2 + row_in_tile;
+      const bool row_ok = grow < args.M;
+      float* crow = args.C + grow * args.ldc;
+      const float* xrow = args.aux != nullptr ? args.aux + grow * args.ldc : nullptr;
+      const uint32_t t_row = tmem_base + static_cast<uint32_t>(acc * BN2) + (static_cast<uint32_t>(q * 32) << 16);
+#pragma unroll 1
+      for (int ch = 0; ch < BN2 / 32; ++ch) {
+        const int col0 = nb * BN2 + ch * 32;
+        if (col0 >= args.N) break;
+        float v[32];
+        tmem_ld_32x32(t_row + static_cast<uint32_t>(ch * 32), v);
+        if (!row_ok) {
+        } else if (atomic) {
+          // split-K: C was zeroed (STORE / RESIDUAL) or holds the running sum (ACCUMULATE)
+          const bool add_aux = first_split && args.epilogue == CTDK_EPI_RESIDUAL;
+          if (args.vec_ok && col0 + 32 <= args.N) {
+            float4* c4 = reinterpret_cast<float4*>(crow + col0);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              float4 r = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+              if (add_aux) {
+                const float4 x = reinterpret_cast<const float4*>(xrow + col0)[j];
+                r.x += x.x;
+                r.y += x.y;
+                r.z += x.z;
+                r.w += x.w;
+              }
+              atomicAdd(&c4[j], r);
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              const int col = col0 + j;
+              if (col < args.N) atomicAdd(&crow[col], v[j] + (add_aux ? xrow[col] : 0.0f));
+            }
+          }
+        } else if (args.vec_ok && col0 + 32 <= args.N) {
+          float4* c4 = reinterpret_cast<float4*>(crow + col0);
+          if (args.epilogue == CTDK_EPI_STORE) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) c4[j] = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+          } else {
+            const float4* x4 = args.epilogue == CTDK_EPI_ACCUMULATE ? reinterpret_cast<const float4*>(crow + col0)
+                                                                    : reinterpret_cast<const float4*>(xrow + col0);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              const float4 x = x4[j];
+              c4[j] = make_float4(v[4 * j] + x.x, v[4 * j + 1] + x.y, v[4 * j + 2] + x.z, v[4 * j + 3] + x.w);
+            }
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const int col = col0 + j;
+            if (col < args.N) {
+              float r = v[j];
+              if (args.epilogue == CTDK_EPI_ACCUMULATE) r += crow[col];
+              else if (args.epilogue == CTDK_EPI_RESIDUAL) r += xrow[col];
+              crow[col] = r;
+            }
+          }
+        }
+        __syncwarp();
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_leader(&tempty[acc]);
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // the peer has drained its accumulators and sent its last signals
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc2(tmem_base, 512);
+  }
+}
+
+template <bool A_MN, bool B_MN>
+int launch2(const CUtensorMap& ta, const CUtensorMap& tb, const Gemm2Args& args, cudaStream_t stream) {
+  auto* kern = gemm_tf32_2cta_kernel<A_MN, B_MN>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem2);
+  if (e != cudaSuccess) return fail(CTDK_ELAUNCH, "gemm(2cta): shared memory opt-in failed: %s", cudaGetErrorString(e));
+  const int tiles = ((args.M + 255) / 256) * ((args.N + BN2 - 1) / BN2) * args.splits;
+  int pairs = sm_count() / 2;
+  if (tiles < pairs) pairs = tiles;
+  kern<<<2 * pairs, 192, kSmem2, stream>>>(ta, tb, args);
+  return check_launch("ctdk_gemm(tcgen05, cta pair)");
+}
+
+}  // namespace
+
+// Enqueues the paired-CTA kernel; the maps must have been encoded with boxes of 128 rows for
+// K-major operands ({32, 128}) and {32, 32} for MN-major ones.
+int gemm_tcgen05_2cta(const CUtensorMap& ta, const CUtensorMap& tb, bool a_mn, bool b_mn, float* C,
+                      const float* aux, int64_t ldc, int M, int N, int K, int epilogue, int vec_ok, int splits,
+                      int* status, cudaStream_t stream) {
+  Gemm2Args args{C, aux, ldc, M, N, K, epilogue, vec_ok, splits, status};
+  if (!a_mn && !b_mn) return launch2<false, false>(ta, tb, args, stream);
+  if (!a_mn && b_mn) return launch2<false, true>(ta, tb, args, stream);
+  if (a_mn && !b_mn) return launch2<true, false>(ta, tb, args, stream);
+  return launch2<true, true>(ta, tb, args, stream);
+}
+
+}  // namespace ctdk

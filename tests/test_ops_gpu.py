@@ -174,7 +174,8 @@ def ints(shape, seed, lim=3):
 
 GEMM_SHAPES = [(128, 256, 32), (128, 128, 64), (2044, 576, 576), (300, 960, 1536), (1, 192, 576),
                (257, 1600, 960), (130, 64, 96), (64, 8, 8), (515, 320, 100), (200, 1000, 36),
-               (192, 576, 3000), (576, 200, 2044), (960, 960, 8192)]   # few tiles, long K: split-K
+               (192, 576, 3000), (576, 200, 2044), (960, 960, 8192),   # few tiles, long K: split-K
+               (2048, 512, 256), (4093, 1600, 960), (1300, 5120, 96)]  # large outputs: paired-CTA kernel
 
 
 @pytest.mark.parametrize("M,N,K_", GEMM_SHAPES)
