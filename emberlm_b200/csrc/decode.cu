@@ -1,0 +1,580 @@
+// KV-cache greedy decoding (batch 1): prefill with the training-path kernels, then one token per
+// step with HBM-bound kernels, the whole step captured once in a CUDA graph and replayed.
+//
+// Replaces the inference path of the reference: Model::forward with a cache
+// (emberlm include/ctd/nn/model.h:155-167), Attention::forward (include/ctd/nn/attention.h:43-97),
+// write_kv_inplace / read_kv_expanded (src/ops/kv_cache.cu:14-47) and the greedy branch of the
+// CPU sampler (src/core/sampling.cpp:13-20: first index of the maximum). Differences in execution:
+// K/V are written to the cache by the same kernel that applies QK-Norm and RoPE; attention reads
+// the cache in place (no expansion to [B,H,L,D] per token, no repeat of kv heads); the argmax runs
+// on the GPU and the next token id never leaves the device; position and token counters live in
+// device memory so that one captured graph serves every step.
+// Cache layout: [layer][kv head][max_seq][D] for K and for V (as the reference's KVLayer,
+// include/ctd/nn/kv_cache.h:23-37).
+#include <cfloat>
+#include <new>
+#include <vector>
+
+#include "common.cuh"
+
+namespace ctdk {
+namespace {
+
+// y[n] = dot(W[n,:], f(x)) (+ residual[n]); one warp per output row, 128-bit loads, f(x) staged in
+// shared memory once per CTA. f is the identity, RMSNorm (x * rsqrt(mean(x^2)+eps) * nw, the
+// reference's norm kernel, emberlm src/ops/norm.cu:18-50) or SwiGLU of a packed gate|up vector
+// (silu(g)*u, include/ctd/nn/mlp.h:16-21) so that no separate kernel has to run per token.
+enum { kPreNone = 0, kPreRmsNorm = 1, kPreSwiglu = 2 };
+
+template <int PRE>
+__global__ void __launch_bounds__(256)
+    gemv_kernel(const float* __restrict__ W, const float* __restrict__ x, float* __restrict__ y,
+                const float* __restrict__ residual, const float* __restrict__ nw, float eps, int N, int K) {
+  extern __shared__ float xs[];
+  __shared__ float red[8];
+  const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+  if (PRE == kPreSwiglu) {
+    for (int i = threadIdx.x; i < K; i += blockDim.x) {
+      const float g = x[i];
+      xs[i] = g / (1.0f + __expf(-g)) * x[K + i];
+    }
+  } else {
+    float ss = 0.0f;
+    for (int i = threadIdx.x; i < K; i += blockDim.x) {
+      const float v = x[i];
+      xs[i] = v;
+      ss += v * v;
+    }
+    if (PRE == kPreRmsNorm) {
+      ss = warp_sum(ss);
+      if (lane == 0) red[wid] = ss;
+      __syncthreads();
+      float tot = 0.0f;
+      for (int i = 0; i < (blockDim.x >> 5); ++i) tot += red[i];
+      const float sc = rsqrtf(tot / static_cast<float>(K) + eps);
+      for (int i = threadIdx.x; i < K; i += blockDim.x) xs[i] = xs[i] * sc * nw[i];
+    }
+  }
+  __syncthreads();
+  const int warp0 = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int nwarps = (gridDim.x * blockDim.x) >> 5;
+  const int K4 = K >> 2;
+  const float4* x4 = reinterpret_cast<const float4*>(xs);
+  for (int n = warp0; n < N; n += nwarps) {
+    const float4* w4 = reinterpret_cast<const float4*>(W + static_cast<int64_t>(n) * K);
+    float acc = 0.0f;
+    for (int i = lane; i < K4; i += 32) {
+      const float4 a = w4[i], b = x4[i];
+      acc += a.x * b.x + a.y * b.y + a.z * b.z + a.w * b.w;
+    }
+    acc = warp_sum(acc);
+    if (lane == 0) y[n] = residual != nullptr ? acc + residual[n] : acc;
+  }
+}
+
+// One warp per head slot of the single new row: per-head RMSNorm (optional) + RoPE at position
+// *pos for q and k; q goes to q_out, k and v go into the cache at position *pos.
+__global__ void __launch_bounds__(256)
+    decode_qkv_post_kernel(const float* __restrict__ qkv, const float* __restrict__ wq,
+                           const float* __restrict__ wk, const float2* __restrict__ table,
+                           const int* __restrict__ pos_ptr, float* __restrict__ q_out,
+                           float* __restrict__ kcache, float* __restrict__ vcache, int H, int Hk, int D,
+                           int max_seq, float eps) {
+  const int lane = threadIdx.x & 31;
+  const int slot = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  if (slot >= H + 2 * Hk) return;
+  const int pos = *pos_ptr;
+  const int Dh = D / 2;
+  const float* xr = qkv + static_cast<int64_t>(slot) * D;
+  if (slot >= H + Hk) {  // v head
+    float* dst = vcache + (static_cast<int64_t>(slot - H - Hk) * max_seq + pos) * D;
+    for (int i = lane; i < D; i += 32) dst[i] = xr[i];
+    return;
+  }
+  const bool is_q = slot < H;
+  const float* w = is_q ? wq : wk;
+  float s = 1.0f;
+  if (w != nullptr) {
+    float ss = 0.0f;
+    for (int i = lane; i < D; i += 32) ss += xr[i] * xr[i];
+    ss = warp_sum(ss);
+    s = rsqrtf(ss / static_cast<float>(D) + eps);
+  }
+  float* dst = is_q ? q_out + static_cast<int64_t>(slot) * D
+                    : kcache + (static_cast<int64_t>(slot - H) * max_seq + pos) * D;
+  for (int i = lane; i < Dh; i += 32) {
+    float a = xr[i], b = xr[i + Dh];
+    if (w != nullptr) {
+      a = a * s * w[i];
+      b = b * s * w[i + Dh];
+    }
+    const float2 cs = table[static_cast<int64_t>(pos) * Dh + i];
+    dst[i] = a * cs.x - b * cs.y;
+    dst[i + Dh] = a * cs.y + b * cs.x;
+  }
+}
+
+// Copies post-RoPE k and v rows of a prefilled qkv[T, (H+2Hk)*D] into the cache at positions 0..T-1.
+__global__ void __launch_bounds__(256)
+    kv_write_rows_kernel(const float* __restrict__ qkv, float* __restrict__ kcache, float* __restrict__ vcache,
+                         int T, int H, int Hk, int D, int max_seq) {
+  const int64_t n = static_cast<int64_t>(T) * 2 * Hk * (D / 4);
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  const int RS = (H + 2 * Hk) * D;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride) {
+    const int c = static_cast<int>(i % (D / 4));
+    const int hh = static_cast<int>((i / (D / 4)) % (2 * Hk));
+    const int t = static_cast<int>(i / (static_cast<int64_t>(D / 4) * 2 * Hk));
+    const float4 v = *reinterpret_cast<const float4*>(qkv + static_cast<int64_t>(t) * RS + (H + hh) * D + 4 * c);
+    float* cache = hh < Hk ? kcache : vcache;
+    const int hk = hh < Hk ? hh : hh - Hk;
+    *reinterpret_cast<float4*>(cache + (static_cast<int64_t>(hk) * max_seq + t) * D + 4 * c) = v;
+  }
+}
+
+// One CTA of 1024 threads per query head: one thread per key computes its score (keys beyond
+// 1024 in further passes), block-wide softmax, then thread (d, part) sums its slice of P*V.
+__global__ void __launch_bounds__(1024)
+    decode_attn_kernel(const float* __restrict__ q, const float* __restrict__ kcache,
+                       const float* __restrict__ vcache, float* __restrict__ out,
+                       const int* __restrict__ pos_ptr, int H, int Hk, int D, int max_seq, float scale) {
+  extern __shared__ float sm[];  // [max_seq] scores, [D] q, [1024] reduction scratch
+  float* sc = sm;
+  float* qs = sm + max_seq;
+  float* red = qs + D;
+  const int h = blockIdx.x, hk = h / (H / Hk);
+  const int L = *pos_ptr + 1;
+  const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  for (int i = threadIdx.x; i < D; i += blockDim.x) qs[i] = q[static_cast<int64_t>(h) * D + i];
+  __syncthreads();
+  const float* kb = kcache + static_cast<int64_t>(hk) * max_seq * D;
+  const float* vb = vcache + static_cast<int64_t>(hk) * max_seq * D;
+  float mx = -FLT_MAX;
+  for (int j = threadIdx.x; j < L; j += blockDim.x) {
+    const float4* kr = reinterpret_cast<const float4*>(kb + static_cast<int64_t>(j) * D);
+    const float4* q4 = reinterpret_cast<const float4*>(qs);
+    float acc = 0.0f;
+    for (int i = 0; i < D / 4; ++i) {
+      const float4 a = kr[i], b = q4[i];
+      acc += a.x * b.x + a.y * b.y + a.z * b.z + a.w * b.w;
+    }
+    acc *= scale;
+    sc[j] = acc;
+    mx = fmaxf(mx, acc);
+  }
+  mx = warp_max(mx);
+  if (lane == 0) red[wid] = mx;
+  __syncthreads();
+  mx = -FLT_MAX;
+  for (int i = 0; i < nw; ++i) mx = fmaxf(mx, red[i]);
+  __syncthreads();
+  float sum = 0.0f;
+  for (int j = threadIdx.x; j < L; j += blockDim.x) {
+    const float e = __expf(sc[j] - mx);
+    sc[j] = e;
+    sum += e;
+  }
+  sum = warp_sum(sum);
+  if (lane == 0) red[wid] = sum;
+  __syncthreads();
+  sum = 0.0f;
+  for (int i = 0; i < nw; ++i) sum += red[i];
+  const float inv = 1.0f / sum;
+  __syncthreads();
+  const int d = threadIdx.x % D, part = threadIdx.x / D, nparts = blockDim.x / D;
+  float acc = 0.0f;
+  for (int j = part; j < L; j += nparts) acc += sc[j] * vb[static_cast<int64_t>(j) * D + d];
+  red[part * D + d] = acc;
+  __syncthreads();
+  if (threadIdx.x < D) {
+    float t = 0.0f;
+    for (int p = 0; p < nparts; ++p) t += red[p * D + threadIdx.x];
+    out[static_cast<int64_t>(h) * D + threadIdx.x] = t * inv;
+  }
+}
+
+// First index of the maximum (the reference's greedy sampler); stores the token as the next input
+// and appends it to out_tokens[*count].
+__global__ void __launch_bounds__(1024)
+    argmax_kernel(const float* __restrict__ logits, int V, int64_t* __restrict__ cur_token,
+                  int64_t* __restrict__ out_tokens, const int* __restrict__ count) {
+  __shared__ float bv[32];
+  __shared__ int bi[32];
+  float best = -FLT_MAX;
+  int idx = 0x7fffffff;
+  for (int i = threadIdx.x; i < V; i += blockDim.x) {
+    const float v = logits[i];
+    if (v > best) {
+      best = v;
+      idx = i;
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
+    if (ov > best || (ov == best && oi < idx)) {
+      best = ov;
+      idx = oi;
+    }
+  }
+  const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+  if (lane == 0) {
+    bv[wid] = best;
+    bi[wid] = idx;
+  }
+  __syncthreads();
+  if (wid == 0) {
+    best = bv[lane];
+    idx = bi[lane];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
+      if (ov > best || (ov == best && oi < idx)) {
+        best = ov;
+        idx = oi;
+      }
+    }
+    if (lane == 0) {
+      *cur_token = idx;
+      if (out_tokens != nullptr) out_tokens[*count] = idx;
+    }
+  }
+}
+
+__global__ void bump_kernel(int* pos, int* count) {
+  *pos += 1;
+  *count += 1;
+}
+__global__ void set_counters_kernel(int* pos, int* count, int p, int c) {
+  *pos = p;
+  *count = c;
+}
+
+}  // namespace
+}  // namespace ctdk
+
+// ----------------------------------------------------------------------------------------
+// Host side: the decode engine
+// ----------------------------------------------------------------------------------------
+namespace ctdk {
+namespace {
+
+struct LayerW {
+  int64_t w_in, wq, wo, wqn, wkn, w_post, wg, wd;
+};
+
+struct Decoder {
+  ctdk_model_config cfg;
+  const float* params;
+  int64_t embed, norm;
+  std::vector<LayerW> lw;
+  int max_seq, QKVN;
+  // workspace
+  float *rope_table, *kcache, *vcache;  // caches: [L][Hk][max_seq][D]
+  float *x, *h1, *qkv, *q, *attn, *hm, *gu, *act, *logits;
+  float *pa, *pb, *pqkv, *pattn, *plse, *pgu, *pact;  // prefill buffers ([max_seq, ...])
+  int64_t* cur_token;
+  int* counters;  // [0] = position of the next token, [1] = tokens generated
+  cudaGraphExec_t graph = nullptr;
+  int64_t* graph_out = nullptr;
+  cudaStream_t graph_stream = nullptr;
+  int64_t prompt_len = 0, generated = 0;
+};
+
+struct Bump2 {
+  char* base;
+  int64_t used = 0;
+  explicit Bump2(void* b) : base(static_cast<char*>(b)) {}
+  float* floats(int64_t n) {
+    const int64_t bytes = (n * 4 + 255) / 256 * 256;
+    float* p = base ? reinterpret_cast<float*>(base + used) : nullptr;
+    used += bytes;
+    return p;
+  }
+};
+
+void carve_decoder(Decoder& d, Bump2& b) {
+  const ctdk_model_config& c = d.cfg;
+  const int64_t hid = c.hidden_size, I = c.intermediate_size, D = c.head_dim, H = c.num_attention_heads,
+                Hk = c.num_key_value_heads, L = c.num_hidden_layers, S = d.max_seq;
+  d.rope_table = b.floats(S * D);
+  d.kcache = b.floats(L * Hk * S * D);
+  d.vcache = b.floats(L * Hk * S * D);
+  d.x = b.floats(hid);
+  d.h1 = b.floats(hid);
+  d.qkv = b.floats(d.QKVN);
+  d.q = b.floats(H * D);
+  d.attn = b.floats(H * D);
+  d.hm = b.floats(hid);
+  d.gu = b.floats(2 * I);
+  d.act = b.floats(I);
+  d.logits = b.floats(c.vocab_size);
+  d.pa = b.floats(S * hid);
+  d.pb = b.floats(S * hid);
+  d.pqkv = b.floats(S * d.QKVN);
+  d.pattn = b.floats(S * H * D);
+  d.plse = b.floats(H * S);
+  d.pgu = b.floats(S * 2 * I);
+  d.pact = b.floats(S * I);
+  d.cur_token = reinterpret_cast<int64_t*>(b.floats(2));
+  d.counters = reinterpret_cast<int*>(b.floats(4));  // position, count, scratch
+}
+
+int init_decoder(Decoder& d, const ctdk_model_config* cfg, int64_t max_seq) {
+  CTDK_REQUIRE(cfg != nullptr && max_seq > 0 && max_seq < (1 << 20), "decoder: bad arguments");
+  const int64_t n = ctdk_model_num_tensors(cfg);
+  if (n < 0) return CTDK_EINVAL;
+  d.cfg = *cfg;
+  d.max_seq = static_cast<int>(max_seq);
+  d.QKVN = (cfg->num_attention_heads + 2 * cfg->num_key_value_heads) * cfg->head_dim;
+  std::vector<int64_t> off(n);
+  int rc = ctdk_model_layout(cfg, off.data(), nullptr, nullptr, nullptr);
+  if (rc != CTDK_OK) return rc;
+  d.embed = off[0];
+  d.norm = off[n - 1];
+  const int per = cfg->qk_norm ? 11 : 9;
+  d.lw.resize(cfg->num_hidden_layers);
+  for (int l = 0; l < cfg->num_hidden_layers; ++l) {
+    const int64_t* o = off.data() + 1 + static_cast<int64_t>(l) * per;
+    LayerW& w = d.lw[l];
+    w.w_in = o[0];
+    w.wq = o[1];
+    w.wo = o[4];
+    int i = 5;
+    if (cfg->qk_norm) {
+      w.wqn = o[5];
+      w.wkn = o[6];
+      i = 7;
+    } else {
+      w.wqn = w.wkn = -1;
+    }
+    w.w_post = o[i];
+    w.wg = o[i + 1];
+    w.wd = o[i + 3];
+  }
+  return CTDK_OK;
+}
+
+#define DTRY(expr)                    \
+  do {                                \
+    int rc_ = (expr);                 \
+    if (rc_ != CTDK_OK) return rc_;   \
+  } while (0)
+
+int gemv(const float* W, const float* x, float* y, const float* residual, int N, int K, cudaStream_t s,
+         int pre = kPreNone, const float* nw = nullptr, float eps = 0.0f) {
+  CTDK_REQUIRE(K % 4 == 0 && K <= 12288, "gemv: K must be a multiple of 4 and at most 12288");
+  const int64_t cap = static_cast<int64_t>(sm_count()) * 8;
+  const int64_t need = (N + 7) / 8;
+  const int grid = static_cast<int>(need < cap ? need : cap);
+  const size_t smem = K * sizeof(float);
+  if (pre == kPreRmsNorm) gemv_kernel<kPreRmsNorm><<<grid, 256, smem, s>>>(W, x, y, residual, nw, eps, N, K);
+  else if (pre == kPreSwiglu) gemv_kernel<kPreSwiglu><<<grid, 256, smem, s>>>(W, x, y, residual, nw, eps, N, K);
+  else gemv_kernel<kPreNone><<<grid, 256, smem, s>>>(W, x, y, residual, nw, eps, N, K);
+  return check_launch("decode gemv");
+}
+
+ctdk_rope_params decode_rope_params(const ctdk_model_config& c) {
+  ctdk_rope_params p;
+  p.theta = c.rope_theta;
+  p.scaling_factor = c.rope_scaling_factor;
+  p.low_freq_wavelen = static_cast<float>(c.rope_scaling_original_max_pos) / c.rope_scaling_low_freq_factor;
+  p.high_freq_wavelen = static_cast<float>(c.rope_scaling_original_max_pos) / c.rope_scaling_high_freq_factor;
+  return p;
+}
+
+// One token: embedding of *cur_token at position *pos -> logits -> argmax -> counters += 1.
+int enqueue_token_step(Decoder& d, int64_t* out_tokens, cudaStream_t s) {
+  const ctdk_model_config& c = d.cfg;
+  const int hid = c.hidden_size, I = c.intermediate_size, D = c.head_dim, H = c.num_attention_heads,
+            Hk = c.num_key_value_heads;
+  const float* P = d.params;
+  const int64_t cache_layer = static_cast<int64_t>(Hk) * d.max_seq * D;
+  const float scale = 1.0f / sqrtf(static_cast<float>(D));
+  DTRY(ctdk_embedding_fwd(d.cur_token, P + d.embed, d.x, 1, hid, c.vocab_size, s));
+  for (int l = 0; l < c.num_hidden_layers; ++l) {
+    const LayerW& w = d.lw[l];
+    DTRY(gemv(P + w.wq, d.x, d.qkv, nullptr, d.QKVN, hid, s, kPreRmsNorm, P + w.w_in, c.rms_norm_eps));
+    decode_qkv_post_kernel<<<ceil_div((H + 2 * Hk) * 32, 256), 256, 0, s>>>(
+        d.qkv, c.qk_norm ? P + w.wqn : nullptr, c.qk_norm ? P + w.wkn : nullptr,
+        reinterpret_cast<const float2*>(d.rope_table), d.counters, d.q, d.kcache + l * cache_layer,
+        d.vcache + l * cache_layer, H, Hk, D, d.max_seq, c.rms_norm_eps);
+    DTRY(check_launch("decode qkv post"));
+    decode_attn_kernel<<<H, 1024, (d.max_seq + D + 1024) * sizeof(float), s>>>(
+        d.q, d.kcache + l * cache_layer, d.vcache + l * cache_layer, d.attn, d.counters, H, Hk, D, d.max_seq, scale);
+    DTRY(check_launch("decode attention"));
+    DTRY(gemv(P + w.wo, d.attn, d.hm, d.x, hid, H * D, s));
+    DTRY(gemv(P + w.wg, d.hm, d.gu, nullptr, 2 * I, hid, s, kPreRmsNorm, P + w.w_post, c.rms_norm_eps));
+    DTRY(gemv(P + w.wd, d.gu, d.x, d.hm, hid, I, s, kPreSwiglu));
+  }
+  DTRY(gemv(P + d.embed, d.x, d.logits, nullptr, c.vocab_size, hid, s, kPreRmsNorm, P + d.norm, c.rms_norm_eps));
+  argmax_kernel<<<1, 1024, 0, s>>>(d.logits, c.vocab_size, d.cur_token, out_tokens, d.counters + 1);
+  DTRY(check_launch("decode argmax"));
+  bump_kernel<<<1, 1, 0, s>>>(d.counters, d.counters + 1);
+  return check_launch("decode bump");
+}
+
+}  // namespace
+}  // namespace ctdk
+
+using namespace ctdk;
+
+extern "C" {
+
+int64_t ctdk_decode_workspace_bytes(const ctdk_model_config* cfg, int64_t max_seq) {
+  Decoder d;
+  if (init_decoder(d, cfg, max_seq) != CTDK_OK) return -1;
+  Bump2 b(nullptr);
+  carve_decoder(d, b);
+  return b.used;
+}
+
+int ctdk_decode_create(const ctdk_model_config* cfg, const float* params, void* workspace,
+                       int64_t workspace_bytes, int64_t max_seq, void** decoder) {
+  CTDK_REQUIRE(decoder && params && workspace, "ctdk_decode_create: null pointer");
+  CTDK_REQUIRE((reinterpret_cast<uintptr_t>(params) & 255u) == 0 && (reinterpret_cast<uintptr_t>(workspace) & 255u) == 0,
+               "ctdk_decode_create: arenas must be 256-byte aligned");
+  Decoder* d = new (std::nothrow) Decoder();
+  if (d == nullptr) return fail(CTDK_ENOMEM, "ctdk_decode_create: out of host memory");
+  int rc = init_decoder(*d, cfg, max_seq);
+  if (rc != CTDK_OK) {
+    delete d;
+    return rc;
+  }
+  CTDK_REQUIRE((static_cast<int64_t>(max_seq) + cfg->head_dim + 1024) * 4 <= 200 * 1024,
+               "ctdk_decode_create: max_seq too large for the decode attention kernel");
+  d->params = params;
+  Bump2 b(workspace);
+  carve_decoder(*d, b);
+  if (b.used > workspace_bytes) {
+    delete d;
+    return fail(CTDK_EINVAL, "ctdk_decode_create: workspace too small");
+  }
+  cudaError_t e = cudaFuncSetAttribute(decode_attn_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       static_cast<int>((max_seq + cfg->head_dim + 1024) * 4));
+  if (e != cudaSuccess) {
+    delete d;
+    return fail(CTDK_ELAUNCH, "ctdk_decode_create: %s", cudaGetErrorString(e));
+  }
+  *decoder = d;
+  return CTDK_OK;
+}
+
+int ctdk_decode_destroy(void* decoder) {
+  Decoder* d = static_cast<Decoder*>(decoder);
+  if (d != nullptr && d->graph != nullptr) cudaGraphExecDestroy(d->graph);
+  delete d;
+  return CTDK_OK;
+}
+
+int ctdk_decode_prefill(void* decoder, const int64_t* ids, int64_t T, void* stream) {
+  CTDK_REQUIRE(decoder && ids, "ctdk_decode_prefill: null pointer");
+  Decoder& d = *static_cast<Decoder*>(decoder);
+  const ctdk_model_config& c = d.cfg;
+  CTDK_REQUIRE(T > 0 && T < d.max_seq, "ctdk_decode_prefill: prompt length must be in [1, max_seq)");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int hid = c.hidden_size, I = c.intermediate_size, D = c.head_dim, H = c.num_attention_heads,
+            Hk = c.num_key_value_heads;
+  const float* P = d.params;
+  const int64_t cache_layer = static_cast<int64_t>(Hk) * d.max_seq * D;
+  const ctdk_rope_params rp = decode_rope_params(c);
+  DTRY(ctdk_rope_table(d.rope_table, d.max_seq, D, 0, &rp, s));
+  DTRY(ctdk_embedding_fwd(ids, P + d.embed, d.pa, T, hid, c.vocab_size, s));
+  const int prec = c.precision;
+  for (int l = 0; l < c.num_hidden_layers; ++l) {
+    const LayerW& w = d.lw[l];
+    DTRY(ctdk_rmsnorm_fwd(d.pa, P + w.w_in, d.pb, nullptr, T, hid, c.rms_norm_eps, s));
+    DTRY(ctdk_gemm(d.pb, P + w.wq, d.pqkv, T, d.QKVN, hid, hid, hid, d.QKVN, 0, 1, prec, CTDK_EPI_STORE, nullptr, s));
+    if (c.qk_norm) {
+      // out of place is required with norm weights: reuse the gate|up buffer as the destination
+      CTDK_REQUIRE(2 * I >= d.QKVN, "ctdk_decode_prefill: intermediate size too small for the QK-Norm buffer");
+      DTRY(ctdk_qk_norm_rope_fwd(d.pqkv, d.pgu, P + w.wqn, P + w.wkn, d.pattn, d.pattn + T * H, d.rope_table, 1, T, H,
+                                 Hk, D, c.rms_norm_eps, s));
+      DTRY(ctdk_scale(d.pgu, 1.0f, d.pqkv, T * static_cast<int64_t>(d.QKVN), s));
+    } else {
+      DTRY(ctdk_qk_norm_rope_fwd(d.pqkv, d.pqkv, nullptr, nullptr, nullptr, nullptr, d.rope_table, 1, T, H, Hk, D,
+                                 c.rms_norm_eps, s));
+    }
+    kv_write_rows_kernel<<<sm_count() * 4, 256, 0, s>>>(d.pqkv, d.kcache + l * cache_layer, d.vcache + l * cache_layer,
+                                                        static_cast<int>(T), H, Hk, D, d.max_seq);
+    DTRY(check_launch("decode kv write"));
+    DTRY(ctdk_attn_fwd(d.pqkv, d.pattn, d.plse, 1, T, H, Hk, D, s));
+    DTRY(ctdk_gemm(d.pattn, P + w.wo, d.pb, T, hid, H * D, H * D, H * D, hid, 0, 1, prec, CTDK_EPI_RESIDUAL, d.pa, s));
+    DTRY(ctdk_rmsnorm_fwd(d.pb, P + w.w_post, d.pa, nullptr, T, hid, c.rms_norm_eps, s));
+    DTRY(ctdk_gemm(d.pa, P + w.wg, d.pgu, T, 2 * I, hid, hid, hid, 2 * I, 0, 1, prec, CTDK_EPI_STORE, nullptr, s));
+    DTRY(ctdk_swiglu_fwd(d.pgu, d.pact, T, I, s));
+    DTRY(ctdk_gemm(d.pact, P + w.wd, d.pa, T, hid, I, I, I, hid, 0, 1, prec, CTDK_EPI_RESIDUAL, d.pb, s));
+  }
+  // logits of the last prompt position only, then the first generated token
+  DTRY(ctdk_rmsnorm_fwd(d.pa + (T - 1) * hid, P + d.norm, d.h1, nullptr, 1, hid, c.rms_norm_eps, s));
+  DTRY(gemv(P + d.embed, d.h1, d.logits, nullptr, c.vocab_size, hid, s));
+  set_counters_kernel<<<1, 1, 0, s>>>(d.counters, d.counters + 1, static_cast<int>(T), 0);
+  d.prompt_len = T;
+  d.generated = 0;
+  return check_launch("decode counters");
+}
+
+int ctdk_decode_logits(void* decoder, const float** logits) {
+  CTDK_REQUIRE(decoder && logits, "ctdk_decode_logits: null pointer");
+  *logits = static_cast<Decoder*>(decoder)->logits;
+  return CTDK_OK;
+}
+
+int ctdk_decode_greedy(void* decoder, int64_t n_new, int64_t* out_tokens, void* stream) {
+  CTDK_REQUIRE(decoder && out_tokens, "ctdk_decode_greedy: null pointer");
+  CTDK_REQUIRE(n_new >= 0, "ctdk_decode_greedy: negative token count");
+  Decoder& d = *static_cast<Decoder*>(decoder);
+  CTDK_REQUIRE(d.prompt_len > 0, "ctdk_decode_greedy: call ctdk_decode_prefill first");
+  CTDK_REQUIRE(d.prompt_len + d.generated + n_new <= d.max_seq,
+               "ctdk_decode_greedy: %lld more tokens would exceed max_seq %d", static_cast<long long>(n_new),
+               d.max_seq);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  int64_t todo = n_new;
+  if (todo > 0 && d.generated == 0) {
+    // the first new token comes from the prefill logits; its position is the prompt length
+    argmax_kernel<<<1, 1024, 0, s>>>(d.logits, d.cfg.vocab_size, d.cur_token, out_tokens, d.counters + 1);
+    DTRY(check_launch("decode argmax"));
+    bump_kernel<<<1, 1, 0, s>>>(d.counters + 2, d.counters + 1);  // count += 1 (position unchanged)
+    DTRY(check_launch("decode bump"));
+    d.generated = 1;
+    --todo;
+  }
+  if (todo == 0) return CTDK_OK;
+  // One token step = ~9 kernels per layer; captured once and replayed, so a step costs one launch.
+  const bool can_capture = s != nullptr;
+  if (can_capture && (d.graph == nullptr || d.graph_out != out_tokens || d.graph_stream != s)) {
+    if (d.graph != nullptr) {
+      cudaGraphExecDestroy(d.graph);
+      d.graph = nullptr;
+    }
+    cudaGraph_t g = nullptr;
+    cudaError_t e = cudaStreamBeginCapture(s, cudaStreamCaptureModeThreadLocal);
+    if (e != cudaSuccess) return fail(CTDK_ELAUNCH, "decode: begin capture: %s", cudaGetErrorString(e));
+    const int rc = enqueue_token_step(d, out_tokens, s);
+    e = cudaStreamEndCapture(s, &g);
+    if (rc != CTDK_OK) {
+      if (g != nullptr) cudaGraphDestroy(g);
+      return rc;
+    }
+    if (e != cudaSuccess) return fail(CTDK_ELAUNCH, "decode: end capture: %s", cudaGetErrorString(e));
+    e = cudaGraphInstantiate(&d.graph, g, 0);
+    cudaGraphDestroy(g);
+    if (e != cudaSuccess) return fail(CTDK_ELAUNCH, "decode: graph instantiate: %s", cudaGetErrorString(e));
+    d.graph_out = out_tokens;
+    d.graph_stream = s;
+  }
+  for (int64_t i = 0; i < todo; ++i) {
+    if (can_capture) {
+      cudaError_t e = cudaGraphLaunch(d.graph, s);
+      if (e != cudaSuccess) return fail(CTDK_ELAUNCH, "decode: graph launch: %s", cudaGetErrorString(e));
+    } else {
+      DTRY(enqueue_token_step(d, out_tokens, s));
+    }
+  }
+  d.generated += todo;
+  return CTDK_OK;
+}
+
+}  // extern "C"

@@ -235,7 +235,7 @@ class TrainEngine:
 
     def __del__(self):
         h = getattr(self, "_h", None)
-        if h:
+        if h and _L is not None:
             _L.ctdk_engine_destroy(h)
             self._h = None
 
@@ -349,3 +349,80 @@ def row_weights(loss_mask: torch.Tensor, micro_batch: int, accum_total: int) -> 
     sm = m.sum(dim=1, keepdim=True)
     w = torch.where(sm > 0, m / (sm * accum_total), torch.zeros_like(m))
     return w.view(rows, T).contiguous()
+
+
+# ----------------------------------------------------------------------------------------------
+# KV-cache greedy decoding (the ctd_generate path)
+# ----------------------------------------------------------------------------------------------
+_L.ctdk_decode_workspace_bytes.restype = C.c_int64
+_L.ctdk_decode_workspace_bytes.argtypes = [C.POINTER(ModelConfig), C.c_int64]
+_L.ctdk_decode_create.restype = C.c_int
+_L.ctdk_decode_create.argtypes = [C.POINTER(ModelConfig), C.c_void_p, C.c_void_p, C.c_int64, C.c_int64,
+                                  C.POINTER(C.c_void_p)]
+_L.ctdk_decode_destroy.restype = C.c_int
+_L.ctdk_decode_destroy.argtypes = [C.c_void_p]
+_L.ctdk_decode_prefill.restype = C.c_int
+_L.ctdk_decode_prefill.argtypes = [C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p]
+_L.ctdk_decode_greedy.restype = C.c_int
+_L.ctdk_decode_greedy.argtypes = [C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p]
+_L.ctdk_decode_logits.restype = C.c_int
+_L.ctdk_decode_logits.argtypes = [C.c_void_p, C.POINTER(C.c_void_p)]
+
+
+class Decoder:
+    """Greedy KV-cache generation, batch 1, as ctd_generate with temperature <= 0
+    (tools/ctd_generate/main.cpp:94-184): prefill the prompt, then one token per step."""
+
+    def __init__(self, cfg: ModelConfig, max_seq_len: int, device="cuda:0", params: torch.Tensor | None = None):
+        self.cfg, self.max_seq_len = cfg, max_seq_len
+        self.device = torch.device(device)
+        self.layout = model_layout(cfg)
+        self.params = params if params is not None else torch.zeros(self.layout.total, dtype=torch.float32,
+                                                                    device=self.device)
+        ws = _L.ctdk_decode_workspace_bytes(C.byref(cfg), max_seq_len)
+        if ws < 0:
+            raise lib.CtdkError(-1, lib.last_error())
+        self.workspace = torch.zeros(ws, dtype=torch.uint8, device=self.device)
+        self._h = C.c_void_p()
+        lib.check(_L.ctdk_decode_create(C.byref(cfg), self.params.data_ptr(), self.workspace.data_ptr(), ws,
+                                        max_seq_len, C.byref(self._h)))
+        self.stream = torch.cuda.Stream(device=self.device)
+
+    def __del__(self):
+        h = getattr(self, "_h", None)
+        if h and _L is not None:
+            _L.ctdk_decode_destroy(h)
+            self._h = None
+
+    def named_parameters(self) -> dict:
+        lo = self.layout
+        return {n: self.params[o:o + k].view(s) for n, s, o, k in zip(lo.names, lo.shapes, lo.offsets, lo.numels)}
+
+    def load_parameters(self, tensors: dict) -> None:
+        for n, v in self.named_parameters().items():
+            src = tensors[n]
+            src = torch.from_numpy(np.ascontiguousarray(src)) if isinstance(src, np.ndarray) else src
+            v.copy_(src.to(torch.float32))
+
+    def generate(self, input_ids, max_new_tokens: int) -> torch.Tensor:
+        """Returns the generated token ids (device int64 [n]); n = min(max_new_tokens, room left in
+        max_seq_len). An empty prompt raises, as the reference reports 'empty_prompt'."""
+        ids = torch.as_tensor(input_ids, dtype=torch.int64, device=self.device).reshape(-1).contiguous()
+        if ids.numel() == 0:
+            raise RuntimeError("generate: empty_prompt")
+        n = min(max_new_tokens, self.max_seq_len - ids.numel())
+        out = torch.zeros(max(n, 1), dtype=torch.int64, device=self.device)
+        self.stream.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(self.stream):
+            lib.check(_L.ctdk_decode_prefill(self._h, ids.data_ptr(), ids.numel(), self.stream.cuda_stream))
+            if n > 0:
+                lib.check(_L.ctdk_decode_greedy(self._h, n, out.data_ptr(), self.stream.cuda_stream))
+        torch.cuda.current_stream().wait_stream(self.stream)
+        return out[:max(n, 0)]
+
+    def last_logits(self) -> torch.Tensor:
+        p = C.c_void_p()
+        lib.check(_L.ctdk_decode_logits(self._h, C.byref(p)))
+        base = self.workspace.data_ptr()
+        off = p.value - base
+        return self.workspace[off:off + 4 * self.cfg.vocab_size].view(torch.float32)

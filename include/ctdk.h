@@ -277,6 +277,27 @@ int ctdk_engine_forward_loss(void* engine, const int64_t* ids, const int64_t* ta
 typedef void (*ctdk_layer_callback)(int layer, void* user);
 int ctdk_engine_set_layer_callback(void* engine, ctdk_layer_callback cb, void* user);
 
+/* ------------------------------------------------------------------------------------
+ * KV-cache greedy decoding, batch 1. Replaces the cached inference path: Model::forward with a
+ * KVCache (include/ctd/nn/model.h:155-167), Attention::forward (include/ctd/nn/attention.h:43-97),
+ * write_kv_inplace / read_kv_expanded (src/ops/kv_cache.cu:49-109) and the greedy sampler
+ * (src/core/sampling.cpp:13-20, first index of the maximum) used by tools/ctd_generate/main.cpp.
+ * The caller owns the parameter arena (same layout as the training engine) and a workspace of
+ * ctdk_decode_workspace_bytes(cfg, max_seq) bytes holding the K/V cache [layer][kv head][max_seq][D].
+ *   prefill : runs the prompt (ids int64 [T], 1 <= T < max_seq) and fills the cache;
+ *   greedy  : appends n_new tokens to out_tokens (device int64), continuing where the last call
+ *             stopped; token ids stay on the device, one CUDA graph launch per token when `stream`
+ *             is not the legacy default stream;
+ *   logits  : device pointer to the [vocab] logits of the last processed position.
+ * ------------------------------------------------------------------------------------ */
+int64_t ctdk_decode_workspace_bytes(const ctdk_model_config* cfg, int64_t max_seq);
+int ctdk_decode_create(const ctdk_model_config* cfg, const float* params, void* workspace,
+                       int64_t workspace_bytes, int64_t max_seq, void** decoder);
+int ctdk_decode_destroy(void* decoder);
+int ctdk_decode_prefill(void* decoder, const int64_t* ids, int64_t T, void* stream);
+int ctdk_decode_greedy(void* decoder, int64_t n_new, int64_t* out_tokens, void* stream);
+int ctdk_decode_logits(void* decoder, const float** logits);
+
 #ifdef __cplusplus
 }
 #endif

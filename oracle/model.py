@@ -259,3 +259,51 @@ def train_step(params, cfg, micro_batches, opt: AdamWState, lr, beta1, beta2, ep
                                                        beta1, beta2, eps, weight_decay if decay else 0.0)
     logged = acc_loss / acc_active if acc_active > 0 else 0.0
     return logged, float(norm), pre_clip
+
+
+def forward_logits(params, cfg: LlamaConfig, ids, acc=F32):
+    """Model::forward without a cache (include/ctd/nn/model.h:155-167): logits [B, T, V]. With a
+    causal mask this equals the cached inference path position by position (the reference tests
+    that in tests/test_integration_kvcache.cpp)."""
+    B, T = ids.shape
+    hid, D = cfg.hidden_size, cfg.head_dim
+    H, Hk = cfg.num_attention_heads, cfg.num_key_value_heads
+    eps, rk = cfg.rms_norm_eps, cfg.rope_kwargs()
+    E = params["model.embed_tokens.weight"]
+    h = ops.embedding(ids, E)
+    for i in range(cfg.num_hidden_layers):
+        p = f"model.layers.{i}."
+        x2 = ops.rms_norm(h, params[p + "input_layernorm.weight"], eps, acc).reshape(B * T, hid)
+        q = ops.matmul(x2, params[p + "self_attn.q_proj.weight"], False, True, acc).reshape(B, T, H, D)
+        k = ops.matmul(x2, params[p + "self_attn.k_proj.weight"], False, True, acc).reshape(B, T, Hk, D)
+        v = ops.matmul(x2, params[p + "self_attn.v_proj.weight"], False, True, acc).reshape(B, T, Hk, D)
+        if cfg.qk_norm:
+            q = ops.rms_norm(q, params[p + "self_attn.q_norm.weight"], eps, acc)
+            k = ops.rms_norm(k, params[p + "self_attn.k_norm.weight"], eps, acc)
+        q, k = ops.rope(q, 0, cfg.rope_theta, 1.0, **rk), ops.rope(k, 0, cfg.rope_theta, 1.0, **rk)
+        attn, _ = ops.attention_train(q, k, v, H // Hk, acc)
+        a = ops.matmul(attn.reshape(B * T, H * D), params[p + "self_attn.o_proj.weight"], False, True, acc)
+        hm = ops.add(h, a.reshape(B, T, hid))
+        y2 = ops.rms_norm(hm, params[p + "post_attention_layernorm.weight"], eps, acc).reshape(B * T, hid)
+        g = ops.matmul(y2, params[p + "mlp.gate_proj.weight"], False, True, acc)
+        u = ops.matmul(y2, params[p + "mlp.up_proj.weight"], False, True, acc)
+        m = ops.matmul(ops.mul(ops.silu(g, acc), u), params[p + "mlp.down_proj.weight"], False, True, acc)
+        h = ops.add(hm, m.reshape(B, T, hid))
+    hf = ops.rms_norm(h, params["model.norm.weight"], eps, acc)
+    return ops.matmul(hf.reshape(B * T, hid), E, False, True, acc).reshape(B, T, -1)
+
+
+def greedy_generate(params, cfg: LlamaConfig, prompt, max_new_tokens, acc=F32):
+    """Greedy decoding as tools/ctd_generate/main.cpp:110-184 with temperature <= 0 and no EOS:
+    argmax = first index of the maximum (src/core/sampling.cpp:13-20). Recomputes the full prefix
+    each step (no cache), which gives the same logits."""
+    ids = list(int(t) for t in prompt)
+    out, margins = [], []
+    for _ in range(max_new_tokens):
+        z = forward_logits(params, cfg, np.array([ids], dtype=np.int64), acc)[0, -1]
+        t = int(np.argmax(z))
+        top2 = np.partition(z, -2)[-2:]
+        margins.append(float(top2[1] - top2[0]))
+        out.append(t)
+        ids.append(t)
+    return out, margins
