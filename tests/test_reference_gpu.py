@@ -69,3 +69,41 @@ def test_engine_matches_committed_reference_outputs(name):
     for k in grads0:
         assert tensor_err(grads0[k], gold["grad/" + k]) <= 1e-2, k
         assert tensor_err(params_out[k], gold["param/" + k]) <= 1e-2, k
+
+
+@pytest.mark.skipif(not ref_run.available(), reason="oracle/_ref/ref_harness not built")
+def test_full_size_smollm2_135m_step_matches_reference():
+    """BASELINE config 1 at full size (SmolLM2-135M shape, 4 rows x 512 tokens, one micro-batch):
+    one optimizer step of the engine against the reference's CUDA build on the same bytes.
+    Stated tolerances (TF32 mode): loss rel <= 1e-3, per-tensor gradient and updated-weight
+    error max|a-b|/max|b| <= 1e-2."""
+    from emberlm_b200 import engine as E
+    from oracle import model as om
+    cfg = om.PRESETS["smollm2_135m"]
+    params = om.init_params(cfg, seed=1234)
+    tok, msk = om.synth_batch(cfg.vocab_size, 4, 512, seed=4321)
+    hp = dict(lr=1e-4, beta1=0.9, beta2=0.999, eps=1e-8, weight_decay=0.01, clip=1.0)
+    ref = ref_run.run_reference(cfg, params, tok, msk, 4, 1, steps=1, warmup=0, **hp)
+    eng = E.TrainEngine(E.make_config(**E.PRESETS["smollm2_135m"]), 4, 511, **hp)
+    eng.load_parameters(params)
+    ids, tgt, m = om.make_batch(tok, msk, [0, 1, 2, 3])
+    d_m = torch.from_numpy(m).cuda()
+    eng.loss_sums.zero_()
+    eng.forward_backward(torch.from_numpy(ids).cuda(), torch.from_numpy(tgt).cuda(), d_m, E.row_weights(d_m, 4, 1))
+    torch.cuda.synchronize()
+    worst_g = ("", 0.0)
+    for k, v in eng.named_grads().items():
+        e = tensor_err(v.cpu().numpy(), ref["grads"][k])
+        worst_g = max(worst_g, (k, e), key=lambda t: t[1])
+    eng.optimizer_step()
+    met = eng.read_metrics()
+    worst_p = ("", 0.0)
+    for k, v in eng.named_parameters().items():
+        e = tensor_err(v.cpu().numpy(), ref["params"][k])
+        worst_p = max(worst_p, (k, e), key=lambda t: t[1])
+    print(f"loss {met['loss']:.6f} vs {ref['loss'][0]:.6f}; grad_norm {met['grad_norm']:.5f} vs "
+          f"{ref['grad_norm'][0]:.5f}; worst grad {worst_g}; worst weight {worst_p}")
+    assert abs(met["loss"] - ref["loss"][0]) <= 1e-3 * abs(ref["loss"][0])
+    assert abs(met["grad_norm"] - ref["grad_norm"][0]) <= 1e-2 * ref["grad_norm"][0]
+    assert worst_g[1] <= 1e-2, worst_g
+    assert worst_p[1] <= 1e-2, worst_p
