@@ -47,6 +47,32 @@ __device__ __forceinline__ void mma_tf32(float (&c)[4], uint32_t a0, uint32_t a1
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
+// One m16n8k8 product in TF32, or (X3) the three-product split a = a_hi + a_lo, b = b_hi + b_lo,
+// a*b ~ a_lo*b_hi + a_hi*b_lo + a_hi*b_hi, which recovers near-fp32 accuracy.
+__device__ __forceinline__ void split_tf32(uint32_t x, uint32_t& hi, uint32_t& lo) {
+  const float f = __uint_as_float(x);
+  hi = f2tf32(f);
+  lo = f2tf32(f - __uint_as_float(hi));
+}
+template <bool X3>
+__device__ __forceinline__ void mma_x(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                      uint32_t b0, uint32_t b1) {
+  if (!X3) {
+    mma_tf32(c, a0, a1, a2, a3, b0, b1);
+  } else {
+    uint32_t ah[4], al[4], bh[2], bl[2];
+    split_tf32(a0, ah[0], al[0]);
+    split_tf32(a1, ah[1], al[1]);
+    split_tf32(a2, ah[2], al[2]);
+    split_tf32(a3, ah[3], al[3]);
+    split_tf32(b0, bh[0], bl[0]);
+    split_tf32(b1, bh[1], bl[1]);
+    mma_tf32(c, al[0], al[1], al[2], al[3], bh[0], bh[1]);
+    mma_tf32(c, ah[0], ah[1], ah[2], ah[3], bl[0], bl[1]);
+    mma_tf32(c, ah[0], ah[1], ah[2], ah[3], bh[0], bh[1]);
+  }
+}
+
 // Copies R rows of D floats (row r from g + (row0+r)*stride) into smem with pitch D+4;
 // rows at or beyond `T` are zero-filled.
 template <int D, int R, int NT>
@@ -63,7 +89,7 @@ __device__ __forceinline__ void load_tile(float* s, const float* __restrict__ g,
 
 // acc[nt] (16 x 8 each, NT8 tiles) += A[16 rows starting at a_row0 of sA][D] * B^T where
 // B rows are the n index: B[n][k] = sB[(nt*8+n)*P + k]. Both tiles have k contiguous.
-template <int D, int NT8>
+template <int D, int NT8, bool X3>
 __device__ __forceinline__ void mma_ab_t(float (&acc)[NT8][4], const float* sA, int a_row0,
                                          const float* sB, int lane) {
   constexpr int P = D + 4;
@@ -78,7 +104,7 @@ __device__ __forceinline__ void mma_ab_t(float (&acc)[NT8][4], const float* sA, 
     for (int nt = 0; nt < NT8; ++nt) {
       const uint32_t b0 = __float_as_uint(sB[(nt * 8 + g) * P + kk * 8 + t]);
       const uint32_t b1 = __float_as_uint(sB[(nt * 8 + g) * P + kk * 8 + t + 4]);
-      mma_tf32(acc[nt], a0, a1, a2, a3, b0, b1);
+      mma_x<X3>(acc[nt], a0, a1, a2, a3, b0, b1);
     }
   }
 }
@@ -88,22 +114,22 @@ __device__ __forceinline__ void mma_ab_t(float (&acc)[NT8][4], const float* sA, 
 // and B[k][n] = sB[(kt*8+k)*P + n]. The k index inside each 8-wide slice is permuted
 // (slot t <-> column 2t, slot t+4 <-> column 2t+1) on both operands, which leaves the
 // contraction unchanged and needs no register shuffles.
-template <int D, int KT>
+template <int D, int KT, bool X3>
 __device__ __forceinline__ void mma_p_b(float (&acc)[D / 8][4], const float (&p)[KT][4],
                                         const float* sB, int lane) {
   constexpr int P = D + 4;
   const int g = lane >> 2, t = lane & 3;
 #pragma unroll
   for (int kt = 0; kt < KT; ++kt) {
-    const uint32_t a0 = f2tf32(p[kt][0]);
-    const uint32_t a1 = f2tf32(p[kt][2]);
-    const uint32_t a2 = f2tf32(p[kt][1]);
-    const uint32_t a3 = f2tf32(p[kt][3]);
+    const uint32_t a0 = X3 ? __float_as_uint(p[kt][0]) : f2tf32(p[kt][0]);
+    const uint32_t a1 = X3 ? __float_as_uint(p[kt][2]) : f2tf32(p[kt][2]);
+    const uint32_t a2 = X3 ? __float_as_uint(p[kt][1]) : f2tf32(p[kt][1]);
+    const uint32_t a3 = X3 ? __float_as_uint(p[kt][3]) : f2tf32(p[kt][3]);
 #pragma unroll
     for (int nt = 0; nt < D / 8; ++nt) {
       const uint32_t b0 = __float_as_uint(sB[(kt * 8 + 2 * t) * P + nt * 8 + g]);
       const uint32_t b1 = __float_as_uint(sB[(kt * 8 + 2 * t + 1) * P + nt * 8 + g]);
-      mma_tf32(acc[nt], a0, a1, a2, a3, b0, b1);
+      mma_x<X3>(acc[nt], a0, a1, a2, a3, b0, b1);
     }
   }
 }
@@ -111,7 +137,7 @@ __device__ __forceinline__ void mma_p_b(float (&acc)[D / 8][4], const float (&p)
 // ---------------------------------------------------------------------------------------
 // Forward
 // ---------------------------------------------------------------------------------------
-template <int D>
+template <int D, bool X3>
 __global__ void __launch_bounds__(128)
     attn_fwd_kernel(const float* __restrict__ qkv, float* __restrict__ out,
                     float* __restrict__ lse, int T, int H, int Hk, float scale_log2) {
@@ -150,7 +176,7 @@ __global__ void __launch_bounds__(128)
     float s[BKV / 8][4];
 #pragma unroll
     for (int i = 0; i < BKV / 8; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.0f;
-    mma_ab_t<D, BKV / 8>(s, Qs, warp * 16, Ks, lane);
+    mma_ab_t<D, BKV / 8, X3>(s, Qs, warp * 16, Ks, lane);
 
     float mx[2] = {-FLT_MAX, -FLT_MAX};
 #pragma unroll
@@ -201,7 +227,7 @@ __global__ void __launch_bounds__(128)
       o[nt][2] *= corr[1];
       o[nt][3] *= corr[1];
     }
-    mma_p_b<D, BKV / 8>(o, s, Vs, lane);
+    mma_p_b<D, BKV / 8, X3>(o, s, Vs, lane);
   }
 
   const float inv_a = 1.0f / l_run[0], inv_b = 1.0f / l_run[1];
@@ -257,7 +283,7 @@ __global__ void __launch_bounds__(256)
 // ---------------------------------------------------------------------------------------
 // Backward, dQ:  dS = P*(dP - delta)*scale, dQ = dS K
 // ---------------------------------------------------------------------------------------
-template <int D>
+template <int D, bool X3>
 __global__ void __launch_bounds__(128)
     attn_bwd_dq_kernel(const float* __restrict__ qkv, const float* __restrict__ dout,
                        const float* __restrict__ lse, const float* __restrict__ delta,
@@ -311,8 +337,8 @@ __global__ void __launch_bounds__(128)
       s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.0f;
       dp[i][0] = dp[i][1] = dp[i][2] = dp[i][3] = 0.0f;
     }
-    mma_ab_t<D, BKV / 8>(s, Qs, warp * 16, Ks, lane);
-    mma_ab_t<D, BKV / 8>(dp, dOs, warp * 16, Vs, lane);
+    mma_ab_t<D, BKV / 8, X3>(s, Qs, warp * 16, Ks, lane);
+    mma_ab_t<D, BKV / 8, X3>(dp, dOs, warp * 16, Vs, lane);
 #pragma unroll
     for (int nt = 0; nt < BKV / 8; ++nt) {
 #pragma unroll
@@ -325,7 +351,7 @@ __global__ void __launch_bounds__(128)
         s[nt][e] = pv * (dp[nt][e] - dl) * scale;
       }
     }
-    mma_p_b<D, BKV / 8>(dq, s, Ks, lane);
+    mma_p_b<D, BKV / 8, X3>(dq, s, Ks, lane);
   }
 
   if (row_a < T) {
@@ -349,7 +375,7 @@ __global__ void __launch_bounds__(128)
 //   dS^T = P^T*(dP^T - delta[q])*scale, dV += P^T dO, dK += dS^T Q.
 // QT = queries per inner tile (64 for D=64, 32 for D=128 to bound registers).
 // ---------------------------------------------------------------------------------------
-template <int D, int QT>
+template <int D, int QT, bool X3>
 __global__ void __launch_bounds__(128)
     attn_bwd_dkv_kernel(const float* __restrict__ qkv, const float* __restrict__ dout,
                         const float* __restrict__ lse, const float* __restrict__ delta,
@@ -412,8 +438,8 @@ __global__ void __launch_bounds__(128)
         st[i][0] = st[i][1] = st[i][2] = st[i][3] = 0.0f;
         dpt[i][0] = dpt[i][1] = dpt[i][2] = dpt[i][3] = 0.0f;
       }
-      mma_ab_t<D, QT / 8>(st, Ks, warp * 16, Qs, lane);
-      mma_ab_t<D, QT / 8>(dpt, Vs, warp * 16, dOs, lane);
+      mma_ab_t<D, QT / 8, X3>(st, Ks, warp * 16, Qs, lane);
+      mma_ab_t<D, QT / 8, X3>(dpt, Vs, warp * 16, dOs, lane);
       float pt[QT / 8][4];
 #pragma unroll
       for (int nt = 0; nt < QT / 8; ++nt) {
@@ -427,8 +453,8 @@ __global__ void __launch_bounds__(128)
           st[nt][e] = pv * (dpt[nt][e] - s_del[ql]) * scale;
         }
       }
-      mma_p_b<D, QT / 8>(dv, pt, dOs, lane);
-      mma_p_b<D, QT / 8>(dk, st, Qs, lane);
+      mma_p_b<D, QT / 8, X3>(dv, pt, dOs, lane);
+      mma_p_b<D, QT / 8, X3>(dk, st, Qs, lane);
     }
   }
 
@@ -473,6 +499,43 @@ int check_attn_args(const char* name, int64_t B, int64_t T, int H, int Hk, int D
   return CTDK_OK;
 }
 
+template <int D, bool X3>
+int run_fwd_legacy(const float* qkv, float* out, float* lse, int64_t B, int64_t T, int H, int Hk, cudaStream_t s) {
+  const float scale_log2 = (1.0f / sqrtf(static_cast<float>(D))) * kLog2e;
+  dim3 grid(static_cast<unsigned>((T + BQ - 1) / BQ), static_cast<unsigned>(H), static_cast<unsigned>(B));
+  const int smem = (BQ + 2 * BKV) * (D + 4) * static_cast<int>(sizeof(float));
+  int rc = set_smem(attn_fwd_kernel<D, X3>, smem, "ctdk_attn_fwd");
+  if (rc != CTDK_OK) return rc;
+  attn_fwd_kernel<D, X3><<<grid, 128, smem, s>>>(qkv, out, lse, static_cast<int>(T), H, Hk, scale_log2);
+  return check_launch("ctdk_attn_fwd");
+}
+
+template <int D, int QT, bool X3>
+int run_bwd_legacy(const float* qkv, const float* dout, const float* lse, const float* delta, float* dqkv,
+                   int64_t B, int64_t T, int H, int Hk, bool do_dq, bool do_dkv, cudaStream_t s) {
+  const float scale = 1.0f / sqrtf(static_cast<float>(D));
+  const int Ti = static_cast<int>(T);
+  dim3 gq(static_cast<unsigned>((T + BQ - 1) / BQ), static_cast<unsigned>(H), static_cast<unsigned>(B));
+  dim3 gk(static_cast<unsigned>((T + BKV - 1) / BKV), static_cast<unsigned>(Hk), static_cast<unsigned>(B));
+  const int smem_q = (2 * BQ + 2 * BKV) * (D + 4) * static_cast<int>(sizeof(float));
+  const int smem_k = ((2 * BKV + 2 * QT) * (D + 4) + 2 * QT) * static_cast<int>(sizeof(float));
+  int rc = CTDK_OK;
+  if (do_dq) {
+    rc = set_smem(attn_bwd_dq_kernel<D, X3>, smem_q, "ctdk_attn_bwd");
+    if (rc != CTDK_OK) return rc;
+    attn_bwd_dq_kernel<D, X3><<<gq, 128, smem_q, s>>>(qkv, dout, lse, delta, dqkv, Ti, H, Hk, scale);
+    rc = check_launch("ctdk_attn_bwd(dq)");
+    if (rc != CTDK_OK) return rc;
+  }
+  if (do_dkv) {
+    rc = set_smem(attn_bwd_dkv_kernel<D, QT, X3>, smem_k, "ctdk_attn_bwd");
+    if (rc != CTDK_OK) return rc;
+    attn_bwd_dkv_kernel<D, QT, X3><<<gk, 128, smem_k, s>>>(qkv, dout, lse, delta, dqkv, Ti, H, Hk, scale);
+    rc = check_launch("ctdk_attn_bwd(dkv)");
+  }
+  return rc;
+}
+
 }  // namespace
 }  // namespace ctdk
 
@@ -480,117 +543,82 @@ using namespace ctdk;
 
 extern "C" {
 
-int ctdk_attn_fwd(const float* qkv, float* out, float* lse, int64_t B, int64_t T, int H,
-                  int Hk, int D, void* stream) {
+int ctdk_attn_fwd_p(const float* qkv, float* out, float* lse, int64_t B, int64_t T, int H, int Hk, int D,
+                    int precision, void* stream) {
   int rc = check_attn_args("ctdk_attn_fwd", B, T, H, Hk, D);
   if (rc != CTDK_OK) return rc;
+  CTDK_REQUIRE(precision == CTDK_GEMM_TF32 || precision == CTDK_GEMM_3XTF32, "ctdk_attn_fwd: unknown precision");
   if (B == 0 || T == 0) return CTDK_OK;
   CTDK_REQUIRE(qkv && out && lse, "ctdk_attn_fwd: null pointer");
-  CTDK_REQUIRE((reinterpret_cast<uintptr_t>(qkv) & 15u) == 0 &&
-                   (reinterpret_cast<uintptr_t>(out) & 7u) == 0,
+  CTDK_REQUIRE((reinterpret_cast<uintptr_t>(qkv) & 15u) == 0 && (reinterpret_cast<uintptr_t>(out) & 7u) == 0,
                "ctdk_attn_fwd: qkv must be 16-byte aligned, out 8-byte aligned");
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  const float scale_log2 = (1.0f / sqrtf(static_cast<float>(D))) * kLog2e;
-  dim3 grid(static_cast<unsigned>((T + BQ - 1) / BQ), static_cast<unsigned>(H),
-            static_cast<unsigned>(B));
-  const int smem = (BQ + 2 * BKV) * (D + 4) * static_cast<int>(sizeof(float));
+  const bool x3 = precision == CTDK_GEMM_3XTF32;
   // causal half of 2 GEMMs: 2 * (2*T*T*D)/2 per (batch, head)
   void* tok = prof_begin(CTDK_PROF_ATTN, 2.0 * B * H * static_cast<double>(T) * T * D, s);
-  if (!attn_use_legacy()) {
+  if (!x3 && !attn_use_legacy()) {
     rc = attn_fwd_tcgen05(qkv, out, lse, B, T, H, Hk, D, s);
     if (rc <= 0) {
       prof_end(tok, s);
       return rc;
     }
   }
-  if (D == 64) {
-    rc = set_smem(attn_fwd_kernel<64>, smem, "ctdk_attn_fwd");
-    if (rc != CTDK_OK) return rc;
-    attn_fwd_kernel<64><<<grid, 128, smem, s>>>(qkv, out, lse, static_cast<int>(T), H, Hk,
-                                               scale_log2);
-  } else {
-    rc = set_smem(attn_fwd_kernel<128>, smem, "ctdk_attn_fwd");
-    if (rc != CTDK_OK) return rc;
-    attn_fwd_kernel<128><<<grid, 128, smem, s>>>(qkv, out, lse, static_cast<int>(T), H, Hk,
-                                                scale_log2);
-  }
+  if (D == 64) rc = x3 ? run_fwd_legacy<64, true>(qkv, out, lse, B, T, H, Hk, s) : run_fwd_legacy<64, false>(qkv, out, lse, B, T, H, Hk, s);
+  else rc = x3 ? run_fwd_legacy<128, true>(qkv, out, lse, B, T, H, Hk, s) : run_fwd_legacy<128, false>(qkv, out, lse, B, T, H, Hk, s);
   prof_end(tok, s);
-  return check_launch("ctdk_attn_fwd");
+  return rc;
 }
 
-int ctdk_attn_bwd(const float* qkv, const float* out, const float* dout, const float* lse,
-                  float* delta, float* dqkv, int64_t B, int64_t T, int H, int Hk, int D,
+int ctdk_attn_fwd(const float* qkv, float* out, float* lse, int64_t B, int64_t T, int H, int Hk, int D,
                   void* stream) {
+  return ctdk_attn_fwd_p(qkv, out, lse, B, T, H, Hk, D, CTDK_GEMM_TF32, stream);
+}
+
+int ctdk_attn_bwd_p(const float* qkv, const float* out, const float* dout, const float* lse, float* delta,
+                    float* dqkv, int64_t B, int64_t T, int H, int Hk, int D, int precision, void* stream) {
   int rc = check_attn_args("ctdk_attn_bwd", B, T, H, Hk, D);
   if (rc != CTDK_OK) return rc;
+  CTDK_REQUIRE(precision == CTDK_GEMM_TF32 || precision == CTDK_GEMM_3XTF32, "ctdk_attn_bwd: unknown precision");
   if (B == 0 || T == 0) return CTDK_OK;
   CTDK_REQUIRE(qkv && out && dout && lse && delta && dqkv, "ctdk_attn_bwd: null pointer");
-  CTDK_REQUIRE((reinterpret_cast<uintptr_t>(qkv) & 15u) == 0 &&
-                   (reinterpret_cast<uintptr_t>(out) & 15u) == 0 &&
-                   (reinterpret_cast<uintptr_t>(dout) & 15u) == 0 &&
-                   (reinterpret_cast<uintptr_t>(dqkv) & 7u) == 0,
+  CTDK_REQUIRE((reinterpret_cast<uintptr_t>(qkv) & 15u) == 0 && (reinterpret_cast<uintptr_t>(out) & 15u) == 0 &&
+                   (reinterpret_cast<uintptr_t>(dout) & 15u) == 0 && (reinterpret_cast<uintptr_t>(dqkv) & 7u) == 0,
                "ctdk_attn_bwd: qkv/out/dout must be 16-byte aligned");
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  const int Ti = static_cast<int>(T);
-  const float scale = 1.0f / sqrtf(static_cast<float>(D));
-
+  const bool x3 = precision == CTDK_GEMM_3XTF32;
   // backward = 2x the forward's algorithmic FLOPs (recomputation is not counted)
   void* tok = prof_begin(CTDK_PROF_ATTN, 4.0 * B * H * static_cast<double>(T) * T * D, s);
   const int64_t items = B * T * H;
   const int64_t cap = static_cast<int64_t>(sm_count()) * 8;
   const int64_t need = (items + 7) / 8;
-  attn_delta_kernel<<<static_cast<int>(need < cap ? need : cap), 256, 0, s>>>(out, dout, delta,
-                                                                             B, Ti, H, D);
+  attn_delta_kernel<<<static_cast<int>(need < cap ? need : cap), 256, 0, s>>>(out, dout, delta, B,
+                                                                             static_cast<int>(T), H, D);
   rc = check_launch("ctdk_attn_bwd(delta)");
   if (rc != CTDK_OK) return rc;
-
-  dim3 gq(static_cast<unsigned>((T + BQ - 1) / BQ), static_cast<unsigned>(H),
-          static_cast<unsigned>(B));
-  dim3 gk(static_cast<unsigned>((T + BKV - 1) / BKV), static_cast<unsigned>(Hk),
-          static_cast<unsigned>(B));
-  const int smem_q = (2 * BQ + 2 * BKV) * (D + 4) * static_cast<int>(sizeof(float));
   // tcgen05 kernels first; each returns 1 when it does not take the shape.
   int dq_done = 1, dkv_done = 1;
-  if (!attn_use_legacy()) {
+  if (!x3 && !attn_use_legacy()) {
     dq_done = attn_bwd_dq_tcgen05(qkv, dout, lse, delta, dqkv, B, T, H, Hk, D, s);
     if (dq_done < 0) return dq_done;
     dkv_done = attn_bwd_dkv_tcgen05(qkv, dout, lse, delta, dqkv, B, T, H, Hk, D, s);
     if (dkv_done < 0) return dkv_done;
   }
-  if (D == 64) {
-    constexpr int QT = 64;
-    const int smem_k = ((2 * BKV + 2 * QT) * (64 + 4) + 2 * QT) * static_cast<int>(sizeof(float));
-    if (dq_done == 1) {
-      rc = set_smem(attn_bwd_dq_kernel<64>, smem_q, "ctdk_attn_bwd");
-      if (rc != CTDK_OK) return rc;
-      attn_bwd_dq_kernel<64><<<gq, 128, smem_q, s>>>(qkv, dout, lse, delta, dqkv, Ti, H, Hk, scale);
-      rc = check_launch("ctdk_attn_bwd(dq)");
-      if (rc != CTDK_OK) return rc;
-    }
-    if (dkv_done == 1) {
-      rc = set_smem(attn_bwd_dkv_kernel<64, QT>, smem_k, "ctdk_attn_bwd");
-      if (rc != CTDK_OK) return rc;
-      attn_bwd_dkv_kernel<64, QT><<<gk, 128, smem_k, s>>>(qkv, dout, lse, delta, dqkv, Ti, H, Hk, scale);
-    }
-  } else {
-    constexpr int QT = 32;
-    const int smem_k =
-        ((2 * BKV + 2 * QT) * (128 + 4) + 2 * QT) * static_cast<int>(sizeof(float));
-    if (dq_done == 1) {
-      rc = set_smem(attn_bwd_dq_kernel<128>, smem_q, "ctdk_attn_bwd");
-      if (rc != CTDK_OK) return rc;
-      attn_bwd_dq_kernel<128><<<gq, 128, smem_q, s>>>(qkv, dout, lse, delta, dqkv, Ti, H, Hk, scale);
-      rc = check_launch("ctdk_attn_bwd(dq)");
-      if (rc != CTDK_OK) return rc;
-    }
-    if (dkv_done == 1) {
-      rc = set_smem(attn_bwd_dkv_kernel<128, QT>, smem_k, "ctdk_attn_bwd");
-      if (rc != CTDK_OK) return rc;
-      attn_bwd_dkv_kernel<128, QT><<<gk, 128, smem_k, s>>>(qkv, dout, lse, delta, dqkv, Ti, H, Hk, scale);
-    }
+  const bool dq = dq_done == 1, dkv = dkv_done == 1;
+  if (dq || dkv) {
+    if (D == 64)
+      rc = x3 ? run_bwd_legacy<64, 64, true>(qkv, dout, lse, delta, dqkv, B, T, H, Hk, dq, dkv, s)
+              : run_bwd_legacy<64, 64, false>(qkv, dout, lse, delta, dqkv, B, T, H, Hk, dq, dkv, s);
+    else
+      rc = x3 ? run_bwd_legacy<128, 32, true>(qkv, dout, lse, delta, dqkv, B, T, H, Hk, dq, dkv, s)
+              : run_bwd_legacy<128, 32, false>(qkv, dout, lse, delta, dqkv, B, T, H, Hk, dq, dkv, s);
   }
   prof_end(tok, s);
-  return check_launch("ctdk_attn_bwd(dkv)");
+  return rc;
+}
+
+int ctdk_attn_bwd(const float* qkv, const float* out, const float* dout, const float* lse, float* delta,
+                  float* dqkv, int64_t B, int64_t T, int H, int Hk, int D, void* stream) {
+  return ctdk_attn_bwd_p(qkv, out, dout, lse, delta, dqkv, B, T, H, Hk, D, CTDK_GEMM_TF32, stream);
 }
 
 }  // extern "C"

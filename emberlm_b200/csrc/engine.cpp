@@ -128,6 +128,8 @@ struct Engine {
   std::vector<LayerActs> acts;    // L entries (all alias entry 0 when checkpointing)
   float *hf, *dh, *dtmp, *dgu, *dact, *dqkv, *dattn, *delta, *norm_scratch, *qk_scratch;
   float* logits;
+  float* ws3 = nullptr;       // operand-split workspace of the 3xTF32 GEMMs
+  int64_t ws3_floats = 0;
   ctdk_layer_callback cb = nullptr;
   void* cb_user = nullptr;
 };
@@ -183,6 +185,27 @@ void carve(Engine& e, Bump& b) {
   e.norm_scratch = b.floats(ctdk_rmsnorm_bwd_scratch_floats(static_cast<int>(hid)));
   e.qk_scratch = b.floats(ctdk_qk_norm_rope_bwd_scratch_floats(static_cast<int>(D)));
   e.logits = b.floats(e.head_rows * c.vocab_size);
+  if (c.precision == CTDK_GEMM_3XTF32) {
+    // largest M*K + K*N over every GEMM (M, N, K) of a step: forward, dX and dW of the four
+    // projections of a layer, and the three GEMMs of an LM-head block
+    const int64_t V = c.vocab_size, HD = H * D, QN = e.QKVN, R = e.head_rows;
+    const int64_t proj[4][2] = {{QN, hid}, {hid, HD}, {2 * I, hid}, {hid, I}};  // {N_out, K_in}
+    int64_t mx = 0;
+    auto need = [&](int64_t M, int64_t N, int64_t K) {
+      const int64_t v = M * K + K * N;
+      mx = v > mx ? v : mx;
+    };
+    for (const auto& p : proj) {
+      need(tok, p[0], p[1]);   // Y  = X W^T
+      need(tok, p[1], p[0]);   // dX = dY W
+      need(p[0], p[1], tok);   // dW = dY^T X
+    }
+    need(R, V, hid);
+    need(R, hid, V);
+    need(V, hid, R);
+    e.ws3_floats = 2 * mx + 128;
+    e.ws3 = b.floats(e.ws3_floats);
+  }
 }
 
 void init_engine_shape(Engine& e, const ctdk_model_config& c, int64_t B, int64_t T) {
@@ -214,6 +237,8 @@ ctdk_rope_params rope_params(const ctdk_model_config& c) {
 int gemm(const Engine& e, const float* A, const float* B, float* C, int64_t M, int64_t N,
          int64_t K, int ta, int tb, int epi, const float* aux, void* s) {
   const int64_t lda = ta ? M : K, ldb = tb ? K : N;
+  if (e.cfg.precision == CTDK_GEMM_3XTF32)
+    return ctdk_gemm_ws(A, B, C, M, N, K, lda, ldb, N, ta, tb, CTDK_GEMM_3XTF32, epi, aux, e.ws3, e.ws3_floats, s);
   return ctdk_gemm(A, B, C, M, N, K, lda, ldb, N, ta, tb, e.cfg.precision, epi, aux, s);
 }
 
@@ -231,7 +256,7 @@ int layer_forward(Engine& e, int l, int64_t B, int64_t T, void* s) {
   TRY(ctdk_qk_norm_rope_fwd(a.qkv_pre, a.qkv, c.qk_norm ? P + w.wqn : nullptr,
                             c.qk_norm ? P + w.wkn : nullptr, a.rstd_q, a.rstd_k, e.rope_table, B,
                             T, H, Hk, D, c.rms_norm_eps, s));
-  TRY(ctdk_attn_fwd(a.qkv, a.attn, a.lse, B, T, H, Hk, D, s));
+  TRY(ctdk_attn_fwd_p(a.qkv, a.attn, a.lse, B, T, H, Hk, D, c.precision, s));
   TRY(gemm(e, a.attn, P + w.wo, a.hm, tok, hid, static_cast<int64_t>(H) * D, 0, 1,
            CTDK_EPI_RESIDUAL, x, s));
   TRY(ctdk_rmsnorm_fwd(a.hm, P + w.w_post, a.h2, nullptr, tok, static_cast<int>(hid),
@@ -265,7 +290,7 @@ int layer_backward(Engine& e, int l, int64_t B, int64_t T, int accumulate, void*
   // attention: hm = x + attn Wo^T
   TRY(gemm(e, e.dh, P + w.wo, e.dattn, tok, HD, hid, 0, 0, CTDK_EPI_STORE, nullptr, s));
   TRY(gemm(e, e.dh, a.attn, G + w.wo, hid, HD, tok, 1, 0, wepi, nullptr, s));
-  TRY(ctdk_attn_bwd(a.qkv, a.attn, e.dattn, a.lse, e.delta, e.dqkv, B, T, H, Hk, D, s));
+  TRY(ctdk_attn_bwd_p(a.qkv, a.attn, e.dattn, a.lse, e.delta, e.dqkv, B, T, H, Hk, D, c.precision, s));
   TRY(ctdk_qk_norm_rope_bwd(e.dqkv, a.qkv_pre, c.qk_norm ? P + w.wqn : nullptr,
                             c.qk_norm ? P + w.wkn : nullptr, a.rstd_q, a.rstd_k,
                             c.qk_norm ? G + w.wqn : nullptr, c.qk_norm ? G + w.wkn : nullptr,

@@ -72,6 +72,28 @@ __global__ void __launch_bounds__(256)
   }
 }
 
+// hi = x rounded to TF32 (10-bit mantissa, round to nearest), lo = x - hi (exact in fp32).
+__global__ void __launch_bounds__(256) split_tf32_kernel(const float* __restrict__ x, float* __restrict__ hi,
+                                                         float* __restrict__ lo, int64_t n4) {
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  auto sp = [](float v, float& h, float& l) {
+    uint32_t r;
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(v));
+    h = __uint_as_float(r);
+    l = v - h;
+  };
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n4; i += stride) {
+    const float4 v = reinterpret_cast<const float4*>(x)[i];
+    float4 h, l;
+    sp(v.x, h.x, l.x);
+    sp(v.y, h.y, l.y);
+    sp(v.z, h.z, l.z);
+    sp(v.w, h.w, l.w);
+    reinterpret_cast<float4*>(hi)[i] = h;
+    reinterpret_cast<float4*>(lo)[i] = l;
+  }
+}
+
 __global__ void fill_rows_kernel(float* C, const float* aux, int64_t M, int64_t N, int64_t ldc,
                                  int epilogue) {
   const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
@@ -130,6 +152,50 @@ int ctdk_gemm(const float* A, const float* B, float* C, int64_t M, int64_t N, in
                                         epilogue);
   prof_end(tok, s);
   return check_launch("ctdk_gemm(simt)");
+}
+
+int64_t ctdk_gemm_3xtf32_workspace_floats(int64_t M, int64_t N, int64_t K) {
+  if (M < 0 || N < 0 || K < 0) return -1;
+  return 2 * (M * K + K * N) + 64;
+}
+
+int ctdk_gemm_ws(const float* A, const float* B, float* C, int64_t M, int64_t N, int64_t K,
+                 int64_t lda, int64_t ldb, int64_t ldc, int transa, int transb, int precision,
+                 int epilogue, const float* aux, float* workspace, int64_t workspace_floats,
+                 void* stream) {
+  const bool dense = lda == (transa ? M : K) && ldb == (transb ? K : N);
+  const bool aligned = ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B) |
+                         reinterpret_cast<uintptr_t>(workspace)) & 15u) == 0 &&
+                       ((M * K) % 4 == 0) && ((K * N) % 4 == 0) && (lda % 4 == 0) && (ldb % 4 == 0);
+  if (precision != CTDK_GEMM_3XTF32 || workspace == nullptr || !dense || !aligned || M == 0 || N == 0 ||
+      K == 0 || N < 8)
+    return ctdk_gemm(A, B, C, M, N, K, lda, ldb, ldc, transa, transb, precision, epilogue, aux, stream);
+  CTDK_REQUIRE(workspace_floats >= ctdk_gemm_3xtf32_workspace_floats(M, N, K),
+               "ctdk_gemm_ws: workspace too small for the 3xTF32 split");
+  // a = a_hi + a_lo, b = b_hi + b_lo with hi exactly representable in TF32:
+  // a*b = a_hi*b_hi + a_hi*b_lo + a_lo*b_hi (+ a_lo*b_lo, below fp32 resolution and dropped).
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int64_t na = M * K, nb = K * N;
+  auto up = [](int64_t v) { return (v + 15) / 16 * 16; };
+  float* a_hi = workspace;
+  float* a_lo = a_hi + up(na);
+  float* b_hi = a_lo + up(na);
+  float* b_lo = b_hi + up(nb);
+  const int cap = sm_count() * 8;
+  auto blocks = [&](int64_t n4) { return static_cast<int>(n4 / 256 + 1 < cap ? n4 / 256 + 1 : cap); };
+  split_tf32_kernel<<<blocks(na / 4), 256, 0, s>>>(A, a_hi, a_lo, na / 4);
+  int rc = check_launch("ctdk_gemm_ws(split A)");
+  if (rc != CTDK_OK) return rc;
+  split_tf32_kernel<<<blocks(nb / 4), 256, 0, s>>>(B, b_hi, b_lo, nb / 4);
+  rc = check_launch("ctdk_gemm_ws(split B)");
+  if (rc != CTDK_OK) return rc;
+  rc = ctdk_gemm(a_hi, b_hi, C, M, N, K, lda, ldb, ldc, transa, transb, CTDK_GEMM_TF32, epilogue, aux, stream);
+  if (rc != CTDK_OK) return rc;
+  rc = ctdk_gemm(a_hi, b_lo, C, M, N, K, lda, ldb, ldc, transa, transb, CTDK_GEMM_TF32, CTDK_EPI_ACCUMULATE,
+                 nullptr, stream);
+  if (rc != CTDK_OK) return rc;
+  return ctdk_gemm(a_lo, b_hi, C, M, N, K, lda, ldb, ldc, transa, transb, CTDK_GEMM_TF32, CTDK_EPI_ACCUMULATE,
+                   nullptr, stream);
 }
 
 int ctdk_bmm(const float* A, const float* B, float* C, int64_t batch, int64_t M, int64_t N,

@@ -51,6 +51,9 @@ _lib = load()
 _p, _i, _l, _f = C.c_void_p, C.c_int, C.c_int64, C.c_float
 _SIGS = {
     "ctdk_gemm": [_p, _p, _p, _l, _l, _l, _l, _l, _l, _i, _i, _i, _i, _p, _p],
+    "ctdk_gemm_ws": [_p, _p, _p, _l, _l, _l, _l, _l, _l, _i, _i, _i, _i, _p, _p, _l, _p],
+    "ctdk_attn_fwd_p": [_p, _p, _p, _l, _l, _i, _i, _i, _i, _p],
+    "ctdk_attn_bwd_p": [_p, _p, _p, _p, _p, _p, _l, _l, _i, _i, _i, _i, _p],
     "ctdk_bmm": [_p, _p, _p, _l, _l, _l, _l, _i, _i, _i, _p],
     "ctdk_rmsnorm_fwd": [_p, _p, _p, _p, _l, _i, _f, _p],
     "ctdk_rmsnorm_bwd": [_p, _p, _p, _p, _p, _p, _l, _i, _f, _i, _i, _p],
@@ -93,6 +96,8 @@ _lib.ctdk_prof_collect.argtypes = [C.c_int, C.POINTER(C.c_double), C.POINTER(C.c
                                    C.POINTER(C.c_longlong)]
 _lib.ctdk_rmsnorm_bwd_scratch_floats.restype = C.c_int64
 _lib.ctdk_rmsnorm_bwd_scratch_floats.argtypes = [C.c_int]
+_lib.ctdk_gemm_3xtf32_workspace_floats.restype = C.c_int64
+_lib.ctdk_gemm_3xtf32_workspace_floats.argtypes = [C.c_int64, C.c_int64, C.c_int64]
 _lib.ctdk_qk_norm_rope_bwd_scratch_floats.restype = C.c_int64
 _lib.ctdk_qk_norm_rope_bwd_scratch_floats.argtypes = [C.c_int]
 

@@ -92,6 +92,13 @@ def matmul(a, b, transa=False, transb=False, precision=lib.GEMM_TF32, out=None, 
         raise RuntimeError("matmul: inner dims disagree")
     if out is None:
         out = torch.empty(M, N, device=a.device, dtype=a.dtype)
+    if precision == lib.GEMM_3XTF32:
+        # near-fp32 on the tensor cores: three passes over split operands, needs a workspace
+        ws = torch.empty(lib.raw().ctdk_gemm_3xtf32_workspace_floats(M, N, K), device=a.device, dtype=a.dtype)
+        lib.call("ctdk_gemm_ws", a.data_ptr(), b.data_ptr(), out.data_ptr(), M, N, K, a.shape[1], b.shape[1], N,
+                 int(transa), int(transb), precision, epilogue, aux.data_ptr() if aux is not None else None,
+                 ws.data_ptr(), ws.numel(), _s())
+        return out
     lib.call("ctdk_gemm", a.data_ptr(), b.data_ptr(), out.data_ptr(), M, N, K, a.shape[1], b.shape[1], N,
              int(transa), int(transb), precision, epilogue, aux.data_ptr() if aux is not None else None, _s())
     return out
@@ -229,19 +236,19 @@ def cross_entropy_masked(logits, targets, loss_mask, dy=1.0, want_dlogits=True):
     return loss, (work if want_dlogits else None), sums[1]
 
 
-def attention(qkv, B, T, H, Hk, D):
+def attention(qkv, B, T, H, Hk, D, precision=lib.GEMM_TF32):
     _chk(qkv, "attention")
     out = torch.empty(B * T, H * D, device=qkv.device)
     lse = torch.empty(B, H, T, device=qkv.device)
-    lib.call("ctdk_attn_fwd", qkv.data_ptr(), out.data_ptr(), lse.data_ptr(), B, T, H, Hk, D, _s())
+    lib.call("ctdk_attn_fwd_p", qkv.data_ptr(), out.data_ptr(), lse.data_ptr(), B, T, H, Hk, D, precision, _s())
     return out, lse
 
 
-def attention_backward(qkv, out, dout, lse, B, T, H, Hk, D):
+def attention_backward(qkv, out, dout, lse, B, T, H, Hk, D, precision=lib.GEMM_TF32):
     dqkv = torch.empty_like(qkv)
     delta = torch.empty(B, H, T, device=qkv.device)
-    lib.call("ctdk_attn_bwd", qkv.data_ptr(), out.data_ptr(), dout.data_ptr(), lse.data_ptr(),
-             delta.data_ptr(), dqkv.data_ptr(), B, T, H, Hk, D, _s())
+    lib.call("ctdk_attn_bwd_p", qkv.data_ptr(), out.data_ptr(), dout.data_ptr(), lse.data_ptr(),
+             delta.data_ptr(), dqkv.data_ptr(), B, T, H, Hk, D, precision, _s())
     return dqkv
 
 

@@ -66,6 +66,18 @@ int ctdk_gemm(const float* A, const float* B, float* C, int64_t M, int64_t N, in
               int64_t lda, int64_t ldb, int64_t ldc, int transa, int transb, int precision,
               int epilogue, const float* aux, void* stream);
 
+/* Same as ctdk_gemm with a caller-provided workspace, which CTDK_GEMM_3XTF32 needs to run on the
+ * tensor cores: both operands are split into a TF32-exact high part and an fp32 remainder and
+ * C = A_hi B_hi + A_hi B_lo + A_lo B_hi is accumulated in three tensor-core passes (relative
+ * error ~1e-6, i.e. near the reference's fp32 cublasSgemm). Needs dense operands (leading
+ * dimensions equal to the row lengths); otherwise, or without a workspace, behaves as ctdk_gemm
+ * (where CTDK_GEMM_3XTF32 selects the exact-fp32 SIMT kernel). */
+int64_t ctdk_gemm_3xtf32_workspace_floats(int64_t M, int64_t N, int64_t K);
+int ctdk_gemm_ws(const float* A, const float* B, float* C, int64_t M, int64_t N, int64_t K,
+                 int64_t lda, int64_t ldb, int64_t ldc, int transa, int transb, int precision,
+                 int epilogue, const float* aux, float* workspace, int64_t workspace_floats,
+                 void* stream);
+
 /* Batched variant with full-matrix strides, as cublasSgemmStridedBatched in
  * ops::bmm_impl (src/ops/matmul.cpp:51-93). */
 int ctdk_bmm(const float* A, const float* B, float* C, int64_t batch, int64_t M, int64_t N,
@@ -202,6 +214,14 @@ int ctdk_attn_fwd(const float* qkv, float* out, float* lse, int64_t B, int64_t T
 int ctdk_attn_bwd(const float* qkv, const float* out, const float* dout, const float* lse,
                   float* delta, float* dqkv, int64_t B, int64_t T, int H, int Hk, int D,
                   void* stream);
+/* Same with a precision: CTDK_GEMM_TF32 (what the plain entry points use) or CTDK_GEMM_3XTF32,
+ * which splits every operand of every contraction into TF32 high and low parts (three tensor-core
+ * products per product) for results close to the reference's fp32 bmm. */
+int ctdk_attn_fwd_p(const float* qkv, float* out, float* lse, int64_t B, int64_t T, int H,
+                    int Hk, int D, int precision, void* stream);
+int ctdk_attn_bwd_p(const float* qkv, const float* out, const float* dout, const float* lse,
+                    float* delta, float* dqkv, int64_t B, int64_t T, int H, int Hk, int D,
+                    int precision, void* stream);
 
 /* ------------------------------------------------------------------------------------
  * Optimizer. ctdk_sumsq adds sum(g^2) into out[0] (sum_sq_kernel_f32,

@@ -72,7 +72,8 @@ def test_engine_matches_committed_reference_outputs(name):
 
 
 @pytest.mark.skipif(not ref_run.available(), reason="oracle/_ref/ref_harness not built")
-def test_full_size_smollm2_135m_step_matches_reference():
+@pytest.mark.parametrize("mode", ["tf32", "3xtf32"])
+def test_full_size_smollm2_135m_step_matches_reference(mode):
     """BASELINE config 1 at full size (SmolLM2-135M shape, 4 rows x 512 tokens, one micro-batch):
     one optimizer step of the engine against the reference's CUDA build on the same bytes.
     Stated tolerances (TF32 mode): loss rel <= 1e-3, per-tensor gradient and updated-weight
@@ -84,7 +85,10 @@ def test_full_size_smollm2_135m_step_matches_reference():
     tok, msk = om.synth_batch(cfg.vocab_size, 4, 512, seed=4321)
     hp = dict(lr=1e-4, beta1=0.9, beta2=0.999, eps=1e-8, weight_decay=0.01, clip=1.0)
     ref = ref_run.run_reference(cfg, params, tok, msk, 4, 1, steps=1, warmup=0, **hp)
-    eng = E.TrainEngine(E.make_config(**E.PRESETS["smollm2_135m"]), 4, 511, **hp)
+    from emberlm_b200 import lib
+    prec = lib.GEMM_3XTF32 if mode == "3xtf32" else lib.GEMM_TF32
+    tol = 1e-4 if mode == "3xtf32" else 1e-2
+    eng = E.TrainEngine(E.make_config(**E.PRESETS["smollm2_135m"], precision=prec), 4, 511, **hp)
     eng.load_parameters(params)
     ids, tgt, m = om.make_batch(tok, msk, [0, 1, 2, 3])
     d_m = torch.from_numpy(m).cuda()
@@ -101,9 +105,13 @@ def test_full_size_smollm2_135m_step_matches_reference():
     for k, v in eng.named_parameters().items():
         e = tensor_err(v.cpu().numpy(), ref["params"][k])
         worst_p = max(worst_p, (k, e), key=lambda t: t[1])
-    print(f"loss {met['loss']:.6f} vs {ref['loss'][0]:.6f}; grad_norm {met['grad_norm']:.5f} vs "
+    print(f"[{mode}] loss {met['loss']:.6f} vs {ref['loss'][0]:.6f}; grad_norm {met['grad_norm']:.5f} vs "
           f"{ref['grad_norm'][0]:.5f}; worst grad {worst_g}; worst weight {worst_p}")
     assert abs(met["loss"] - ref["loss"][0]) <= 1e-3 * abs(ref["loss"][0])
     assert abs(met["grad_norm"] - ref["grad_norm"][0]) <= 1e-2 * ref["grad_norm"][0]
-    assert worst_g[1] <= 1e-2, worst_g
-    assert worst_p[1] <= 1e-2, worst_p
+    assert worst_g[1] <= tol, worst_g
+    # AdamW's first step is sign-like (m_hat/sqrt(v_hat) = g/|g|): an element whose gradient is at
+    # rounding-noise level can land on the other side of zero in either implementation and then
+    # differs by 2*lr, whatever the precision of the contractions. The weight bound is therefore the
+    # stated tolerance or 2*lr relative to the largest weight, whichever is larger.
+    assert worst_p[1] <= max(tol, 2.5 * hp["lr"] / 0.09), worst_p
