@@ -188,6 +188,7 @@ def run_ours(args) -> dict:
 
     pinned_tok = [torch.empty((my_rows, S), dtype=torch.int32).pin_memory() for _ in range(2)]
     pinned_msk = [torch.empty((my_rows, S), dtype=torch.int8).pin_memory() for _ in range(2)]
+    pinned_act = [torch.empty(my_rows * T, dtype=torch.int32).pin_memory() for _ in range(2)]
     host = [host_batch(s) for s in range(min(n_steps, 4))]
 
     def to_device(step, slot):
@@ -196,13 +197,16 @@ def run_ours(args) -> dict:
         t, m = host[step % len(host)]
         pinned_tok[slot].copy_(torch.from_numpy(t))
         pinned_msk[slot].copy_(torch.from_numpy(m))
+        act = np.flatnonzero(m[:, 1:]).astype(np.int32)      # supervised positions, known to the loader
+        pinned_act[slot][:act.size].copy_(torch.from_numpy(act))
         d_tok = pinned_tok[slot].cuda(non_blocking=True)
         d_msk = pinned_msk[slot].cuda(non_blocking=True)
+        d_act = pinned_act[slot][:act.size].cuda(non_blocking=True)
         ids = d_tok[:, :-1].to(torch.int64).contiguous()
         tgt = d_tok[:, 1:].to(torch.int64).contiguous()
         mask = d_msk[:, 1:].to(torch.float32).contiguous()
         w = E.row_weights(mask, mb, A)
-        return ids, tgt, mask, w
+        return ids, tgt, mask, w, d_act
 
     def barrier():
         if world > 1:
@@ -227,8 +231,8 @@ def run_ours(args) -> dict:
     torch.cuda.synchronize()
 
     def step_resident(s):
-        ids, tgt, mask, w = resident[s % len(resident)]
-        eng.train_step(ids, tgt, mask, w)
+        ids, tgt, mask, w, act = resident[s % len(resident)]
+        eng.train_step(ids, tgt, mask, w, active_rows=act)
 
     for s in range(args.warmup):
         step_resident(s)
@@ -257,14 +261,15 @@ def run_ours(args) -> dict:
     losses = []
 
     def step_e2e(s):
-        ids, tgt, mask, w = to_device(s, s % 2)
-        eng.train_step(ids, tgt, mask, w)
+        ids, tgt, mask, w, act = to_device(s, s % 2)
+        eng.train_step(ids, tgt, mask, w, active_rows=act)
         losses.append(eng.read_metrics()["loss"])      # D2H read of the step's loss / grad norm
 
     step_e2e(0)
     ms_e2e = timed(step_e2e, args.steps)
 
     positions = rows * T
+    act_mean = int(np.mean([int(m[:, 1:].sum()) for _, m in host]))
     value = positions * args.steps / (ms_total / 1e3)
     e2e_value = positions * args.steps / (ms_e2e / 1e3)
     peaks = measured_peaks()
@@ -279,13 +284,14 @@ def run_ours(args) -> dict:
         "data": "synthetic", "impl": "ours",
         "config": {"workload": args.workload, "global_batch": rows, "seq_len": S, "positions_per_step": positions,
                    "micro_batch": mb, "grad_accum": A, "parallelism": f"dp{world}+zero1",
-                   "gradient_checkpointing": ckpt, "l2": "inputs larger than L2 (activations of several GB per step)",
+                   "gradient_checkpointing": ckpt, "supervised_positions_per_rank": act_mean,
+                   "lm_head": "supervised rows only (masked rows have zero loss and gradient)", "l2": "inputs larger than L2 (activations of several GB per step)",
                    "algorithmic_tflop_per_step": flops_step / 1e12},
         "step_tflops_per_gpu": flops_step / (ms_total / args.steps / 1e3) / 1e12 / world,
         "step_frac_of_tf32_peak": flops_step / (ms_total / args.steps / 1e3) / 1e12 / world / tf32_peak,
         "loss": metrics["loss"], "grad_norm": metrics["grad_norm"],
         "e2e": {"value": e2e_value, "unit": "tokens/s", "ms_per_step": ms_e2e / args.steps,
-                "h2d_bytes_per_step": my_rows * S * 5, "d2h_bytes_per_step": 24},
+                "h2d_bytes_per_step": my_rows * S * 5 + 4 * act_mean, "d2h_bytes_per_step": 24},
         "gpu_launches": int(launches),
         "clocks": clocks,
         "roofline": {"kernel": "gemm_tf32_kernel (tcgen05)", "bound": "tensor", "achieved": achieved,

@@ -193,6 +193,35 @@ __global__ void __launch_bounds__(512)
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
+// dst[i] = src[idx[i]] (gather) or dst[idx[i]] = src[i] (scatter), rows of H floats, one warp per row.
+template <bool SCATTER>
+__global__ void __launch_bounds__(256)
+    move_rows_kernel(const float* __restrict__ src, const int32_t* __restrict__ idx, float* __restrict__ dst,
+                     int64_t n, int H4) {
+  const int lane = threadIdx.x & 31;
+  const int64_t warp0 = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const int64_t nwarps = (static_cast<int64_t>(gridDim.x) * blockDim.x) >> 5;
+  for (int64_t i = warp0; i < n; i += nwarps) {
+    const int64_t r = idx[i];
+    const float4* s4 = reinterpret_cast<const float4*>(src) + (SCATTER ? i : r) * H4;
+    float4* d4 = reinterpret_cast<float4*>(dst) + (SCATTER ? r : i) * H4;
+    for (int c = lane; c < H4; c += 32) d4[c] = s4[c];
+  }
+}
+
+__global__ void __launch_bounds__(256)
+    gather_ce_inputs_kernel(const int64_t* __restrict__ targets, const float* __restrict__ mask,
+                            const float* __restrict__ weight, const int32_t* __restrict__ idx,
+                            int64_t* __restrict__ t_out, float* __restrict__ m_out, float* __restrict__ w_out,
+                            int64_t n) {
+  const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const int64_t r = idx[i];
+  t_out[i] = targets[r];
+  m_out[i] = mask != nullptr ? mask[r] : 1.0f;
+  if (w_out != nullptr) w_out[i] = weight != nullptr ? weight[r] : 0.0f;
+}
+
 }  // namespace
 }  // namespace ctdk
 
@@ -227,6 +256,36 @@ int ctdk_embedding_bwd(const int64_t* ids, const float* dy, float* dW, int64_t r
   embedding_bwd_kernel<<<static_cast<int>(need < cap ? need : cap), 256, 0,
                          static_cast<cudaStream_t>(stream)>>>(ids, dy, dW, rows, H, V, st);
   return check_launch("ctdk_embedding_bwd");
+}
+
+int ctdk_gather_rows(const float* src, const int32_t* idx, float* dst, int64_t n, int H, void* stream) {
+  CTDK_REQUIRE(n >= 0 && H > 0 && H % 4 == 0, "ctdk_gather_rows: H must be a positive multiple of 4");
+  if (n == 0) return CTDK_OK;
+  CTDK_REQUIRE(src && idx && dst && aligned16(src) && aligned16(dst), "ctdk_gather_rows: bad pointer");
+  const int64_t cap = static_cast<int64_t>(sm_count()) * 8, need = (n + 7) / 8;
+  move_rows_kernel<false><<<static_cast<int>(need < cap ? need : cap), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      src, idx, dst, n, H / 4);
+  return check_launch("ctdk_gather_rows");
+}
+
+int ctdk_scatter_rows(const float* src, const int32_t* idx, float* dst, int64_t n, int H, void* stream) {
+  CTDK_REQUIRE(n >= 0 && H > 0 && H % 4 == 0, "ctdk_scatter_rows: H must be a positive multiple of 4");
+  if (n == 0) return CTDK_OK;
+  CTDK_REQUIRE(src && idx && dst && aligned16(src) && aligned16(dst), "ctdk_scatter_rows: bad pointer");
+  const int64_t cap = static_cast<int64_t>(sm_count()) * 8, need = (n + 7) / 8;
+  move_rows_kernel<true><<<static_cast<int>(need < cap ? need : cap), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      src, idx, dst, n, H / 4);
+  return check_launch("ctdk_scatter_rows");
+}
+
+int ctdk_gather_ce_inputs(const int64_t* targets, const float* mask, const float* weight, const int32_t* idx,
+                          int64_t* t_out, float* m_out, float* w_out, int64_t n, void* stream) {
+  CTDK_REQUIRE(n >= 0, "ctdk_gather_ce_inputs: negative size");
+  if (n == 0) return CTDK_OK;
+  CTDK_REQUIRE(targets && idx && t_out && m_out, "ctdk_gather_ce_inputs: null pointer");
+  gather_ce_inputs_kernel<<<ceil_div(n, 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(targets, mask, weight, idx,
+                                                                                         t_out, m_out, w_out, n);
+  return check_launch("ctdk_gather_ce_inputs");
 }
 
 int ctdk_ce_masked(float* logits, const int64_t* targets, const float* loss_mask,

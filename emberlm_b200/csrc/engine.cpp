@@ -128,6 +128,11 @@ struct Engine {
   std::vector<LayerActs> acts;    // L entries (all alias entry 0 when checkpointing)
   float *hf, *dh, *dtmp, *dgu, *dact, *dqkv, *dattn, *delta, *norm_scratch, *qk_scratch;
   float* logits;
+  float *hfc, *dhfc, *mask_c, *w_c;  // compacted LM-head inputs (supervised rows only)
+  int64_t* tgt_c;
+  const int32_t* active_rows = nullptr;
+  const int32_t* active_rows_last = nullptr;
+  int64_t n_active = 0;
   float* ws3 = nullptr;       // operand-split workspace of the 3xTF32 GEMMs
   int64_t ws3_floats = 0;
   ctdk_layer_callback cb = nullptr;
@@ -185,6 +190,11 @@ void carve(Engine& e, Bump& b) {
   e.norm_scratch = b.floats(ctdk_rmsnorm_bwd_scratch_floats(static_cast<int>(hid)));
   e.qk_scratch = b.floats(ctdk_qk_norm_rope_bwd_scratch_floats(static_cast<int>(D)));
   e.logits = b.floats(e.head_rows * c.vocab_size);
+  e.hfc = b.floats(tok * hid);
+  e.dhfc = b.floats(tok * hid);
+  e.mask_c = b.floats(tok);
+  e.w_c = b.floats(tok);
+  e.tgt_c = reinterpret_cast<int64_t*>(b.floats(2 * tok));
   if (c.precision == CTDK_GEMM_3XTF32) {
     // largest M*K + K*N over every GEMM (M, N, K) of a step: forward, dX and dW of the four
     // projections of a layer, and the three GEMMs of an LM-head block
@@ -333,22 +343,48 @@ int run(Engine& e, const int64_t* ids, const int64_t* targets, const float* loss
   TRY(ctdk_rmsnorm_fwd(e.xs[L], P + e.layout.norm, e.hf, nullptr, tok, static_cast<int>(hid),
                        c.rms_norm_eps, s));
 
-  // LM head + masked CE (+ its backward) in row blocks. dhf goes to dtmp.
+  // LM head + masked CE (+ its backward) in row blocks. dhf goes to dtmp. When the caller named the
+  // supervised rows, only those are run through the head: hf, targets, mask and weights are
+  // compacted first and d(hf) is scattered back into a zeroed buffer afterwards.
   const float* E = P + e.layout.embed;
   float* dE = G + e.layout.embed;
+  const bool compact = e.active_rows != nullptr && e.n_active > 0 && e.n_active < tok;
+  const int64_t head_n = compact ? e.n_active : tok;
+  const float* hf = e.hf;
+  const int64_t* tg = targets;
+  const float* mk = loss_mask;
+  const float* rw = row_weight;
+  float* dhf = e.dtmp;
+  if (compact) {
+    TRY(ctdk_gather_rows(e.hf, e.active_rows, e.hfc, head_n, static_cast<int>(hid), s));
+    TRY(ctdk_gather_ce_inputs(targets, loss_mask, row_weight, e.active_rows, e.tgt_c, e.mask_c,
+                              backward ? e.w_c : nullptr, head_n, s));
+    hf = e.hfc;
+    tg = e.tgt_c;
+    mk = e.mask_c;
+    rw = e.w_c;
+    dhf = e.dhfc;
+  }
+  e.active_rows_last = e.active_rows;
+  e.active_rows = nullptr;  // one call only
+  e.n_active = 0;
   bool first_block = true;
-  for (int64_t r0 = 0; r0 < tok; r0 += e.head_rows) {
-    const int64_t n = (tok - r0 < e.head_rows) ? tok - r0 : e.head_rows;
-    TRY(gemm(e, e.hf + r0 * hid, E, e.logits, n, V, hid, 0, 1, CTDK_EPI_STORE, nullptr, s));
-    TRY(ctdk_ce_masked(e.logits, targets + r0, loss_mask ? loss_mask + r0 : nullptr,
-                       backward ? row_weight + r0 : nullptr, loss_sums, nullptr, n, V,
-                       backward ? 1 : 0, s));
+  for (int64_t r0 = 0; r0 < head_n; r0 += e.head_rows) {
+    const int64_t n = (head_n - r0 < e.head_rows) ? head_n - r0 : e.head_rows;
+    TRY(gemm(e, hf + r0 * hid, E, e.logits, n, V, hid, 0, 1, CTDK_EPI_STORE, nullptr, s));
+    TRY(ctdk_ce_masked(e.logits, tg + r0, mk ? mk + r0 : nullptr, backward ? rw + r0 : nullptr, loss_sums,
+                       nullptr, n, V, backward ? 1 : 0, s));
     if (backward) {
-      TRY(gemm(e, e.logits, E, e.dtmp + r0 * hid, n, hid, V, 0, 0, CTDK_EPI_STORE, nullptr, s));
+      TRY(gemm(e, e.logits, E, dhf + r0 * hid, n, hid, V, 0, 0, CTDK_EPI_STORE, nullptr, s));
       const int epi = (accumulate || !first_block) ? CTDK_EPI_ACCUMULATE : CTDK_EPI_STORE;
-      TRY(gemm(e, e.logits, e.hf + r0 * hid, dE, V, hid, n, 1, 0, epi, nullptr, s));
+      TRY(gemm(e, e.logits, hf + r0 * hid, dE, V, hid, n, 1, 0, epi, nullptr, s));
     }
     first_block = false;
+  }
+  if (backward && compact) {
+    if (cudaMemsetAsync(e.dtmp, 0, sizeof(float) * tok * hid, static_cast<cudaStream_t>(s)) != cudaSuccess)
+      return fail(CTDK_ELAUNCH, "engine: memset failed");
+    TRY(ctdk_scatter_rows(e.dhfc, e.active_rows_last, e.dtmp, head_n, static_cast<int>(hid), s));
   }
   if (!backward) return CTDK_OK;
 
@@ -440,6 +476,15 @@ int ctdk_engine_set_layer_callback(void* engine, ctdk_layer_callback cb, void* u
   Engine* e = static_cast<Engine*>(engine);
   e->cb = cb;
   e->cb_user = user;
+  return CTDK_OK;
+}
+
+int ctdk_engine_set_active_rows(void* engine, const int32_t* rows, int64_t n) {
+  CTDK_REQUIRE(engine != nullptr, "ctdk_engine_set_active_rows: null engine");
+  Engine* e = static_cast<Engine*>(engine);
+  CTDK_REQUIRE(n >= 0 && n <= e->tok_cap, "ctdk_engine_set_active_rows: bad row count");
+  e->active_rows = n > 0 ? rows : nullptr;
+  e->n_active = n;
   return CTDK_OK;
 }
 

@@ -190,6 +190,8 @@ _L.ctdk_engine_forward_backward.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, 
 _L.ctdk_engine_forward_loss.restype = C.c_int
 _L.ctdk_engine_forward_loss.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64,
                                         C.c_void_p, C.c_void_p]
+_L.ctdk_engine_set_active_rows.restype = C.c_int
+_L.ctdk_engine_set_active_rows.argtypes = [C.c_void_p, C.c_void_p, C.c_int64]
 LAYER_CALLBACK = C.CFUNCTYPE(None, C.c_int, C.c_void_p)
 _L.ctdk_engine_set_layer_callback.restype = C.c_int
 _L.ctdk_engine_set_layer_callback.argtypes = [C.c_void_p, LAYER_CALLBACK, C.c_void_p]
@@ -279,6 +281,13 @@ class TrainEngine:
         self._cb = LAYER_CALLBACK(lambda layer, _u: fn(layer)) if fn else LAYER_CALLBACK(0)
         lib.check(_L.ctdk_engine_set_layer_callback(self._h, self._cb, None))
 
+    def set_active_rows(self, rows: torch.Tensor | None) -> None:
+        """Names the supervised positions (ascending int32 indices into the flattened batch) of the
+        next forward_backward / forward_loss call, so the LM head skips the others."""
+        self._active = rows  # keep alive until the kernels have run
+        n = 0 if rows is None else rows.numel()
+        lib.check(_L.ctdk_engine_set_active_rows(self._h, rows.data_ptr() if n else None, n))
+
     def forward_backward(self, ids, targets, loss_mask, row_weight, accumulate=False) -> None:
         B, T = ids.shape
         lib.check(_L.ctdk_engine_forward_backward(
@@ -325,9 +334,12 @@ class TrainEngine:
             import torch.distributed as dist
             dist.all_gather_into_tensor(self.params, pshard, group=self.group)
 
-    def train_step(self, ids, targets, loss_mask, row_weight, lr=None) -> None:
-        """One optimizer step on this rank's rows (already weighted per micro-batch)."""
+    def train_step(self, ids, targets, loss_mask, row_weight, lr=None, active_rows=None) -> None:
+        """One optimizer step on this rank's rows (already weighted per micro-batch). active_rows:
+        optional int32 device tensor of the supervised positions (see set_active_rows)."""
         self.loss_sums.zero_()
+        if active_rows is not None:
+            self.set_active_rows(active_rows)
         self.forward_backward(ids, targets, loss_mask, row_weight, accumulate=False)
         self.optimizer_step(lr)
 

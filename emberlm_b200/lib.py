@@ -73,6 +73,9 @@ _SIGS = {
     "ctdk_embedding_fwd": [_p, _p, _p, _l, _i, _l, _p],
     "ctdk_embedding_bwd": [_p, _p, _p, _l, _i, _l, _p],
     "ctdk_ce_masked": [_p, _p, _p, _p, _p, _p, _l, _l, _i, _p],
+    "ctdk_gather_rows": [_p, _p, _p, _l, _i, _p],
+    "ctdk_scatter_rows": [_p, _p, _p, _l, _i, _p],
+    "ctdk_gather_ce_inputs": [_p, _p, _p, _p, _p, _p, _p, _l, _p],
     "ctdk_attn_fwd": [_p, _p, _p, _l, _l, _i, _i, _i, _p],
     "ctdk_attn_bwd": [_p, _p, _p, _p, _p, _p, _l, _l, _i, _i, _i, _p],
     "ctdk_sumsq": [_p, _l, _p, _p],

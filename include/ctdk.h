@@ -200,6 +200,15 @@ int ctdk_ce_masked(float* logits, const int64_t* targets, const float* loss_mask
                    const float* row_weight, float* loss_sum, float* lse_out, int64_t n,
                    int64_t V, int dlogits_inplace, void* stream);
 
+/* Row gather / scatter used to run the LM head and the loss only on supervised positions: rows
+ * whose loss mask is 0 contribute exactly 0 to the loss and to every gradient
+ * (ce_masked_bwd_kernel_f32 scales them by mk = 0, src/ops/loss.cu:318-327), so they need no
+ * logits at all. idx holds the kept row numbers (int32, ascending). */
+int ctdk_gather_rows(const float* src, const int32_t* idx, float* dst, int64_t n, int H, void* stream);
+int ctdk_scatter_rows(const float* src, const int32_t* idx, float* dst, int64_t n, int H, void* stream);
+int ctdk_gather_ce_inputs(const int64_t* targets, const float* mask, const float* weight, const int32_t* idx,
+                          int64_t* t_out, float* m_out, float* w_out, int64_t n, void* stream);
+
 /* ------------------------------------------------------------------------------------
  * Causal softmax attention with grouped-query heads on packed projections.
  * Replaces the bmm -> mul_scalar -> causal mask -> softmax -> bmm chain of
@@ -287,6 +296,11 @@ int ctdk_engine_destroy(void* engine);
 int ctdk_engine_forward_backward(void* engine, const int64_t* ids, const int64_t* targets,
                                  const float* loss_mask, const float* row_weight, int64_t B,
                                  int64_t T, int accumulate, float* loss_sums, void* stream);
+/* Optional, before the next forward_backward / forward_loss call only: the rows (positions of the
+ * flattened [B*T] batch) whose loss mask is non-zero, as an ascending int32 device array. The final
+ * norm output is then compacted to these rows before the LM head, so the head GEMMs and the loss
+ * skip the unsupervised half of a typical SFT batch. n == 0 or never calling it keeps all rows. */
+int ctdk_engine_set_active_rows(void* engine, const int32_t* rows, int64_t n);
 /* Forward and loss only (the no-grad validation pass, tools/ctd_train/main.cpp:191-206). */
 int ctdk_engine_forward_loss(void* engine, const int64_t* ids, const int64_t* targets,
                              const float* loss_mask, int64_t B, int64_t T, float* loss_sums,

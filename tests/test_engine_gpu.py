@@ -163,3 +163,41 @@ def test_forward_loss_only_and_errors():
     big = torch.zeros(3, 39, dtype=torch.int64, device="cuda")
     with pytest.raises(lib.CtdkError):
         eng.forward_loss(big, big, torch.zeros(3, 39, device="cuda"))
+
+
+def test_supervised_row_compaction_matches_dense_head():
+    """Naming the supervised rows skips the LM head on masked-out rows. Those rows carry weight 0 in
+    the masked CE (src/ops/loss.cu:318-327), so the loss sums are identical and the gradients agree
+    to summation order (the head GEMMs see a different K / M split)."""
+    ocfg, ecfg = cfg_pair(vocab_size=1000, hidden_size=128, intermediate_size=256)
+    params = perturbed_params(ocfg, 13)
+    tok, msk = om.synth_batch(ocfg.vocab_size, 3, 131, seed=8)
+    ids, tgt, m = om.make_batch(tok, msk, [0, 1, 2])
+    assert 0 < m.sum() < m.size
+    eng, dense, ls_dense, (d_ids, d_tgt, d_m, w) = run_engine(ecfg, params, ids, tgt, m, 3, 1)
+    rows = torch.nonzero(d_m.view(-1) > 0).to(torch.int32).view(-1).contiguous()
+    eng.loss_sums.zero_()
+    eng.set_active_rows(rows)
+    eng.forward_backward(d_ids, d_tgt, d_m, w)
+    torch.cuda.synchronize()
+    ls = eng.loss_sums.tolist()
+    assert ls[1] == ls_dense[1] and abs(ls[0] - ls_dense[0]) <= 1e-5 * abs(ls_dense[0])
+    for k, v in eng.named_grads().items():
+        assert tensor_err(v.cpu().numpy(), dense[k].astype(np.float64)) <= 2e-3, k
+    # the setting lasts one call: the next one is dense again and reproduces the first run
+    eng.loss_sums.zero_()
+    eng.forward_backward(d_ids, d_tgt, d_m, w)
+    torch.cuda.synchronize()
+    for k, v in eng.named_grads().items():
+        if k != "model.embed_tokens.weight":
+            assert np.array_equal(v.cpu().numpy(), dense[k]), k
+    # against the oracle too
+    _, _, ref = om.forward_backward(params, ocfg, ids, tgt, m, dy=1.0, acc=np.float64)
+    eng.loss_sums.zero_()
+    eng.set_active_rows(rows)
+    eng.forward_backward(d_ids, d_tgt, d_m, w)
+    torch.cuda.synchronize()
+    for k, v in eng.named_grads().items():
+        assert tensor_err(v.cpu().numpy(), ref[k]) <= TENSOR_TOL, k
+    with pytest.raises(Exception):
+        eng.set_active_rows(torch.zeros(3 * 131 + 1, dtype=torch.int32, device="cuda"))

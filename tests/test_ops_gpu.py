@@ -318,6 +318,33 @@ def test_cross_entropy_masked_identities_and_zero_sum(K):
         K.cross_entropy_masked(dev(z), dev(t), dev(np.zeros(5, F32)))
 
 
+@pytest.mark.parametrize("n,H", [(0, 64), (1, 4), (257, 960), (4099, 576)])
+def test_row_gather_scatter_and_ce_input_gather(n, H):
+    from emberlm_b200 import lib
+    rows = 2 * n + 3
+    rng = np.random.default_rng(41)
+    idx = np.sort(rng.choice(rows, size=n, replace=False)).astype(np.int32)
+    src = rnd((rows, H), 42)
+    d_src, d_idx = dev(src), dev(idx)
+    out = torch.full((max(n, 1), H), -7.0, device="cuda")
+    lib.call("ctdk_gather_rows", d_src.data_ptr(), d_idx.data_ptr(), out.data_ptr(), n, H, None)
+    assert np.array_equal(host(out)[:n], src[idx])
+    back = torch.zeros(rows, H, device="cuda")
+    lib.call("ctdk_scatter_rows", out.data_ptr(), d_idx.data_ptr(), back.data_ptr(), n, H, None)
+    want = np.zeros_like(src)
+    want[idx] = src[idx]
+    assert np.array_equal(host(back), want)
+    t = rng.integers(0, 1000, size=rows).astype(np.int64)
+    m, w = rnd(rows, 43), rnd(rows, 44)
+    to = torch.zeros(max(n, 1), dtype=torch.int64, device="cuda")
+    mo, wo = torch.zeros(max(n, 1), device="cuda"), torch.zeros(max(n, 1), device="cuda")
+    d_t, d_m, d_w = dev(t), dev(m), dev(w)
+    lib.call("ctdk_gather_ce_inputs", d_t.data_ptr(), d_m.data_ptr(), d_w.data_ptr(), d_idx.data_ptr(),
+             to.data_ptr(), mo.data_ptr(), wo.data_ptr(), n, None)
+    assert np.array_equal(host(to)[:n], t[idx]) and np.array_equal(host(mo)[:n], m[idx])
+    assert np.array_equal(host(wo)[:n], w[idx])
+
+
 # ---------------------------------------------------------------------------------------
 def test_adamw_closed_form_and_weight_decay(K):
     from tests import ref_cases as rc
