@@ -253,29 +253,43 @@ __global__ void __launch_bounds__(128)
 }
 
 // delta[b][h][t] = sum_d dO*O  (the rowsum of softmax backward, emberlm
-// src/ops/softmax.cu:56-93). One warp per (row, head).
+// src/ops/softmax.cu:56-93). D/4 lanes per (row, head), one float4 of each operand per lane and
+// four rows in flight per lane group, so the kernel runs at memory speed.
+template <int D>
 __global__ void __launch_bounds__(256)
     attn_delta_kernel(const float* __restrict__ out, const float* __restrict__ dout,
-                      float* __restrict__ delta, int64_t B, int T, int H, int D) {
-  const int lane = threadIdx.x & 31;
-  const int64_t warp0 = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
-  const int64_t nwarps = (static_cast<int64_t>(gridDim.x) * blockDim.x) >> 5;
+                      float* __restrict__ delta, int64_t B, int T, int H) {
+  constexpr int LP = D / 4;          // lanes per item: 16 (D = 64) or 32 (D = 128)
+  constexpr int UN = 4;              // items in flight per lane group
+  const int sub = threadIdx.x % LP;
+  const int64_t group0 = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) / LP;
+  const int64_t ngroups = (static_cast<int64_t>(gridDim.x) * blockDim.x) / LP;
   const int64_t items = B * T * H;
-  for (int64_t it = warp0; it < items; it += nwarps) {
-    const float4* o4 = reinterpret_cast<const float4*>(out + it * D);
-    const float4* d4 = reinterpret_cast<const float4*>(dout + it * D);
-    float acc = 0.0f;
-    for (int i = lane; i < D / 4; i += 32) {
-      const float4 a = o4[i], c = d4[i];
-      acc += a.x * c.x + a.y * c.y + a.z * c.z + a.w * c.w;
+  for (int64_t base = group0 * UN; base < items; base += ngroups * UN) {
+    float4 a[UN], c[UN];
+#pragma unroll
+    for (int u = 0; u < UN; ++u) {
+      const int64_t it = base + u;
+      if (it < items) {
+        a[u] = __ldcs(reinterpret_cast<const float4*>(out + it * D) + sub);
+        c[u] = __ldg(reinterpret_cast<const float4*>(dout + it * D) + sub);   // read again by the dQ / dK,dV kernels
+      } else {
+        a[u] = c[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+      }
     }
-    acc = warp_sum(acc);
-    if (lane == 0) {
-      const int64_t bt = it / H;
-      const int h = static_cast<int>(it - bt * H);
-      const int64_t bb = bt / T;
-      const int tt = static_cast<int>(bt - bb * T);
-      delta[(bb * H + h) * T + tt] = acc;
+#pragma unroll
+    for (int u = 0; u < UN; ++u) {
+      float acc = a[u].x * c[u].x + a[u].y * c[u].y + a[u].z * c[u].z + a[u].w * c[u].w;
+#pragma unroll
+      for (int o = LP / 2; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+      const int64_t it = base + u;
+      if (sub == 0 && it < items) {
+        const int64_t bt = it / H;
+        const int h = static_cast<int>(it - bt * H);
+        const int64_t bb = bt / T;
+        const int tt = static_cast<int>(bt - bb * T);
+        delta[(bb * H + h) * T + tt] = acc;
+      }
     }
   }
 }
@@ -589,10 +603,16 @@ int ctdk_attn_bwd_p(const float* qkv, const float* out, const float* dout, const
   // backward = 2x the forward's algorithmic FLOPs (recomputation is not counted)
   void* tok = prof_begin(CTDK_PROF_ATTN, 4.0 * B * H * static_cast<double>(T) * T * D, s);
   const int64_t items = B * T * H;
-  const int64_t cap = static_cast<int64_t>(sm_count()) * 8;
-  const int64_t need = (items + 7) / 8;
-  attn_delta_kernel<<<static_cast<int>(need < cap ? need : cap), 256, 0, s>>>(out, dout, delta, B,
-                                                                             static_cast<int>(T), H, D);
+  {
+    const int lp = D / 4;
+    const int64_t cap = static_cast<int64_t>(sm_count()) * 8;
+    const int64_t need = (items + (256 / lp) * 4 - 1) / ((256 / lp) * 4);
+    const int grid = static_cast<int>(need < cap ? need : cap);
+    if (D == 64)
+      attn_delta_kernel<64><<<grid, 256, 0, s>>>(out, dout, delta, B, static_cast<int>(T), H);
+    else
+      attn_delta_kernel<128><<<grid, 256, 0, s>>>(out, dout, delta, B, static_cast<int>(T), H);
+  }
   rc = check_launch("ctdk_attn_bwd(delta)");
   if (rc != CTDK_OK) return rc;
   // tcgen05 kernels first; each returns 1 when it does not take the shape.

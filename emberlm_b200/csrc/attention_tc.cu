@@ -138,7 +138,8 @@ __global__ void __launch_bounds__(192, FwdCfg<D>::kCtasPerSm)
   uint64_t* s_full = bars + 10;     // [2]  S(g) is in tensor memory
   uint64_t* p_ready = bars + 12;    // [2]  P(g) has replaced S(g) (128 arrivals)
   uint64_t* pv_full = bars + 14;    // 1    O += P(g) V(g) has finished (one phase per step)
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 15);
+  uint64_t* o_full = bars + 15;     // 1    the item's last P V has finished (one phase per item)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
@@ -154,6 +155,7 @@ __global__ void __launch_bounds__(192, FwdCfg<D>::kCtasPerSm)
       mbar_init(&p_ready[i], 128);
     }
     mbar_init(pv_full, 1);
+    mbar_init(o_full, 1);
     mbar_fence_init();
     tma_prefetch_desc(&tm_q);
     tma_prefetch_desc(&tm_k);
@@ -278,6 +280,7 @@ __global__ void __launch_bounds__(192, FwdCfg<D>::kCtasPerSm)
           }
           umma_commit(&v_empty[s]);
           umma_commit(pv_full);
+          if (j == w.n_steps - 1) umma_commit(o_full);
           if (j + 2 < w.n_steps) ok = issue_s(j + 2);
         }
         g0 += static_cast<uint32_t>(w.n_steps);
@@ -294,10 +297,10 @@ __global__ void __launch_bounds__(192, FwdCfg<D>::kCtasPerSm)
     const uint32_t lane_off = static_cast<uint32_t>(qd * 32) << 16;
     const float sc = args.scale_log2;
     const uint32_t to = tm_o + lane_off;
-    uint32_t g0 = 0;
+    uint32_t g0 = 0, n_done = 0;
     bool ok = true;
     PROBE_DECL();
-    for (int it = blockIdx.x; it < args.n_items && ok; it += gridDim.x) {
+    for (int it = blockIdx.x; it < args.n_items && ok; it += gridDim.x, ++n_done) {
       const FwdItem w = fwd_item(args, it);
       const int row = w.q0 + qd * 32 + lane;   // query position inside the sequence
       float m_ref = 0.0f, l_run = 0.0f;
@@ -373,11 +376,13 @@ __global__ void __launch_bounds__(192, FwdCfg<D>::kCtasPerSm)
         PROBE_IF(threadIdx.x == 64) { PROBE_ADD(5); PROBE_CNT(8); }
       }
       g0 += static_cast<uint32_t>(w.n_steps);
-      // the item's last P V: completion number g0 of pv_full. The next item's first P V cannot
-      // start before these threads have read O and arrived at its p_ready.
+      // The item's last P V, on a barrier of its own with one phase per item: pv_full cannot be
+      // used here, because up to two of its phases may still be outstanding at this point and a
+      // parity wait cannot tell them apart. The next item's first P V cannot start before these
+      // threads have read O and arrived at its p_ready.
       {
         PROBE_T0();
-        if (!ok || !mbar_wait_bounded(pv_full, (g0 - 1u) & 1u, args.status, 33)) { ok = false; break; }
+        if (!ok || !mbar_wait_bounded(o_full, n_done & 1u, args.status, 33)) { ok = false; break; }
         PROBE_IF(threadIdx.x == 64) PROBE_ADD(6);
       }
       PROBE_T0();

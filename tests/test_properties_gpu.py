@@ -37,6 +37,9 @@ def test_attention_causality_batch_independence_and_backward_fd(K):
     qkv = torch.randn(B * T, (H + 2 * Hk) * D, generator=g, device="cuda") * 0.5
     out, lse = K.attention(qkv, B, T, H, Hk, D)
     assert torch.isfinite(out).all() and torch.isfinite(lse).all()
+    # determinism: the same launch twice gives the same bits (a missed wait shows up here first)
+    out_b, lse_b = K.attention(qkv, B, T, H, Hk, D)
+    assert torch.equal(out, out_b) and torch.equal(lse, lse_b)
     # causality: changing tokens >= 700 of every row leaves outputs of earlier positions unchanged
     q2 = qkv.clone().view(B, T, -1)
     q2[:, 700:] += 1.0
