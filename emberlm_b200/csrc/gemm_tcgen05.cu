@@ -435,9 +435,9 @@ int dispatch_major(bool a_mn, bool b_mn, const CUtensorMap& ta, const CUtensorMa
 
 }  // namespace
 
-int gemm_tcgen05_2cta(const CUtensorMap& ta, const CUtensorMap& tb, bool a_mn, bool b_mn, float* C,
-                      const float* aux, int64_t ldc, int M, int N, int K, int epilogue, int vec_ok, int splits,
-                      int* status, cudaStream_t stream);
+int gemm_tcgen05_2cta(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, bool a_mn, bool b_mn,
+                      bool a3d, bool b3d, int tma_out, float* C, const float* aux, int64_t ldc, int M, int N, int K,
+                      int epilogue, int vec_ok, int splits, int* status, cudaStream_t stream);
 
 // Returns CTDK_OK after enqueueing, or 1 when the shape/alignment is not eligible for the
 // tensor-core path (the caller then uses the SIMT kernel).
@@ -522,10 +522,23 @@ int gemm_tcgen05(const float* A, const float* B, float* Cp, int64_t M, int64_t N
 
   CUtensorMap ta, tb;
   int rc;
-  if (a_mn) rc = make_map(&ta, A, M, K, lda, BK, true, false);
+  // The pair kernel takes an MN-major operand whose contiguous extent is a multiple of 32 through
+  // a 3-D map {32 columns, K rows, extent / 32 column groups}: one {32, 32, 4} box per k-block
+  // instead of four {32, 32} boxes (issuing a TMA copy costs the producer thread ~140 cycles).
+  auto make_map3 = [&](CUtensorMap* m, const float* base, int64_t extent, int64_t ld) {
+    const uint64_t dims[3] = {32u, static_cast<uint64_t>(K), static_cast<uint64_t>(extent / 32)};
+    const uint64_t strides[2] = {static_cast<uint64_t>(ld) * sizeof(float), 128u};
+    const uint32_t box[3] = {32u, 32u, 4u};
+    return encode_tensor_map(m, base, 3, dims, strides, box, true);
+  };
+  const bool a3d = use_pair && a_mn && (M % 32 == 0);
+  const bool b3d = use_pair && b_mn && (N % 32 == 0);
+  if (a3d) rc = make_map3(&ta, A, M, lda);
+  else if (a_mn) rc = make_map(&ta, A, M, K, lda, BK, true, false);
   else rc = make_map(&ta, A, K, M, lda, BM, false, false);
   if (rc != CTDK_OK) return rc;
-  if (b_mn) rc = make_map(&tb, B, N, K, ldb, BK, true, false);
+  if (b3d) rc = make_map3(&tb, B, N, ldb);
+  else if (b_mn) rc = make_map(&tb, B, N, K, ldb, BK, true, false);
   else rc = make_map(&tb, B, K, N, ldb, use_pair ? 128 : bn, false, false);
   if (rc != CTDK_OK) return rc;
 
@@ -538,8 +551,18 @@ int gemm_tcgen05(const float* A, const float* B, float* Cp, int64_t M, int64_t N
                                         static_cast<size_t>(N) * sizeof(float), static_cast<size_t>(M), stream);
       if (e != cudaSuccess) return fail(CTDK_ELAUNCH, "gemm: memset failed: %s", cudaGetErrorString(e));
     }
-    return gemm_tcgen05_2cta(ta, tb, a_mn, b_mn, Cp, aux, ldc, static_cast<int>(M), static_cast<int>(N),
-                             static_cast<int>(K), epilogue, vec, splits, st, stream);
+    // Output through TMA (coalesced, off the load/store pipe): plain store, or an fp32 add at L2
+    // for accumulation and for split-K partial tiles. The residual epilogue reads a second
+    // matrix and keeps the direct path.
+    int tma_out = 0;
+    CUtensorMap tc = ta;
+    if (vec && epilogue != CTDK_EPI_RESIDUAL) {
+      tma_out = (epilogue == CTDK_EPI_ACCUMULATE || splits > 1) ? 2 : 1;
+      rc = make_map(&tc, Cp, N, M, ldc, 32, false, true);
+      if (rc != CTDK_OK) return rc;
+    }
+    return gemm_tcgen05_2cta(ta, tb, tc, a_mn, b_mn, a3d, b3d, tma_out, Cp, aux, ldc, static_cast<int>(M),
+                             static_cast<int>(N), static_cast<int>(K), epilogue, vec, splits, st, stream);
   }
 
   GemmArgs args;

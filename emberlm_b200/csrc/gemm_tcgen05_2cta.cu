@@ -24,9 +24,24 @@ constexpr int kBHalf = (BN2 / 2) * BK2 * 4;  // 16 KB
 constexpr int kStage2 = kATile + kBHalf;
 constexpr int kStages2 = 6;
 constexpr int kChunk2 = 32 * BK2 * 4;    // one {32 x 32} box of an MN-major operand
-constexpr int kSmem2 = kStages2 * kStage2 + 1024 + 256;
+constexpr int kEpiBuf = 32 * 128;         // one {32 x 32} fp32 output box in transit
+constexpr int kEpiStage = 4 * 2 * kEpiBuf;  // 4 epilogue warps x 2 buffers
+constexpr int kSmem2 = kStages2 * kStage2 + kEpiStage + 1024 + 256;
 constexpr uint32_t kPeerMask = 0xFEFFFFFFu;  // clears the CTA-rank bit of a shared::cluster address
 constexpr int kGroupM2 = 8;
+
+#ifdef CTDK_GEMM_PROBE
+__device__ long long g_gemm_probe[16];
+#define GP_DECL() long long _acc[8] = {0, 0, 0, 0, 0, 0, 0, 0}
+#define GP_T0() const long long _pt0 = clock64()
+#define GP_ADD(i) _acc[i] += clock64() - _pt0
+#define GP_FLUSH(lo, hi) for (int _i = lo; _i < hi; ++_i) atomicAdd(reinterpret_cast<unsigned long long*>(&g_gemm_probe[_i]), static_cast<unsigned long long>(_acc[_i]))
+#else
+#define GP_DECL()
+#define GP_T0()
+#define GP_ADD(i)
+#define GP_FLUSH(lo, hi)
+#endif
 
 struct Gemm2Args {
   float* C;
@@ -36,6 +51,8 @@ struct Gemm2Args {
   int epilogue;
   int vec_ok;
   int splits;  // K ranges per tile; >1: partial tiles are added to C with atomics
+  int a3d, b3d;   // MN-major operand described by a 3-D map: one {32 x 32 x 4} box per k-block
+  int tma_out;    // 1: C is written (2: added to) through TMA from shared-memory staging
   int* status;
 };
 
@@ -67,6 +84,35 @@ __device__ __forceinline__ void tma_load_2d_pair(void* smem_dst, const CUtensorM
       "l"(reinterpret_cast<uint64_t>(m)), "r"(smem_u32(bar) & kPeerMask), "r"(c0), "r"(c1)
       : "memory");
 }
+__device__ __forceinline__ void tma_load_3d_pair(void* smem_dst, const CUtensorMap* m, uint64_t* bar, int c0,
+                                                 int c1, int c2) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4, %5}], [%2];"
+      ::"r"(smem_u32(smem_dst)),
+      "l"(reinterpret_cast<uint64_t>(m)), "r"(smem_u32(bar) & kPeerMask), "r"(c0), "r"(c1), "r"(c2)
+      : "memory");
+}
+// Shared-memory box -> global tile (out-of-range rows / columns are clipped by the map).
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* m, const void* smem_src, int c0, int c1) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(
+                   reinterpret_cast<uint64_t>(m)),
+               "r"(smem_u32(smem_src)), "r"(c0), "r"(c1)
+               : "memory");
+}
+// Same, but added to the tile in global memory (fp32 add performed at L2).
+__device__ __forceinline__ void tma_reduce_add_2d(const CUtensorMap* m, const void* smem_src, int c0, int c1) {
+  asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3}], [%1];" ::"l"(
+                   reinterpret_cast<uint64_t>(m)),
+               "r"(smem_u32(smem_src)), "r"(c0), "r"(c1)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void bulk_wait_read() {
+  asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+}
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ void umma_tf32_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
                                                uint32_t accumulate) {
   asm volatile(
@@ -106,11 +152,12 @@ __device__ __forceinline__ void tile_coords2(int tile, int m_blocks, int n_block
 template <bool A_MN, bool B_MN>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
     gemm_tf32_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                          const Gemm2Args args) {
+                          const __grid_constant__ CUtensorMap tmC, const Gemm2Args args) {
   extern __shared__ unsigned char smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   unsigned char* smem = smem_raw + ((1024u - (raw & 1023u)) & 1023u);
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStages2 * kStage2);
+  unsigned char* epi_stage = smem + kStages2 * kStage2;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(epi_stage + kEpiStage);
   uint64_t* full = bars;                   // [kStages2]  used in the leader only
   uint64_t* empty = bars + kStages2;       // [kStages2]  one per CTA, signalled by multicast commit
   uint64_t* tfull = bars + 2 * kStages2;   // [2]         one per CTA, multicast commit
@@ -139,6 +186,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
     mbar_fence_init();
     tma_prefetch_desc(&tmA);
     tma_prefetch_desc(&tmB);
+    if (args.tma_out) tma_prefetch_desc(&tmC);
   }
   if (warp == 1) {
     tmem_alloc2(tmem_slot, 512);
@@ -156,6 +204,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
       int s = 0;
       uint32_t ph = 0;
       bool ok = true;
+      GP_DECL();
+      const long long _k0 = clock64();
       for (int unit = pair; unit < num_units && ok; unit += n_pairs) {
         int mb, nb;
         tile_coords2(unit % num_tiles, m_blocks, n_blocks, mb, nb);
@@ -165,34 +215,52 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
         const int kb0 = static_cast<int>(static_cast<int64_t>(split) * k_blocks / args.splits);
         const int kb1 = static_cast<int>(static_cast<int64_t>(split + 1) * k_blocks / args.splits);
         for (int kb = kb0; kb < kb1; ++kb) {
-          if (!mbar_wait_bounded(&empty[s], ph ^ 1u, args.status, 61)) {
-            ok = false;
-            break;
+          {
+            GP_T0();
+            if (!mbar_wait_bounded(&empty[s], ph ^ 1u, args.status, 61)) {
+              ok = false;
+              break;
+            }
+            GP_ADD(0);
           }
+          GP_T0();
           unsigned char* a_dst = smem + s * kStage2;
           unsigned char* b_dst = a_dst + kATile;
           if (leader) mbar_expect_tx(&full[s], 2 * kStage2);  // bytes of both CTAs
           const int k0 = kb * BK2;
           if (A_MN) {
+            if (args.a3d) {
+              tma_load_3d_pair(a_dst, &tmA, &full[s], 0, k0, m0 >> 5);
+            } else {
 #pragma unroll
-            for (int c = 0; c < BM2 / 32; ++c)
-              tma_load_2d_pair(a_dst + c * kChunk2, &tmA, &full[s], m0 + 32 * c, k0);
+              for (int c = 0; c < BM2 / 32; ++c)
+                tma_load_2d_pair(a_dst + c * kChunk2, &tmA, &full[s], m0 + 32 * c, k0);
+            }
           } else {
             tma_load_2d_pair(a_dst, &tmA, &full[s], k0, m0);
           }
           if (B_MN) {
+            if (args.b3d) {
+              tma_load_3d_pair(b_dst, &tmB, &full[s], 0, k0, n0 >> 5);
+            } else {
 #pragma unroll
-            for (int c = 0; c < BN2 / 64; ++c)
-              tma_load_2d_pair(b_dst + c * kChunk2, &tmB, &full[s], n0 + 32 * c, k0);
+              for (int c = 0; c < BN2 / 64; ++c)
+                tma_load_2d_pair(b_dst + c * kChunk2, &tmB, &full[s], n0 + 32 * c, k0);
+            }
           } else {
             tma_load_2d_pair(b_dst, &tmB, &full[s], k0, n0);
           }
+          GP_ADD(1);
           if (++s == kStages2) {
             s = 0;
             ph ^= 1u;
           }
         }
       }
+#ifdef CTDK_GEMM_PROBE
+      _acc[2] = clock64() - _k0;
+      if (leader) { GP_FLUSH(0, 3); }
+#endif
     }
     __syncwarp();
   } else if (warp == 1) {
@@ -206,23 +274,33 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
       uint32_t ph = 0;
       bool ok = true;
       int it = 0;
+      GP_DECL();
       for (int unit = pair; unit < num_units && ok; unit += n_pairs, ++it) {
         const int split = unit / num_tiles;
         const int kb0 = static_cast<int>(static_cast<int64_t>(split) * k_blocks / args.splits);
         const int kb1 = static_cast<int>(static_cast<int64_t>(split + 1) * k_blocks / args.splits);
         const int acc = it & 1;
         const uint32_t acc_ph = (static_cast<uint32_t>(it) >> 1) & 1u;
-        if (!mbar_wait_bounded(&tempty[acc], acc_ph ^ 1u, args.status, 62)) {
-          ok = false;
-          break;
+        {
+          GP_T0();
+          if (!mbar_wait_bounded(&tempty[acc], acc_ph ^ 1u, args.status, 62)) {
+            ok = false;
+            break;
+          }
+          GP_ADD(3);
         }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BN2);
         for (int kb = kb0; kb < kb1; ++kb) {
-          if (!mbar_wait_bounded(&full[s], ph, args.status, 63)) {
-            ok = false;
-            break;
+          {
+            GP_T0();
+            if (!mbar_wait_bounded(&full[s], ph, args.status, 63)) {
+              ok = false;
+              break;
+            }
+            GP_ADD(4);
           }
+          GP_T0();
           tc_fence_after();
           const uint32_t a_addr = smem_u32(smem + s * kStage2);
           const uint32_t b_addr = a_addr + kATile;
@@ -235,6 +313,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
             umma_tf32_pair(d_tmem, adesc, bdesc, idesc, (kb != kb0 || ks != 0) ? 1u : 0u);
           }
           umma_commit_pair(&empty[s]);
+          GP_ADD(5);
           if (++s == kStages2) {
             s = 0;
             ph ^= 1u;
@@ -242,6 +321,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
         }
         if (ok) umma_commit_pair(&tfull[acc]);
       }
+      GP_FLUSH(3, 6);
     }
     __syncwarp();
   } else {
@@ -250,6 +330,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
     const int row_in_tile = static_cast<int>(rank) * BM2 + q * 32 + lane;
     int it = 0;
     bool ok = true;
+    GP_DECL();
     for (int unit = pair; unit < num_units && ok; unit += n_pairs, ++it) {
       int mb, nb;
       tile_coords2(unit % num_tiles, m_blocks, n_blocks, mb, nb);
@@ -257,10 +338,15 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
       const bool atomic = args.splits > 1;
       const int acc = it & 1;
       const uint32_t acc_ph = (static_cast<uint32_t>(it) >> 1) & 1u;
-      if (!mbar_wait_bounded(&tfull[acc], acc_ph, args.status, 64)) {
-        ok = false;
-        break;
+      {
+        GP_T0();
+        if (!mbar_wait_bounded(&tfull[acc], acc_ph, args.status, 64)) {
+          ok = false;
+          break;
+        }
+        GP_ADD(6);
       }
+      GP_T0();
       tc_fence_after();
       const int64_t grow = static_cast<int64_t>(mb) * 2 * BM2 + row_in_tile;
       const bool row_ok = grow < args.M;
@@ -273,7 +359,27 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
         if (col0 >= args.N) break;
         float v[32];
         tmem_ld_32x32(t_row + static_cast<uint32_t>(ch * 32), v);
-        if (!row_ok) {
+        if (args.tma_out) {
+          // 32 rows x 32 columns through a 4 KB staging box (128-byte rows, 16-byte chunks XORed
+          // with the row number as the map's swizzle expects), then one TMA store / reduce-add.
+          unsigned char* buf = epi_stage + (q * 2 + (ch & 1)) * kEpiBuf;
+          if (ch >= 2 && lane == 0) bulk_wait_read<1>();   // the box sent two chunks ago has left
+          __syncwarp();
+#pragma unroll
+          for (int c = 0; c < 8; ++c)
+            *reinterpret_cast<float4*>(buf + lane * 128 + ((c ^ (lane & 7)) << 4)) =
+                make_float4(v[4 * c], v[4 * c + 1], v[4 * c + 2], v[4 * c + 3]);
+          fence_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            const int r0 = mb * 2 * BM2 + static_cast<int>(rank) * BM2 + q * 32;
+            if (r0 < args.M) {
+              if (args.tma_out == 2) tma_reduce_add_2d(&tmC, buf, col0, r0);
+              else tma_store_2d(&tmC, buf, col0, r0);
+            }
+            bulk_commit();
+          }
+        } else if (!row_ok) {
         } else if (atomic) {
           // split-K: C was zeroed (STORE / RESIDUAL) or holds the running sum (ACCUMULATE)
           const bool add_aux = first_split && args.epilogue == CTDK_EPI_RESIDUAL;
@@ -328,8 +434,15 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
       }
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive_leader(&tempty[acc]);
+      if (lane == 0) {
+        mbar_arrive_leader(&tempty[acc]);
+        if (args.tma_out) bulk_wait_read<0>();   // both staging boxes are free for the next tile
+      }
+      GP_ADD(7);
     }
+#ifdef CTDK_GEMM_PROBE
+    if (threadIdx.x == 64 && leader) { GP_FLUSH(6, 8); }
+#endif
   }
 
   tc_fence_before();
@@ -342,29 +455,31 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
 }
 
 template <bool A_MN, bool B_MN>
-int launch2(const CUtensorMap& ta, const CUtensorMap& tb, const Gemm2Args& args, cudaStream_t stream) {
+int launch2(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const Gemm2Args& args,
+            cudaStream_t stream) {
   auto* kern = gemm_tf32_2cta_kernel<A_MN, B_MN>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem2);
   if (e != cudaSuccess) return fail(CTDK_ELAUNCH, "gemm(2cta): shared memory opt-in failed: %s", cudaGetErrorString(e));
   const int tiles = ((args.M + 255) / 256) * ((args.N + BN2 - 1) / BN2) * args.splits;
   int pairs = sm_count() / 2;
   if (tiles < pairs) pairs = tiles;
-  kern<<<2 * pairs, 192, kSmem2, stream>>>(ta, tb, args);
+  kern<<<2 * pairs, 192, kSmem2, stream>>>(ta, tb, tc, args);
   return check_launch("ctdk_gemm(tcgen05, cta pair)");
 }
 
 }  // namespace
 
-// Enqueues the paired-CTA kernel; the maps must have been encoded with boxes of 128 rows for
-// K-major operands ({32, 128}) and {32, 32} for MN-major ones.
-int gemm_tcgen05_2cta(const CUtensorMap& ta, const CUtensorMap& tb, bool a_mn, bool b_mn, float* C,
-                      const float* aux, int64_t ldc, int M, int N, int K, int epilogue, int vec_ok, int splits,
-                      int* status, cudaStream_t stream) {
-  Gemm2Args args{C, aux, ldc, M, N, K, epilogue, vec_ok, splits, status};
-  if (!a_mn && !b_mn) return launch2<false, false>(ta, tb, args, stream);
-  if (!a_mn && b_mn) return launch2<false, true>(ta, tb, args, stream);
-  if (a_mn && !b_mn) return launch2<true, false>(ta, tb, args, stream);
-  return launch2<true, true>(ta, tb, args, stream);
+// Enqueues the paired-CTA kernel. K-major operands: 2-D maps with {32, 128} boxes. MN-major operands:
+// 2-D maps with {32, 32} boxes, or (a3d / b3d) 3-D maps {32 columns, K rows, columns / 32} with
+// {32, 32, 4} boxes. tc: 2-D map of C with {32, 32} boxes, used when tma_out != 0.
+int gemm_tcgen05_2cta(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, bool a_mn, bool b_mn,
+                      bool a3d, bool b3d, int tma_out, float* C, const float* aux, int64_t ldc, int M, int N, int K,
+                      int epilogue, int vec_ok, int splits, int* status, cudaStream_t stream) {
+  Gemm2Args args{C, aux, ldc, M, N, K, epilogue, vec_ok, splits, a3d ? 1 : 0, b3d ? 1 : 0, tma_out, status};
+  if (!a_mn && !b_mn) return launch2<false, false>(ta, tb, tc, args, stream);
+  if (!a_mn && b_mn) return launch2<false, true>(ta, tb, tc, args, stream);
+  if (a_mn && !b_mn) return launch2<true, false>(ta, tb, tc, args, stream);
+  return launch2<true, true>(ta, tb, tc, args, stream);
 }
 
 }  // namespace ctdk
