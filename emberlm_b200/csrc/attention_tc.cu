@@ -216,10 +216,12 @@ __global__ void __launch_bounds__(192, FwdCfg<D>::kCtasPerSm)
     __syncwarp();
   } else if (warp == 1) {
     // ------------------------------- MMA issuer -------------------------------
-    if (lane == 0) {
+    // The whole warp runs this role converged; one elected lane issues each MMA / commit.
+    {
       const uint32_t idesc_s = idesc_tf32(false, TK);
       const uint32_t idesc_pv = idesc_tf32(true, D);
-      const uint32_t q_addr = smem_u32(q_s);
+      const uint32_t k_base = smem_u32(k_s), v_base = smem_u32(v_s);
+      const uint64_t qd_ = make_smem_desc(smem_u32(q_s), 16, 1024, kLayoutSw128);
       uint32_t g0 = 0, n_it = 0;
       bool ok = true;
       PROBE_DECL();
@@ -229,26 +231,24 @@ __global__ void __launch_bounds__(192, FwdCfg<D>::kCtasPerSm)
           const uint32_t g = g0 + static_cast<uint32_t>(j), s = g & 1u;
           {
             PROBE_T0();
-            if (!mbar_wait_bounded(&k_full[s], (g >> 1) & 1u, args.status, 22)) return false;
+            if (!mbar_wait_bounded_w(&k_full[s], (g >> 1) & 1u, args.status, 22)) return false;
             PROBE_ADD(1);
           }
           tc_fence_after();
-          const uint32_t k_addr = smem_u32(k_s + s * C::kKBytes);
+          const uint64_t kd = make_smem_desc(k_base + s * C::kKBytes, 16, 1024, kLayoutSw128);
+          const uint32_t ts = tm_s(g);
 #pragma unroll
-          for (int ks = 0; ks < D / 8; ++ks) {
-            umma_tf32(tm_s(g),
-                      make_smem_desc(q_addr + (ks >> 2) * kQChunk + (ks & 3) * 32, 16, 1024, kLayoutSw128),
-                      make_smem_desc(k_addr + (ks >> 2) * kKChunk + (ks & 3) * 32, 16, 1024, kLayoutSw128),
-                      idesc_s, ks != 0 ? 1u : 0u);
-          }
-          umma_commit(&k_empty[s]);
-          umma_commit(&s_full[s]);
-          if (j == w.n_steps - 1) umma_commit(q_empty);   // the item's last use of Q
+          for (int ks = 0; ks < D / 8; ++ks)   // descriptor address field counts 16-byte units
+            umma_tf32_w(ts, qd_ + (((ks >> 2) * kQChunk + (ks & 3) * 32) >> 4),
+                        kd + (((ks >> 2) * kKChunk + (ks & 3) * 32) >> 4), idesc_s, ks != 0 ? 1u : 0u);
+          umma_commit_w(&k_empty[s]);
+          umma_commit_w(&s_full[s]);
+          if (j == w.n_steps - 1) umma_commit_w(q_empty);   // the item's last use of Q
           return true;
         };
         {
           PROBE_T0();
-          if (!mbar_wait_bounded(q_full, n_it & 1u, args.status, 21)) break;
+          if (!mbar_wait_bounded_w(q_full, n_it & 1u, args.status, 21)) break;
           PROBE_ADD(0);
         }
         tc_fence_after();
@@ -260,32 +260,31 @@ __global__ void __launch_bounds__(192, FwdCfg<D>::kCtasPerSm)
           const uint32_t g = g0 + static_cast<uint32_t>(j), s = g & 1u, ph = (g >> 1) & 1u;
           {
             PROBE_T0();
-            if (!mbar_wait_bounded(&p_ready[s], ph, args.status, 23)) { ok = false; break; }
+            if (!mbar_wait_bounded_w(&p_ready[s], ph, args.status, 23)) { ok = false; break; }
             PROBE_ADD(2);
           }
           {
             PROBE_T0();
-            if (!mbar_wait_bounded(&v_full[s], ph, args.status, 24)) { ok = false; break; }
+            if (!mbar_wait_bounded_w(&v_full[s], ph, args.status, 24)) { ok = false; break; }
             PROBE_ADD(3);
           }
           tc_fence_after();
-          const uint32_t v_addr = smem_u32(v_s + s * C::kKBytes);
+          // A: 8 probability columns of tensor memory; B: 8 key rows (two 4-row swizzle
+          // groups, SBO 512) of every 32-float chunk of V (chunks kKChunk apart, LBO).
+          const uint64_t vd = make_smem_desc(v_base + s * C::kKBytes, kKChunk, 512, kLayoutSw128Base32);
+          const uint32_t ts = tm_s(g);
+          const uint32_t acc0 = j != 0 ? 1u : 0u;
 #pragma unroll
-          for (int ks = 0; ks < TK / 8; ++ks) {
-            // A: 8 probability columns of tensor memory; B: 8 key rows (two 4-row swizzle
-            // groups, SBO 512) of every 32-float chunk of V (chunks kKChunk apart, LBO).
-            umma_tf32_ta(tm_o, tm_s(g) + static_cast<uint32_t>(ks * 8),
-                         make_smem_desc(v_addr + ks * 1024, kKChunk, 512, kLayoutSw128Base32), idesc_pv,
-                         (j != 0 || ks != 0) ? 1u : 0u);
-          }
-          umma_commit(&v_empty[s]);
-          umma_commit(pv_full);
-          if (j == w.n_steps - 1) umma_commit(o_full);
+          for (int ks = 0; ks < TK / 8; ++ks)
+            umma_tf32_ta_w(tm_o, ts + static_cast<uint32_t>(ks * 8), vd + ((ks * 1024) >> 4), idesc_pv, ks != 0 ? 1u : acc0);
+          umma_commit_w(&v_empty[s]);
+          umma_commit_w(pv_full);
+          if (j == w.n_steps - 1) umma_commit_w(o_full);
           if (j + 2 < w.n_steps) ok = issue_s(j + 2);
         }
         g0 += static_cast<uint32_t>(w.n_steps);
       }
-      PROBE_FLUSH(0, 4);
+      if (lane == 0) { PROBE_FLUSH(0, 4); }
     }
     __syncwarp();
   } else {

@@ -14,6 +14,7 @@
 // Operands that are needed both K-major and MN-major (K in the dQ kernel; Q and dO in the dK/dV
 // kernel) are loaded twice by TMA, once per swizzle layout. Every mbarrier wait is bounded.
 #include <cfloat>
+#include <cstdlib>
 
 #include "common.cuh"
 
@@ -294,12 +295,26 @@ int launch_dq(const float* qkv, const float* dout, const BwdArgs& a, int64_t B, 
 
 }  // namespace
 
+// Head size 64: persistent kernels with the left-hand operands in tensor memory (attention_tc_bwd64.cu).
+int attn_bwd_dq_tc64(const float* qkv, const float* dout, const float* lse, const float* delta, float* dqkv,
+                     int64_t B, int64_t T, int H, int Hk, cudaStream_t stream);
+int attn_bwd_dkv_tc64(const float* qkv, const float* dout, const float* lse, const float* delta, float* dqkv,
+                      int64_t B, int64_t T, int H, int Hk, cudaStream_t stream);
+static bool bwd64_off() {
+  static const bool off = [] {
+    const char* e = getenv("CTDK_ATTN_BWD_GENERIC");
+    return e != nullptr && e[0] == '1';
+  }();
+  return off;
+}
+
 // dQ part of the backward. Returns CTDK_OK, a negative status, or 1 when not eligible.
 int attn_bwd_dq_tcgen05(const float* qkv, const float* dout, const float* lse, const float* delta, float* dqkv,
                         int64_t B, int64_t T, int H, int Hk, int D, cudaStream_t stream) {
   if ((reinterpret_cast<uintptr_t>(qkv) & 15u) || (reinterpret_cast<uintptr_t>(dout) & 15u) ||
       (reinterpret_cast<uintptr_t>(dqkv) & 15u))
     return 1;
+  if (D == 64 && !bwd64_off()) return attn_bwd_dq_tc64(qkv, dout, lse, delta, dqkv, B, T, H, Hk, stream);
   BwdArgs a;
   a.lse = lse;
   a.delta = delta;
@@ -591,6 +606,7 @@ int attn_bwd_dkv_tcgen05(const float* qkv, const float* dout, const float* lse, 
   if ((reinterpret_cast<uintptr_t>(qkv) & 15u) || (reinterpret_cast<uintptr_t>(dout) & 15u) ||
       (reinterpret_cast<uintptr_t>(dqkv) & 15u))
     return 1;
+  if (D == 64 && !bwd64_off()) return attn_bwd_dkv_tc64(qkv, dout, lse, delta, dqkv, B, T, H, Hk, stream);
   BwdArgs a;
   a.lse = lse;
   a.delta = delta;
