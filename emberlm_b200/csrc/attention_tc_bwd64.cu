@@ -73,6 +73,7 @@ struct Bwd64Args {
   int n_items;
   float scale;
   int* status;
+  int* work_counter;   // dK/dV kernel: next unclaimed item (zeroed before the launch)
 };
 
 // Copies this thread's row (64 floats, 256 bytes) of a {2 x [128 rows x 128 bytes]} tile with the
@@ -438,7 +439,8 @@ __global__ void __launch_bounds__(320, 1)
                           const __grid_constant__ CUtensorMap tm_dok,   // dout {32, 64, 2, 1} 16-byte swizzle
                           const __grid_constant__ CUtensorMap tm_qm,    // qkv  {32, 64, 2, 1} 32-byte swizzle
                           const __grid_constant__ CUtensorMap tm_dom,   // dout {32, 64, 2, 1} 32-byte swizzle
-                          const float* __restrict__ qkv, const Bwd64Args args) {
+                          const __grid_constant__ CUtensorMap tm_kvt,   // qkv  {32, 128, 2, 1} 16-byte swizzle (K, V tiles)
+                          const Bwd64Args args) {
   extern __shared__ unsigned char smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   unsigned char* smem = smem_raw + ((1024u - (raw & 1023u)) & 1023u);
@@ -456,7 +458,10 @@ __global__ void __launch_bounds__(320, 1)
   uint64_t* pds_ready = bars + 15;   // [2]  P^T and dS^T are in place (256 arrivals)
   uint64_t* done_bar = bars + 17;    // 1    the item's last dV / dK MMA has finished
   uint64_t* const_full = bars + 18;  // [3]  the unit's per-query constants are in shared memory (128 arrivals)
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 21);
+  uint64_t* iq_full = bars + 21;     // [2]  work queue: item number published by the producer
+  uint64_t* iq_empty = bars + 23;    // [2]  ... and read by the MMA warp (1) and every compute thread (256)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 25);
+  volatile int* item_q = reinterpret_cast<volatile int*>(tmem_slot + 1);   // [2]
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int G = args.H / args.Hk;
@@ -474,6 +479,8 @@ __global__ void __launch_bounds__(320, 1)
     for (int i = 0; i < 2; ++i) {
       mbar_init(&sdp_full[i], 1);
       mbar_init(&pds_ready[i], 256);
+      mbar_init(&iq_full[i], 1);
+      mbar_init(&iq_empty[i], 257);
     }
     mbar_init(done_bar, 1);
     mbar_fence_init();
@@ -481,6 +488,7 @@ __global__ void __launch_bounds__(320, 1)
     tma_prefetch_desc(&tm_dok);
     tma_prefetch_desc(&tm_qm);
     tma_prefetch_desc(&tm_dom);
+    tma_prefetch_desc(&tm_kvt);
   }
   if (warp == 1) {
     tmem_alloc(tmem_slot, 512);
@@ -493,17 +501,42 @@ __global__ void __launch_bounds__(320, 1)
   const uint32_t tm_ka = tmem_base, tm_va = tmem_base + 64u, tm_dv = tmem_base + 128u, tm_dk = tmem_base + 192u;
   auto tm_s = [&](uint32_t g) { return tmem_base + 256u + (g & 1u) * 128u; };    // S^T, later P^T
   auto tm_dp = [&](uint32_t g) { return tmem_base + 320u + (g & 1u) * 128u; };   // dP^T, later dS^T
-  // g = running count of units over all items of this CTA: stage g % 3, score buffer g & 1.
+  // Two running counts over all items of this CTA: r numbers the entries of the 3-stage operand
+  // ring (the item's K / V tiles take one entry, then one per unit); g numbers the units (score
+  // buffer g & 1, constant buffer g % 3).
 
   if (warp == 0) {
     // ------------------------------- TMA producer -------------------------------
     if (lane == 0) {
-      uint32_t g0 = 0;
+      // Items differ in length by up to 8x (a key tile meets between 2 and 16 query blocks per
+      // head), so they are claimed one at a time from a global counter, in batch-major order with
+      // the longest items of a sequence first, and published to the other warps through a
+      // two-entry queue in shared memory.
+      uint32_t r0 = 0;
       bool ok = true;
-      for (int it = blockIdx.x; it < args.n_items && ok; it += gridDim.x) {
+      for (uint32_t n = 0; ok; ++n) {
+        const uint32_t slot = n & 1u;
+        if (!mbar_wait_bounded(&iq_empty[slot], ((n >> 1) & 1u) ^ 1u, args.status, 50)) break;
+        int it = atomicAdd(args.work_counter, 1);
+        if (it >= args.n_items) it = -1;
+        item_q[slot] = it;
+        mbar_arrive(&iq_full[slot]);
+        if (it < 0) break;
         const KvItem w = kv_item(args, it);
+        {
+          // the item's K and V tiles land in one ring entry (K in the first half, V in the
+          // second) and are moved to tensor memory by the compute warps
+          const uint32_t st = r0 % kKvStages, ph = (r0 / kKvStages) & 1u;
+          unsigned char* sb = stages + st * kKvStageBytes;
+          if (!mbar_wait_bounded(&qk_empty[st], ph ^ 1u, args.status, 51)) break;
+          mbar_expect_tx(&qk_full[st], kRowTileBytes);
+          tma_load_4d(sb, &tm_kvt, &qk_full[st], 0, w.k0, ((args.H + w.hk) * D) >> 5, w.b);
+          if (!mbar_wait_bounded(&qm_empty[st], ph ^ 1u, args.status, 52)) break;
+          mbar_expect_tx(&qm_full[st], kRowTileBytes);
+          tma_load_4d(sb + kRowTileBytes, &tm_kvt, &qm_full[st], 0, w.k0, ((args.H + args.Hk + w.hk) * D) >> 5, w.b);
+        }
         for (int u = 0; u < w.n_units && ok; ++u) {
-          const uint32_t g = g0 + static_cast<uint32_t>(u), st = g % kKvStages, ph = (g / kKvStages) & 1u;
+          const uint32_t g = r0 + 1u + static_cast<uint32_t>(u), st = g % kKvStages, ph = (g / kKvStages) & 1u;
           const int gi = u / w.per_head;
           const int q0 = (w.first_qt + (u - gi * w.per_head)) * TN;
           const int chunk_q = ((w.hk * G + gi) * D) >> 5;
@@ -517,7 +550,7 @@ __global__ void __launch_bounds__(320, 1)
           tma_load_4d(sb + 2 * kColTileBytes, &tm_qm, &qm_full[st], 0, q0, chunk_q, w.b);
           tma_load_4d(sb + 3 * kColTileBytes, &tm_dom, &qm_full[st], 0, q0, chunk_q, w.b);
         }
-        g0 += static_cast<uint32_t>(w.n_units);
+        r0 += static_cast<uint32_t>(w.n_units) + 1u;
       }
     }
     __syncwarp();
@@ -527,16 +560,21 @@ __global__ void __launch_bounds__(320, 1)
     {
       const uint32_t id_k = idesc64(false), id_mn = idesc64(true);
       const uint32_t stages_addr = smem_u32(stages);
-      uint32_t g0 = 0, n_it = 0;
+      uint32_t g0 = 0, r0 = 0, n_it = 0;
       bool ok = true;
       BP_DECL();
-      for (int it = blockIdx.x; it < args.n_items && ok; it += gridDim.x, ++n_it) {
+      for (;; ++n_it) {
+        if (!mbar_wait_bounded_w(&iq_full[n_it & 1u], (n_it >> 1) & 1u, args.status, 60)) break;
+        const int it = item_q[n_it & 1u];
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&iq_empty[n_it & 1u]);
+        if (it < 0 || !ok) break;
         const KvItem w = kv_item(args, it);
         auto issue_sdp = [&](int u) {
-          const uint32_t g = g0 + static_cast<uint32_t>(u), st = g % kKvStages;
+          const uint32_t g = g0 + static_cast<uint32_t>(u), r = r0 + 1u + static_cast<uint32_t>(u), st = r % kKvStages;
           {
             BP_T0();
-            if (!mbar_wait_bounded_w(&qk_full[st], (g / kKvStages) & 1u, args.status, 54)) return false;
+            if (!mbar_wait_bounded_w(&qk_full[st], (r / kKvStages) & 1u, args.status, 54)) return false;
             BP_ADD(1);
           }
           tc_fence_after();
@@ -561,10 +599,15 @@ __global__ void __launch_bounds__(320, 1)
           BP_ADD(0);
         }
         tc_fence_after();
+        if (lane == 0) {   // K and V sit in tensor memory: their ring entry is free again
+          mbar_arrive(&qk_empty[r0 % kKvStages]);
+          mbar_arrive(&qm_empty[r0 % kKvStages]);
+        }
+        __syncwarp();
         ok = issue_sdp(0);
         if (ok && w.n_units > 1) ok = issue_sdp(1);
         for (int u = 0; u < w.n_units && ok; ++u) {
-          const uint32_t g = g0 + static_cast<uint32_t>(u), st = g % kKvStages;
+          const uint32_t g = g0 + static_cast<uint32_t>(u), r = r0 + 1u + static_cast<uint32_t>(u), st = r % kKvStages;
           {
             BP_T0();
             if (!mbar_wait_bounded_w(&pds_ready[g & 1u], (g >> 1) & 1u, args.status, 55)) { ok = false; break; }
@@ -572,7 +615,7 @@ __global__ void __launch_bounds__(320, 1)
           }
           {
             BP_T0();
-            if (!mbar_wait_bounded_w(&qm_full[st], (g / kKvStages) & 1u, args.status, 56)) { ok = false; break; }
+            if (!mbar_wait_bounded_w(&qm_full[st], (r / kKvStages) & 1u, args.status, 56)) { ok = false; break; }
             BP_ADD(3);
           }
           tc_fence_after();
@@ -593,6 +636,7 @@ __global__ void __launch_bounds__(320, 1)
           if (u + 2 < w.n_units) ok = issue_sdp(u + 2);
         }
         g0 += static_cast<uint32_t>(w.n_units);
+        r0 += static_cast<uint32_t>(w.n_units) + 1u;
       }
       if (lane == 0) { BP_FLUSH(16, 0, 4); }
     }
@@ -607,10 +651,14 @@ __global__ void __launch_bounds__(320, 1)
     const uint32_t lane_off = static_cast<uint32_t>(qd * 32) << 16;
     const float sc2 = args.scale * kLog2ef;
     float* stg = reinterpret_cast<float*>(o_stage + cw * 2048);
-    uint32_t g0 = 0, n_it = 0;
+    uint32_t g0 = 0, r0 = 0, n_it = 0;
     bool ok = true;
     BP_DECL();
-    for (int it = blockIdx.x; it < args.n_items && ok; it += gridDim.x, ++n_it) {
+    for (;; ++n_it) {
+      if (!mbar_wait_bounded(&iq_full[n_it & 1u], (n_it >> 1) & 1u, args.status, 61)) break;
+      const int it = item_q[n_it & 1u];
+      mbar_arrive(&iq_empty[n_it & 1u]);
+      if (it < 0 || !ok) break;
       const KvItem w = kv_item(args, it);
       const int key = w.k0 + qd * 32 + lane;
       const int col_k = (args.H + w.hk) * D, col_v = (args.H + args.Hk + w.hk) * D;
@@ -627,29 +675,15 @@ __global__ void __launch_bounds__(320, 1)
         return r;
       };
       float next_const = fetch_const(0);
-      // K (first warp of the pair) or V (second) row of this thread: global -> tensor memory,
-      // rounded to TF32 like the operands TMA delivers.
+      // K (first warp of the pair) or V (second) row of this thread: shared -> tensor memory.
+      // The tensor-memory copies of the previous item are free: its last MMA was awaited below.
       {
         BP_T0();
+        const uint32_t st = r0 % kKvStages, ph = (r0 / kKvStages) & 1u;
+        if (!mbar_wait_bounded(half == 0 ? &qk_full[st] : &qm_full[st], ph, args.status, 62)) { ok = false; break; }
         float v[64];
-        const float* src = qkv + (static_cast<int64_t>(w.b) * args.T + key) * RS + (half == 0 ? col_k : col_v);
-        if (key < args.T) {
-#pragma unroll
-          for (int c = 0; c < 16; ++c) {
-            const float4 x = __ldg(reinterpret_cast<const float4*>(src) + c);
-            v[4 * c] = x.x;
-            v[4 * c + 1] = x.y;
-            v[4 * c + 2] = x.z;
-            v[4 * c + 3] = x.w;
-          }
-        } else {
-#pragma unroll
-          for (int c = 0; c < 64; ++c) v[c] = 0.0f;
-        }
-        uint32_t* vb = reinterpret_cast<uint32_t*>(v);
-#pragma unroll
-        for (int c = 0; c < 64; ++c) vb[c] = rna_bits(v[c]);
-        tmem_st_32x64((half == 0 ? tm_ka : tm_va) + lane_off, *reinterpret_cast<uint32_t(*)[64]>(vb));
+        load_row_sw128(stages + st * kKvStageBytes + half * kRowTileBytes, qd * 32 + lane, v);
+        tmem_st_32x64((half == 0 ? tm_ka : tm_va) + lane_off, *reinterpret_cast<uint32_t(*)[64]>(v));
         tmem_wait_st();
         BP_ADD(5);
       }
@@ -733,6 +767,7 @@ __global__ void __launch_bounds__(320, 1)
         BP_CNT(10);
       }
       g0 += static_cast<uint32_t>(w.n_units);
+      r0 += static_cast<uint32_t>(w.n_units) + 1u;
       {
         BP_T0();
         if (!ok || !mbar_wait_bounded(done_bar, n_it & 1u, args.status, 58)) { ok = false; break; }
@@ -795,6 +830,7 @@ int attn_bwd_dq_tc64(const float* qkv, const float* dout, const float* lse, cons
   a.n_items = static_cast<int>(items);
   a.scale = 1.0f / sqrtf(static_cast<float>(D));
   a.status = device_status_word();
+  a.work_counter = nullptr;
   if (a.status == nullptr) return fail(CTDK_ELAUNCH, "attn_bwd(tcgen05): no status word");
   CUtensorMap tq, tdo, tkv, tkm;
   int rc = map4(&tq, qkv, RS, T, B, TM, D / 32, false);
@@ -817,6 +853,10 @@ int attn_bwd_dq_tc64(const float* qkv, const float* dout, const float* lse, cons
   return check_launch("ctdk_attn_bwd(dq, tcgen05)");
 }
 
+namespace {
+__device__ int g_kv_work_counter;
+}  // namespace
+
 // dK/dV part of the backward for D = 64. Returns CTDK_OK or a negative status.
 int attn_bwd_dkv_tc64(const float* qkv, const float* dout, const float* lse, const float* delta, float* dqkv,
                       int64_t B, int64_t T, int H, int Hk, cudaStream_t stream) {
@@ -836,8 +876,17 @@ int attn_bwd_dkv_tc64(const float* qkv, const float* dout, const float* lse, con
   a.scale = 1.0f / sqrtf(static_cast<float>(D));
   a.status = device_status_word();
   if (a.status == nullptr) return fail(CTDK_ELAUNCH, "attn_bwd(tcgen05): no status word");
-  CUtensorMap tqk, tdok, tqm, tdom;
+  {
+    void* cptr = nullptr;
+    if (cudaGetSymbolAddress(&cptr, g_kv_work_counter) != cudaSuccess || cptr == nullptr)
+      return fail(CTDK_ELAUNCH, "attn_bwd dkv(tcgen05): no work counter");
+    a.work_counter = static_cast<int*>(cptr);
+    if (cudaMemsetAsync(cptr, 0, sizeof(int), stream) != cudaSuccess)
+      return fail(CTDK_ELAUNCH, "attn_bwd dkv(tcgen05): counter reset failed");
+  }
+  CUtensorMap tqk, tdok, tqm, tdom, tkvt;
   int rc = map4(&tqk, qkv, RS, T, B, TN, D / 32, false);
+  if (rc == CTDK_OK) rc = map4(&tkvt, qkv, RS, T, B, TM, D / 32, false);
   if (rc == CTDK_OK) rc = map4(&tdok, dout, HD, T, B, TN, D / 32, false);
   if (rc == CTDK_OK) rc = map4(&tqm, qkv, RS, T, B, TN, D / 32, true);
   if (rc == CTDK_OK) rc = map4(&tdom, dout, HD, T, B, TN, D / 32, true);
@@ -845,7 +894,7 @@ int attn_bwd_dkv_tc64(const float* qkv, const float* dout, const float* lse, con
   cudaError_t e = cudaFuncSetAttribute(attn_bwd_dkv64_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kKvSmem);
   if (e != cudaSuccess) return fail(CTDK_ELAUNCH, "attn_bwd dkv(tcgen05): shared memory opt-in failed: %s", cudaGetErrorString(e));
   const int sms = sm_count();
-  attn_bwd_dkv64_kernel<<<a.n_items < sms ? a.n_items : sms, 320, kKvSmem, stream>>>(tqk, tdok, tqm, tdom, qkv, a);
+  attn_bwd_dkv64_kernel<<<a.n_items < sms ? a.n_items : sms, 320, kKvSmem, stream>>>(tqk, tdok, tqm, tdom, tkvt, a);
   return check_launch("ctdk_attn_bwd(dkv, tcgen05)");
 }
 
