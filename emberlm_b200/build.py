@@ -1,9 +1,10 @@
-"""Builds libctdk.so (the sm_100a kernels + C-ABI) in-tree with nvcc.
+"""Builds libctdk.so (the sm_100a kernels + C-ABI) and the command-line tools in-tree with nvcc.
 
 Usage: python -m emberlm_b200.build [--force] [--verbose]
 Every .cu / .cpp file under csrc/ is compiled to an object next to this file's build/
 directory and linked into emberlm_b200/libctdk.so. Objects are rebuilt only when their
-source (or a header) is newer.
+source (or a header) is newer. Each cli/*.cpp becomes an executable of the same name next to the
+library (emberlm_b200/ctd_train), linked against it with an $ORIGIN run path.
 """
 from __future__ import annotations
 
@@ -67,7 +68,23 @@ def build(force: bool = False, verbose: bool = False) -> Path:
         r = subprocess.run(cmd, capture_output=True, text=True)
         if r.returncode != 0:
             raise RuntimeError(f"link failed:\n{r.stdout}\n{r.stderr}")
+    _build_tools(force)
     return LIB
+
+
+def _build_tools(force: bool) -> None:
+    cli = HERE / "cli"
+    hdrs = list(cli.glob("*.hpp")) + list((HERE.parent / "include").glob("*.h"))
+    newest_hdr = max((h.stat().st_mtime for h in hdrs), default=0.0)
+    for src in sorted(cli.glob("*.cpp")):
+        exe = HERE / src.stem
+        if not force and exe.exists() and exe.stat().st_mtime >= max(src.stat().st_mtime, newest_hdr, LIB.stat().st_mtime):
+            continue
+        cmd = [NVCC, "-O2", "-std=c++17", "-Xcompiler", "-Wall", "-o", str(exe), str(src), "-L", str(HERE), "-lctdk",
+               "-lcudart", "-Xlinker", "-rpath", "-Xlinker", "$ORIGIN"]
+        r = subprocess.run(cmd, capture_output=True, text=True)
+        if r.returncode != 0:
+            raise RuntimeError(f"building {src.name} failed:\n{r.stdout}\n{r.stderr}")
 
 
 if __name__ == "__main__":

@@ -191,7 +191,10 @@ __global__ void __launch_bounds__(320, 1)
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  const uint32_t tm_qa = tmem_base, tm_doa = tmem_base + 64u, tm_dq = tmem_base + 128u;
+  const uint32_t tm_qa = tmem_base, tm_doa = tmem_base + 64u;
+  // two dQ accumulators (items alternate), so that an item's result is read and stored while the
+  // next item's first MMAs are already running
+  auto tm_dq = [&](uint32_t n) { return tmem_base + ((n & 1u) ? 448u : 128u); };
   auto tm_s = [&](uint32_t g) { return tmem_base + 192u + (g & 1u) * 128u; };    // S, later dS
   auto tm_dp = [&](uint32_t g) { return tmem_base + 256u + (g & 1u) * 128u; };   // dP
   // g = running count of key steps over all items of this CTA: stage g % 3, score buffer g & 1.
@@ -288,11 +291,11 @@ __global__ void __launch_bounds__(320, 1)
           tc_fence_after();
           const uint64_t kmd =
               make_smem_desc(stages_addr + st * kDqStageBytes + 2 * kColTileBytes, kColChunk, 512, kLayoutSw128Base32);
-          const uint32_t ts = tm_s(g);
+          const uint32_t ts = tm_s(g), tdq = tm_dq(n_it);
           const uint32_t acc0 = j != 0 ? 1u : 0u;
 #pragma unroll
           for (int ks = 0; ks < TN / 8; ++ks)
-            umma_tf32_ta_w(tm_dq, ts + static_cast<uint32_t>(ks * 8), kmd + ((ks * 1024) >> 4), id_mn, ks != 0 ? 1u : acc0);
+            umma_tf32_ta_w(tdq, ts + static_cast<uint32_t>(ks * 8), kmd + ((ks * 1024) >> 4), id_mn, ks != 0 ? 1u : acc0);
           umma_commit_w(&km_empty[st]);
           if (j == w.n_steps - 1) umma_commit_w(dq_done);
           if (j + 2 < w.n_steps) ok = issue_sdp(j + 2);
@@ -314,6 +317,28 @@ __global__ void __launch_bounds__(320, 1)
     uint32_t g0 = 0, n_it = 0;
     bool ok = true;
     BP_DECL();
+    const int64_t RS = static_cast<int64_t>(args.H + 2 * args.Hk) * D;
+    // Reads item n's finished dQ out of its accumulator and stores it. Runs after the NEXT item's
+    // Q / dO have been handed to the MMA warp, i.e. while that item's first S / dP MMAs execute.
+    auto epilogue = [&](const DqItem& w, uint32_t n) {
+      {
+        BP_T0();
+        if (!mbar_wait_bounded(dq_done, n & 1u, args.status, 49)) return false;
+        BP_ADD(8);
+      }
+      BP_T0();
+      tc_fence_after();
+      float v[32];
+      tmem_ld_32x32(tm_dq(n) + lane_off + static_cast<uint32_t>(half * 32), v);
+      float* dst = args.dqkv + (static_cast<int64_t>(w.b) * args.T + w.q0 + qd * 32) * RS + w.h * D + half * 32;
+      store_block_32x32(stg, v, dst, RS, args.T - (w.q0 + qd * 32), lane);
+      tc_fence_before();
+      BP_ADD(9);
+      BP_CNT(11);
+      return true;
+    };
+    DqItem prev{};
+    bool have_prev = false;
     for (int it = blockIdx.x; it < args.n_items && ok; it += gridDim.x, ++n_it) {
       const DqItem w = dq_item(args, it);
       const int row = w.q0 + qd * 32 + lane;
@@ -337,6 +362,7 @@ __global__ void __launch_bounds__(320, 1)
       }
       tc_fence_before();
       mbar_arrive(qdo_ready);
+      if (have_prev && !epilogue(prev, n_it - 1u)) { ok = false; break; }
       for (int j = 0; j < w.n_steps && ok; ++j) {
         const uint32_t g = g0 + static_cast<uint32_t>(j);
         {
@@ -377,24 +403,10 @@ __global__ void __launch_bounds__(320, 1)
         BP_CNT(10);
       }
       g0 += static_cast<uint32_t>(w.n_steps);
-      {
-        BP_T0();
-        if (!ok || !mbar_wait_bounded(dq_done, n_it & 1u, args.status, 49)) { ok = false; break; }
-        BP_ADD(8);
-      }
-      BP_T0();
-      tc_fence_after();
-      {
-        float v[32];
-        tmem_ld_32x32(tm_dq + lane_off + static_cast<uint32_t>(half * 32), v);
-        const int64_t RS = static_cast<int64_t>(args.H + 2 * args.Hk) * D;
-        float* dst = args.dqkv + (static_cast<int64_t>(w.b) * args.T + w.q0 + qd * 32) * RS + w.h * D + half * 32;
-        store_block_32x32(stg, v, dst, RS, args.T - (w.q0 + qd * 32), lane);
-      }
-      tc_fence_before();
-      BP_ADD(9);
-      BP_CNT(11);
+      prev = w;
+      have_prev = true;
     }
+    if (ok && have_prev) epilogue(prev, n_it - 1u);
 #ifdef CTDK_ATTN_PROBE
     if (threadIdx.x == 64) { BP_FLUSH(0, 4, 12); }
 #endif

@@ -131,6 +131,49 @@ def shard_bounds(total_padded: int, world: int, rank: int) -> tuple[int, int]:
     return rank * shard, (rank + 1) * shard
 
 
+def tensor_layer(name: str, num_layers: int) -> int:
+    """Backward-completion index of a parameter: the layer number for decoder-layer tensors,
+    num_layers for the final norm, -1 for the (tied) embedding, whose gradient is final only after
+    the embedding backward at the very end (the layer callback of the engine uses the same
+    numbering)."""
+    if name.startswith("model.layers."):
+        return int(name.split(".")[2])
+    return num_layers if name == "model.norm.weight" else -1
+
+
+def make_buckets(layout: Layout, total_padded: int, world: int, num_layers: int, layers_per_bucket: int = 4):
+    """Cuts the arena into contiguous buckets [lo, hi) whose lengths are multiples of 64 * world:
+    the embedding, then groups of `layers_per_bucket` decoder layers (the last one also takes the
+    final norm and the padding). Cuts are rounded down to the unit, so a bucket may begin inside the
+    last tensor of the previous group. Returns [(lo, hi, ready)] in arena order; `ready` is the
+    lowest completion index (see tensor_layer) of the tensors the bucket overlaps: the bucket's
+    gradients are final once the layer callback has fired for `ready` (backward runs from the
+    last layer down to the embedding). Rank r owns slice r of every bucket."""
+    unit = 64 * world
+    layer_of = [tensor_layer(n, num_layers) for n in layout.names]
+    first = {}
+    for o, l in zip(layout.offsets, layer_of):
+        first[l] = min(first.get(l, o), o)
+    cuts = [0]
+    for l in range(0, num_layers, max(1, layers_per_bucket)):
+        c = first[l] // unit * unit
+        if c > cuts[-1]:
+            cuts.append(c)
+    cuts.append(total_padded)
+    out = []
+    for lo, hi in zip(cuts[:-1], cuts[1:]):
+        ready = min((l for o, k, l in zip(layout.offsets, layout.numels, layer_of) if o < hi and o + k > lo),
+                    default=num_layers)
+        out.append((lo, hi, ready))
+    return out
+
+
+def bucket_slice(lo: int, hi: int, world: int, rank: int) -> tuple[int, int]:
+    """Arena range of bucket [lo, hi) that `rank` owns."""
+    n = (hi - lo) // world
+    return lo + rank * n, lo + (rank + 1) * n
+
+
 def deal_micro_batches(accum: int, world: int, rank: int) -> list[int]:
     """The step's `accum` micro-batches are dealt round-robin: rank r runs r, r+world, ..."""
     if accum % world:
@@ -229,11 +272,14 @@ class TrainEngine:
         self.hp = dict(lr=lr, beta1=beta1, beta2=beta2, eps=eps, weight_decay=weight_decay, clip=clip)
         self.step_count = 0
         self._cb = None
+        self._user_cb = None
         if train:
             self.m = torch.zeros(self.shard, dtype=torch.float32, device=self.device)
             self.v = torch.zeros(self.shard, dtype=torch.float32, device=self.device)
             self._scalars = torch.zeros(4, dtype=torch.float32, device=self.device)  # sumsq, scale, norm
             self._build_segments()
+            if self.world > 1:
+                self._install_bucket_callback()
 
     def __del__(self):
         h = getattr(self, "_h", None)
@@ -271,13 +317,53 @@ class TrainEngine:
                 v.fill_(1.0)
 
     def _build_segments(self) -> None:
-        ends, wds = build_segments(self.layout, self.hp["weight_decay"], self.rank * self.shard,
-                                   (self.rank + 1) * self.shard)
-        self.seg_end = torch.tensor(ends, dtype=torch.int64, device=self.device)
-        self.seg_wd = torch.tensor(wds, dtype=torch.float32, device=self.device)
+        """One rank: one segment table over the whole arena. Several ranks: the arena is cut into
+        buckets (make_buckets), rank r owns slice r of each; m / v hold the slices back to back and
+        every slice has its own weight-decay segment table."""
+        wd = self.hp["weight_decay"]
+        if self.world == 1:
+            ends, wds = build_segments(self.layout, wd, 0, self.total)
+            self.seg_end = torch.tensor(ends, dtype=torch.int64, device=self.device)
+            self.seg_wd = torch.tensor(wds, dtype=torch.float32, device=self.device)
+            self.buckets = []
+            return
+        self.buckets = []
+        pos = 0
+        for lo, hi, ready in make_buckets(self.layout, self.total, self.world, self.cfg.num_hidden_layers):
+            a, b = bucket_slice(lo, hi, self.world, self.rank)
+            ends, wds = build_segments(self.layout, wd, a, b)
+            self.buckets.append(dict(
+                lo=lo, hi=hi, ready=ready, a=a, b=b, state=pos,
+                seg_end=torch.tensor(ends, dtype=torch.int64, device=self.device),
+                seg_wd=torch.tensor(wds, dtype=torch.float32, device=self.device), work=None))
+            pos += b - a
+        assert pos == self.shard
+
+    def _install_bucket_callback(self) -> None:
+        """Reduce-scatter of a bucket starts as soon as the backward kernels of the last layer it
+        needs have been enqueued: the collective runs on the process group's own stream behind an
+        event on the compute stream, so it overlaps the backward of the layers below."""
+        import torch.distributed as dist
+
+        def on_layer(layer: int) -> None:
+            if self._user_cb is not None:
+                self._user_cb(layer)
+            if not self._reduce_in_backward:
+                return
+            for bk in self.buckets:
+                if bk["ready"] == layer and bk["work"] is None:
+                    bk["work"] = dist.reduce_scatter_tensor(self.grads[bk["a"]:bk["b"]], self.grads[bk["lo"]:bk["hi"]],
+                                                            op=dist.ReduceOp.SUM, group=self.group, async_op=True)
+
+        self._reduce_in_backward = False
+        self._cb = LAYER_CALLBACK(lambda layer, _u: on_layer(layer))
+        lib.check(_L.ctdk_engine_set_layer_callback(self._h, self._cb, None))
 
     # ---- step -------------------------------------------------------------------------
     def set_layer_callback(self, fn) -> None:
+        if self.world > 1 and self.grads is not None:
+            self._user_cb = fn          # chained in front of the gradient-bucket callback
+            return
         self._cb = LAYER_CALLBACK(lambda layer, _u: fn(layer)) if fn else LAYER_CALLBACK(0)
         lib.check(_L.ctdk_engine_set_layer_callback(self._h, self._cb, None))
 
@@ -288,11 +374,17 @@ class TrainEngine:
         n = 0 if rows is None else rows.numel()
         lib.check(_L.ctdk_engine_set_active_rows(self._h, rows.data_ptr() if n else None, n))
 
-    def forward_backward(self, ids, targets, loss_mask, row_weight, accumulate=False) -> None:
+    def forward_backward(self, ids, targets, loss_mask, row_weight, accumulate=False, last=False) -> None:
+        """last=True (several ranks): this is the step's final backward pass, so each gradient
+        bucket is reduce-scattered as soon as it is complete; optimizer_step() picks the results up."""
         B, T = ids.shape
-        lib.check(_L.ctdk_engine_forward_backward(
-            self._h, ids.data_ptr(), targets.data_ptr(), loss_mask.data_ptr(), row_weight.data_ptr(),
-            B, T, int(accumulate), self.loss_sums.data_ptr(), _stream_ptr()))
+        self._reduce_in_backward = bool(last) and self.world > 1
+        try:
+            lib.check(_L.ctdk_engine_forward_backward(
+                self._h, ids.data_ptr(), targets.data_ptr(), loss_mask.data_ptr(), row_weight.data_ptr(),
+                B, T, int(accumulate), self.loss_sums.data_ptr(), _stream_ptr()))
+        finally:
+            self._reduce_in_backward = False
 
     def forward_loss(self, ids, targets, loss_mask) -> None:
         B, T = ids.shape
@@ -302,37 +394,53 @@ class TrainEngine:
 
     def optimizer_step(self, lr=None) -> None:
         """reduce-scatter(grads) -> sum of squares (+ all-reduce) -> clip scale -> fused AdamW on
-        this rank's shard -> all-gather(params). No host synchronisation."""
+        this rank's slices -> all-gather(params). No host synchronisation. With several ranks the
+        arena is handled bucket by bucket: reduce-scatters that forward_backward(last=True) already
+        started are only waited for (a stream dependency), the rest are issued here; the all-gather
+        of a bucket overlaps the AdamW of the next."""
         hp = self.hp
         lr = hp["lr"] if lr is None else lr
         s = _stream_ptr()
-        lo_, hi_ = self.rank * self.shard, (self.rank + 1) * self.shard
-        if self.world > 1:
-            import torch.distributed as dist
-            gshard = self.grads[lo_:hi_]
-            dist.reduce_scatter_tensor(gshard, self.grads, op=dist.ReduceOp.SUM, group=self.group)
-        else:
-            gshard = self.grads
         sc = self._scalars
         sc.zero_()
-        lib.call("ctdk_sumsq", gshard.data_ptr(), self.shard, sc.data_ptr(), s)
         if self.world > 1:
             import torch.distributed as dist
+            order = sorted(self.buckets, key=lambda bk: -bk["ready"])   # the order backward completes them
+            for bk in order:
+                if bk["work"] is None:
+                    bk["work"] = dist.reduce_scatter_tensor(self.grads[bk["a"]:bk["b"]], self.grads[bk["lo"]:bk["hi"]],
+                                                            op=dist.ReduceOp.SUM, group=self.group, async_op=True)
+            for bk in order:
+                bk["work"].wait()
+                bk["work"] = None
+                lib.call("ctdk_sumsq", self.grads[bk["a"]:bk["b"]].data_ptr(), bk["b"] - bk["a"], sc.data_ptr(), s)
             dist.all_reduce(sc[0:1], group=self.group)
             dist.all_reduce(self.loss_sums, group=self.group)
+        else:
+            lib.call("ctdk_sumsq", self.grads.data_ptr(), self.shard, sc.data_ptr(), s)
         lib.call("ctdk_clip_scale", sc.data_ptr(), hp["clip"], 1e-6, sc[1:].data_ptr(), sc[2:].data_ptr(), s)
         self.step_count += 1
         t = np.float32(self.step_count)
         bc1 = np.float32(1.0) - np.power(np.float32(hp["beta1"]), t, dtype=np.float32)
         bc2 = np.float32(1.0) - np.power(np.float32(hp["beta2"]), t, dtype=np.float32)
         ap = lib.AdamWParams(lr, hp["beta1"], hp["beta2"], hp["eps"], 0.0, float(bc1), float(bc2))
-        pshard = self.params[lo_:hi_]
-        lib.call("ctdk_adamw", pshard.data_ptr(), gshard.data_ptr(), self.m.data_ptr(), self.v.data_ptr(),
-                 self.shard, C.byref(ap), sc[1:].data_ptr(), self.seg_end.data_ptr(), self.seg_wd.data_ptr(),
-                 self.seg_end.numel(), s)
-        if self.world > 1:
-            import torch.distributed as dist
-            dist.all_gather_into_tensor(self.params, pshard, group=self.group)
+        if self.world == 1:
+            lib.call("ctdk_adamw", self.params.data_ptr(), self.grads.data_ptr(), self.m.data_ptr(),
+                     self.v.data_ptr(), self.shard, C.byref(ap), sc[1:].data_ptr(), self.seg_end.data_ptr(),
+                     self.seg_wd.data_ptr(), self.seg_end.numel(), s)
+            return
+        import torch.distributed as dist
+        gathers = []
+        for bk in self.buckets:   # arena order = the order the next forward pass reads them
+            n, st = bk["b"] - bk["a"], bk["state"]
+            pslice = self.params[bk["a"]:bk["b"]]
+            lib.call("ctdk_adamw", pslice.data_ptr(), self.grads[bk["a"]:bk["b"]].data_ptr(),
+                     self.m[st:st + n].data_ptr(), self.v[st:st + n].data_ptr(), n, C.byref(ap), sc[1:].data_ptr(),
+                     bk["seg_end"].data_ptr(), bk["seg_wd"].data_ptr(), bk["seg_end"].numel(), s)
+            gathers.append(dist.all_gather_into_tensor(self.params[bk["lo"]:bk["hi"]], pslice, group=self.group,
+                                                       async_op=True))
+        for w in gathers:
+            w.wait()
 
     def train_step(self, ids, targets, loss_mask, row_weight, lr=None, active_rows=None) -> None:
         """One optimizer step on this rank's rows (already weighted per micro-batch). active_rows:
@@ -340,7 +448,7 @@ class TrainEngine:
         self.loss_sums.zero_()
         if active_rows is not None:
             self.set_active_rows(active_rows)
-        self.forward_backward(ids, targets, loss_mask, row_weight, accumulate=False)
+        self.forward_backward(ids, targets, loss_mask, row_weight, accumulate=False, last=True)
         self.optimizer_step(lr)
 
     def read_metrics(self) -> dict:

@@ -40,7 +40,6 @@ def _worker(rank, world, port, out):
     ocfg, ecfg = om.LlamaConfig(**KW), E.make_config(**KW)
     layout = E.model_layout(ecfg)
     total = E.padded_total(layout.total, world)
-    lo, hi = E.shard_bounds(total, world, rank)
     params = om.init_params(ocfg, seed=3, std=0.05)
     tok, msk = om.synth_batch(ocfg.vocab_size, A * MB, S, seed=4)
     # this rank's micro-batches, fused into one pass with per-row weights
@@ -56,26 +55,33 @@ def _worker(rank, world, port, out):
         # the weights the engine would get are exactly dy/sum(mask) on the masked positions
         assert np.allclose(w[sl][m[sl] > 0], (1.0 / A) / m[sl].sum())
     gflat = torch.from_numpy(_flatten(layout, grads, total))
-    dist.all_reduce(gflat)                       # gloo has no reduce_scatter: sum, then keep own slice
-    gshard = gflat[lo:hi].numpy()
-    ss = torch.tensor([float((gshard.astype(np.float64) ** 2).sum())], dtype=torch.float64)
+    dist.all_reduce(gflat)                       # gloo has no reduce_scatter: sum, then keep own slices
+    # ownership as in TrainEngine: rank r owns slice r of every bucket (one layer per bucket here)
+    buckets = E.make_buckets(layout, total, world, ocfg.num_hidden_layers, layers_per_bucket=1)
+    mine_sl = [E.bucket_slice(lo, hi, world, rank) for lo, hi, _ in buckets]
+    ss = torch.tensor([sum(float((gflat[a:b].numpy().astype(np.float64) ** 2).sum()) for a, b in mine_sl)],
+                      dtype=torch.float64)
     dist.all_reduce(ss)
     norm = np.float32(np.sqrt(ss.item()))
     scale = np.float32(HP["clip"]) / (norm + np.float32(1e-6)) if norm > HP["clip"] else np.float32(1.0)
     pflat = _flatten(layout, params, total)
-    ends, wds = E.build_segments(layout, HP["weight_decay"], lo, hi)
-    new = pflat[lo:hi].copy()
-    start = 0
-    for end, wd in zip(ends, wds):
-        p, _, _ = oo.adamw_step(pflat[lo + start:lo + end], (gshard[start:end] * scale).astype(np.float32),
-                                np.zeros(end - start, np.float32), np.zeros(end - start, np.float32), 1,
-                                HP["lr"], HP["beta1"], HP["beta2"], HP["eps"], wd)
-        new[start:end] = p
-        start = end
-    gathered = [torch.zeros(hi - lo) for _ in range(world)]
-    dist.all_gather(gathered, torch.from_numpy(new))
+    full = np.zeros(total, np.float32)
+    for (lo, hi, _), (a, b) in zip(buckets, mine_sl):
+        gshard = gflat[a:b].numpy()
+        ends, wds = E.build_segments(layout, HP["weight_decay"], a, b)
+        new = pflat[a:b].copy()
+        start = 0
+        for end, wd in zip(ends, wds):
+            p, _, _ = oo.adamw_step(pflat[a + start:a + end], (gshard[start:end] * scale).astype(np.float32),
+                                    np.zeros(end - start, np.float32), np.zeros(end - start, np.float32), 1,
+                                    HP["lr"], HP["beta1"], HP["beta2"], HP["eps"], wd)
+            new[start:end] = p
+            start = end
+        gathered = [torch.zeros(b - a) for _ in range(world)]
+        dist.all_gather(gathered, torch.from_numpy(new))
+        full[lo:hi] = np.concatenate([g.numpy() for g in gathered])
     if rank == 0:
-        np.save(out, np.concatenate([g.numpy() for g in gathered]))
+        np.save(out, full)
         np.save(out + ".norm.npy", np.array([norm]))
     dist.destroy_process_group()
 
@@ -117,6 +123,46 @@ def test_shard_segments_cover_every_tensor_once():
         assert (wd >= 0).all()
         for o, k, d in zip(layout.offsets, layout.numels, layout.decay):
             assert (wd[o:o + k] == (0.01 if d else 0.0)).all()
+
+
+def test_buckets_partition_the_arena_and_know_when_they_are_complete():
+    from emberlm_b200 import engine as E
+    for preset in ("smollm2_360m", "qwen3_0_6b"):
+        cfg = E.make_config(**E.PRESETS[preset])
+        layout = E.model_layout(cfg)
+        L = cfg.num_hidden_layers
+        for world in (2, 4, 8):
+            total = E.padded_total(layout.total, world)
+            buckets = E.make_buckets(layout, total, world, L)
+            assert buckets[0][0] == 0 and buckets[-1][1] == total
+            assert all(x[1] == y[0] for x, y in zip(buckets[:-1], buckets[1:]))
+            assert all((hi - lo) % (64 * world) == 0 and hi > lo for lo, hi, _ in buckets)
+            # the embedding bucket is complete last (-1), later buckets earlier and earlier
+            assert buckets[0][2] == -1 and [b[2] for b in buckets] == sorted(b[2] for b in buckets)
+            # a bucket is complete once the lowest-numbered tensor it touches is
+            for lo, hi, ready in buckets:
+                touching = [E.tensor_layer(n, L) for n, o, k in zip(layout.names, layout.offsets, layout.numels)
+                            if o < hi and o + k > lo]
+                assert ready == min(touching)
+            # slices of all ranks tile every bucket; per-slice decay segments match the tensors
+            wd = np.full(total, -1.0)
+            owned = 0
+            for r in range(world):
+                for lo, hi, _ in buckets:
+                    a, b = E.bucket_slice(lo, hi, world, r)
+                    owned += b - a
+                    ends, wds = E.build_segments(layout, 0.01, a, b)
+                    assert ends[-1] == b - a
+                    start = 0
+                    for e, w in zip(ends, wds):
+                        assert (wd[a + start:a + e] == -1.0).all()
+                        wd[a + start:a + e] = w
+                        start = e
+            assert owned == total and (wd >= 0).all()
+            for o, k, d in zip(layout.offsets, layout.numels, layout.decay):
+                assert (wd[o:o + k] == (0.01 if d else 0.0)).all()
+    assert E.tensor_layer("model.layers.17.mlp.up_proj.weight", 32) == 17
+    assert E.tensor_layer("model.norm.weight", 32) == 32 and E.tensor_layer("model.embed_tokens.weight", 32) == -1
 
 
 def test_dealing_and_row_weights():
