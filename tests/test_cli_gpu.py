@@ -70,7 +70,10 @@ def test_two_steps_match_the_engine_then_resume(tmp_path):
     for n, v in eng.named_parameters().items():
         ref = v.cpu().numpy()
         assert final[n].shape == ref.shape
-        assert np.abs(final[n] - ref).max() <= 3e-4 * max(np.abs(ref).max(), 1e-12), n   # lr-sized AdamW sign noise
+        # AdamW's first steps are sign-like: an element whose gradient is atomics-order noise can move by
+        # up to 2*lr per step in either run, so bound the error by that and require it to be rare
+        d = np.abs(final[n] - ref)
+        assert d.max() <= 4.5e-4 and np.mean(d > 2e-5) < 2e-2 and np.median(d) < 1e-6, n
     opt = safetensors_io.load_safetensors(str(run_dir / "final.safetensors") + ".opt.safetensors")
     assert float(opt["optimizer.step"][0]) == 2.0
     assert set(opt) == {"optimizer.step"} | {f"optimizer.{k}.{n}" for k in "mv" for n, _ in names}
