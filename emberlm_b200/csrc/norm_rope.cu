@@ -127,23 +127,38 @@ __global__ void __launch_bounds__(256)
     wv[j] = (c < H4) ? w4[c] : make_float4(0.f, 0.f, 0.f, 0.f);
     dwv[j] = make_float4(0.f, 0.f, 0.f, 0.f);
   }
-  int slot = 0;
-  for (int64_t row = blockIdx.x; row < rows; row += gridDim.x, slot ^= 1) {
+  // The next row's x and dy are fetched before the current row is reduced, so a CTA always has
+  // two rows of loads in flight across the block-wide reductions.
+  const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
+  float4 xn[NV], gn[NV], pn[NV];
+  auto fetch = [&](int64_t row) {
     const float4* x4 = reinterpret_cast<const float4*>(x) + row * H4;
     const float4* g4 = reinterpret_cast<const float4*>(dy) + row * H4;
-    float4* dx4 = reinterpret_cast<float4*>(dx) + row * H4;
-    float4 xv[NV], gv[NV];
-    float acc[2] = {0.0f, 0.0f};
+    const float4* p4 = reinterpret_cast<const float4*>(dx) + row * H4;
 #pragma unroll
     for (int j = 0; j < NV; ++j) {
       const int c = threadIdx.x + j * blockDim.x;
-      if (c < H4) {
-        xv[j] = x4[c];
-        gv[j] = g4[c];
-      } else {
-        xv[j] = make_float4(0.f, 0.f, 0.f, 0.f);
-        gv[j] = make_float4(0.f, 0.f, 0.f, 0.f);
-      }
+      const bool in = c < H4 && row < rows;
+      xn[j] = in ? __ldcs(x4 + c) : zero4;
+      gn[j] = in ? __ldcs(g4 + c) : zero4;
+      pn[j] = (in && add_to_dx) ? p4[c] : zero4;
+    }
+  };
+  fetch(blockIdx.x);
+  int slot = 0;
+  for (int64_t row = blockIdx.x; row < rows; row += gridDim.x, slot ^= 1) {
+    float4* dx4 = reinterpret_cast<float4*>(dx) + row * H4;
+    float4 xv[NV], gv[NV], pv[NV];
+    float acc[2] = {0.0f, 0.0f};
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
+      xv[j] = xn[j];
+      gv[j] = gn[j];
+      pv[j] = pn[j];
+    }
+    fetch(row + gridDim.x);
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
       acc[0] += xv[j].x * xv[j].x + xv[j].y * xv[j].y + xv[j].z * xv[j].z + xv[j].w * xv[j].w;
       acc[1] += gv[j].x * wv[j].x * xv[j].x + gv[j].y * wv[j].y * xv[j].y +
                 gv[j].z * wv[j].z * xv[j].z + gv[j].w * wv[j].w * xv[j].w;
@@ -160,13 +175,10 @@ __global__ void __launch_bounds__(256)
         o.y = s * (gv[j].y * wv[j].y - xv[j].y * k);
         o.z = s * (gv[j].z * wv[j].z - xv[j].z * k);
         o.w = s * (gv[j].w * wv[j].w - xv[j].w * k);
-        if (add_to_dx) {
-          const float4 p = dx4[c];
-          o.x += p.x;
-          o.y += p.y;
-          o.z += p.z;
-          o.w += p.w;
-        }
+        o.x += pv[j].x;   // zero unless add_to_dx
+        o.y += pv[j].y;
+        o.z += pv[j].z;
+        o.w += pv[j].w;
         dx4[c] = o;
         dwv[j].x += gv[j].x * xv[j].x * s;
         dwv[j].y += gv[j].y * xv[j].y * s;

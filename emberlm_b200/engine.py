@@ -10,6 +10,7 @@ optim::AdamW (src/core/optim.cu:132-168), clipping as optim::clip_grad_norm_
 from __future__ import annotations
 
 import ctypes as C
+import os
 import math
 from dataclasses import dataclass
 
@@ -155,10 +156,11 @@ def make_buckets(layout: Layout, total_padded: int, world: int, num_layers: int,
     for o, l in zip(layout.offsets, layer_of):
         first[l] = min(first.get(l, o), o)
     cuts = [0]
-    for l in range(0, num_layers, max(1, layers_per_bucket)):
-        c = first[l] // unit * unit
-        if c > cuts[-1]:
-            cuts.append(c)
+    if layers_per_bucket > 0:       # 0: one bucket = the whole arena (reduced after the backward pass)
+        for l in range(0, num_layers, layers_per_bucket):
+            c = first[l] // unit * unit
+            if c > cuts[-1]:
+                cuts.append(c)
     cuts.append(total_padded)
     out = []
     for lo, hi in zip(cuts[:-1], cuts[1:]):
@@ -329,7 +331,8 @@ class TrainEngine:
             return
         self.buckets = []
         pos = 0
-        for lo, hi, ready in make_buckets(self.layout, self.total, self.world, self.cfg.num_hidden_layers):
+        per = int(os.environ.get("CTDK_DP_BUCKET_LAYERS", "4"))
+        for lo, hi, ready in make_buckets(self.layout, self.total, self.world, self.cfg.num_hidden_layers, per):
             a, b = bucket_slice(lo, hi, self.world, self.rank)
             ends, wds = build_segments(self.layout, wd, a, b)
             self.buckets.append(dict(
