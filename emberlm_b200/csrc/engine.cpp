@@ -137,6 +137,8 @@ struct Engine {
   int64_t ws3_floats = 0;
   ctdk_layer_callback cb = nullptr;
   void* cb_user = nullptr;
+  ctdk_layer_callback fcb = nullptr;   // before each part of the forward pass
+  void* fcb_user = nullptr;
 };
 
 int64_t pick_head_rows(const ctdk_model_config& c, int64_t tok) {
@@ -338,8 +340,13 @@ int run(Engine& e, const int64_t* ids, const int64_t* targets, const float* loss
   CTDK_REQUIRE(ids && targets && loss_sums, "engine: null input");
   CTDK_REQUIRE(!backward || row_weight, "engine: row_weight required for the backward");
 
+  if (e.fcb) e.fcb(-1, e.fcb_user);
   TRY(ctdk_embedding_fwd(ids, P + e.layout.embed, e.xs[0], tok, static_cast<int>(hid), V, s));
-  for (int l = 0; l < L; ++l) TRY(layer_forward(e, l, B, T, s));
+  for (int l = 0; l < L; ++l) {
+    if (e.fcb) e.fcb(l, e.fcb_user);
+    TRY(layer_forward(e, l, B, T, s));
+  }
+  if (e.fcb) e.fcb(L, e.fcb_user);
   TRY(ctdk_rmsnorm_fwd(e.xs[L], P + e.layout.norm, e.hf, nullptr, tok, static_cast<int>(hid),
                        c.rms_norm_eps, s));
 
@@ -476,6 +483,14 @@ int ctdk_engine_set_layer_callback(void* engine, ctdk_layer_callback cb, void* u
   Engine* e = static_cast<Engine*>(engine);
   e->cb = cb;
   e->cb_user = user;
+  return CTDK_OK;
+}
+
+int ctdk_engine_set_forward_callback(void* engine, ctdk_layer_callback cb, void* user) {
+  CTDK_REQUIRE(engine != nullptr, "ctdk_engine_set_forward_callback: null engine");
+  Engine* e = static_cast<Engine*>(engine);
+  e->fcb = cb;
+  e->fcb_user = user;
   return CTDK_OK;
 }
 

@@ -238,6 +238,8 @@ _L.ctdk_engine_forward_loss.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_
 _L.ctdk_engine_set_active_rows.restype = C.c_int
 _L.ctdk_engine_set_active_rows.argtypes = [C.c_void_p, C.c_void_p, C.c_int64]
 LAYER_CALLBACK = C.CFUNCTYPE(None, C.c_int, C.c_void_p)
+_L.ctdk_engine_set_forward_callback.restype = C.c_int
+_L.ctdk_engine_set_forward_callback.argtypes = [C.c_void_p, C.CFUNCTYPE(None, C.c_int, C.c_void_p), C.c_void_p]
 _L.ctdk_engine_set_layer_callback.restype = C.c_int
 _L.ctdk_engine_set_layer_callback.argtypes = [C.c_void_p, LAYER_CALLBACK, C.c_void_p]
 
@@ -291,6 +293,8 @@ class TrainEngine:
 
     # ---- parameters -------------------------------------------------------------------
     def named_parameters(self) -> dict:
+        if getattr(self, "buckets", None):
+            self.wait_parameters()
         lo = self.layout
         return {n: self.params[o:o + k].view(s) for n, s, o, k in zip(lo.names, lo.shapes, lo.offsets, lo.numels)}
 
@@ -361,6 +365,33 @@ class TrainEngine:
         self._reduce_in_backward = False
         self._cb = LAYER_CALLBACK(lambda layer, _u: on_layer(layer))
         lib.check(_L.ctdk_engine_set_layer_callback(self._h, self._cb, None))
+
+        # All-gathers of the updated parameters are left in flight by optimizer_step(); each part of
+        # the next forward pass first makes the compute stream wait for the buckets it reads (the
+        # embedding bucket is also the tied LM head, read again at the end).
+        L = self.cfg.num_hidden_layers
+        for bk in self.buckets:
+            touched = [tensor_layer(n, L) for n, o, k in zip(self.layout.names, self.layout.offsets, self.layout.numels)
+                       if o < bk["hi"] and o + k > bk["lo"]]
+            bk["first_use"] = min(touched) if touched else L
+            bk["gather"] = None
+
+        def on_forward(layer: int) -> None:
+            for bk in self.buckets:
+                if bk["gather"] is not None and bk["first_use"] <= layer:
+                    bk["gather"].wait()
+                    bk["gather"] = None
+
+        self._fcb = LAYER_CALLBACK(lambda layer, _u: on_forward(layer))
+        lib.check(_L.ctdk_engine_set_forward_callback(self._h, self._fcb, None))
+
+    def wait_parameters(self) -> None:
+        """Makes the current stream wait for every all-gather that optimizer_step() left in flight.
+        Called before anything other than the engine's own forward pass reads self.params."""
+        for bk in getattr(self, "buckets", []):
+            if bk.get("gather") is not None:
+                bk["gather"].wait()
+                bk["gather"] = None
 
     # ---- step -------------------------------------------------------------------------
     def set_layer_callback(self, fn) -> None:
@@ -433,17 +464,16 @@ class TrainEngine:
                      self.seg_wd.data_ptr(), self.seg_end.numel(), s)
             return
         import torch.distributed as dist
-        gathers = []
         for bk in self.buckets:   # arena order = the order the next forward pass reads them
             n, st = bk["b"] - bk["a"], bk["state"]
             pslice = self.params[bk["a"]:bk["b"]]
             lib.call("ctdk_adamw", pslice.data_ptr(), self.grads[bk["a"]:bk["b"]].data_ptr(),
                      self.m[st:st + n].data_ptr(), self.v[st:st + n].data_ptr(), n, C.byref(ap), sc[1:].data_ptr(),
                      bk["seg_end"].data_ptr(), bk["seg_wd"].data_ptr(), bk["seg_end"].numel(), s)
-            gathers.append(dist.all_gather_into_tensor(self.params[bk["lo"]:bk["hi"]], pslice, group=self.group,
-                                                       async_op=True))
-        for w in gathers:
-            w.wait()
+            bk["gather"] = dist.all_gather_into_tensor(self.params[bk["lo"]:bk["hi"]], pslice, group=self.group,
+                                                       async_op=True)
+        if os.environ.get("CTDK_DP_GATHER_OVERLAP", "1") != "1":
+            self.wait_parameters()
 
     def train_step(self, ids, targets, loss_mask, row_weight, lr=None, active_rows=None) -> None:
         """One optimizer step on this rank's rows (already weighted per micro-batch). active_rows:

@@ -310,6 +310,11 @@ int ctdk_engine_forward_loss(void* engine, const int64_t* ids, const int64_t* ta
  * so the caller can start reducing that layer's gradients while earlier layers still run. */
 typedef void (*ctdk_layer_callback)(int layer, void* user);
 int ctdk_engine_set_layer_callback(void* engine, ctdk_layer_callback cb, void* user);
+/* Optional host callback invoked right BEFORE the forward kernels that first read a part of the
+ * parameter arena are enqueued (layer == -1: embedding; 0..L-1: decoder layer; L: final norm + LM
+ * head), so a data-parallel caller can let the all-gather of the updated parameters of later
+ * layers run underneath the forward pass of earlier ones and only make the stream wait here. */
+int ctdk_engine_set_forward_callback(void* engine, ctdk_layer_callback cb, void* user);
 
 /* ------------------------------------------------------------------------------------
  * KV-cache greedy decoding, batch 1. Replaces the cached inference path: Model::forward with a

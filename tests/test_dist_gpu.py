@@ -45,6 +45,8 @@ def _run(rank, world, port, out):
         d_m = torch.from_numpy(m).cuda()
         eng.train_step(torch.from_numpy(ids).cuda(), torch.from_numpy(tgt).cuda(), d_m, E.row_weights(d_m, MB, A))
         losses.append(eng.read_metrics())
+    if world > 1:
+        eng.wait_parameters()      # the last step's all-gathers are still in flight on NCCL's stream
     if rank == 0:
         np.savez(out, loss=np.array([x["loss"] for x in losses]), norm=np.array([x["grad_norm"] for x in losses]),
                  params=eng.params[:eng.layout.total].cpu().numpy())
