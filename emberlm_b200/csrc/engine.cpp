@@ -273,8 +273,12 @@ int layer_forward(Engine& e, int l, int64_t B, int64_t T, void* s) {
            CTDK_EPI_RESIDUAL, x, s));
   TRY(ctdk_rmsnorm_fwd(a.hm, P + w.w_post, a.h2, nullptr, tok, static_cast<int>(hid),
                        c.rms_norm_eps, s));
-  TRY(gemm(e, a.h2, P + w.wg, a.gu, tok, 2 * I, hid, 0, 1, CTDK_EPI_STORE, nullptr, s));
-  TRY(ctdk_swiglu_fwd(a.gu, a.act, tok, static_cast<int>(I), s));
+  if (c.precision == CTDK_GEMM_TF32) {
+    TRY(ctdk_gemm_swiglu(a.h2, P + w.wg, a.gu, a.act, tok, I, hid, CTDK_GEMM_TF32, s));
+  } else {
+    TRY(gemm(e, a.h2, P + w.wg, a.gu, tok, 2 * I, hid, 0, 1, CTDK_EPI_STORE, nullptr, s));
+    TRY(ctdk_swiglu_fwd(a.gu, a.act, tok, static_cast<int>(I), s));
+  }
   TRY(gemm(e, a.act, P + w.wd, e.xs[l + 1], tok, hid, I, 0, 1, CTDK_EPI_RESIDUAL, a.hm, s));
   return CTDK_OK;
 }

@@ -106,9 +106,34 @@ __global__ void fill_rows_kernel(float* C, const float* aux, int64_t M, int64_t 
 }  // namespace
 }  // namespace ctdk
 
+namespace ctdk {
+int gemm_swiglu_tcgen05(const float* A, const float* W, float* gu, float* act, int64_t M, int64_t I, int64_t K,
+                        cudaStream_t stream);
+}  // namespace ctdk
+
 using namespace ctdk;
 
 extern "C" {
+
+int ctdk_gemm_swiglu(const float* A, const float* W, float* gu, float* act, int64_t M, int64_t I, int64_t K,
+                     int precision, void* stream) {
+  CTDK_REQUIRE(M >= 0 && I > 0 && K > 0, "ctdk_gemm_swiglu: bad shape");
+  if (M == 0) return CTDK_OK;
+  CTDK_REQUIRE(A && W && gu && act, "ctdk_gemm_swiglu: null pointer");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (precision == CTDK_GEMM_TF32) {
+    void* tok = prof_begin(CTDK_PROF_GEMM, 4.0 * static_cast<double>(M) * I * K, s);
+    const int rc = gemm_swiglu_tcgen05(A, W, gu, act, M, I, K, s);
+    if (rc <= 0) {
+      prof_end(tok, s);
+      return rc;
+    }
+    prof_end(tok, s);   // not eligible: nothing was enqueued; the two-kernel path below reports itself
+  }
+  int rc = ctdk_gemm(A, W, gu, M, 2 * I, K, K, K, 2 * I, 0, 1, precision, CTDK_EPI_STORE, nullptr, stream);
+  if (rc != CTDK_OK) return rc;
+  return ctdk_swiglu_fwd(gu, act, M, static_cast<int>(I), stream);
+}
 
 int ctdk_gemm(const float* A, const float* B, float* C, int64_t M, int64_t N, int64_t K,
               int64_t lda, int64_t ldb, int64_t ldc, int transa, int transb, int precision,

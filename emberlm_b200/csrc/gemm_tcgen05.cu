@@ -439,6 +439,27 @@ int gemm_tcgen05_2cta(const CUtensorMap& ta, const CUtensorMap& tb, const CUtens
                       bool a3d, bool b3d, int tma_out, float* C, const float* aux, int64_t ldc, int M, int N, int K,
                       int epilogue, int vec_ok, int splits, int* status, cudaStream_t stream);
 
+int gemm_tcgen05_2cta_swiglu(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tgu, const CUtensorMap& tact,
+                             int M, int N, int K, int* status, cudaStream_t stream);
+
+// gu[M, 2I] = A[M, K] W[2I, K]^T and act[M, I] = silu(gu[:, :I]) * gu[:, I:] in one paired-CTA launch.
+// Returns CTDK_OK after enqueueing, a negative status, or 1 when the shape is not eligible.
+int gemm_swiglu_tcgen05(const float* A, const float* W, float* gu, float* act, int64_t M, int64_t I, int64_t K,
+                        cudaStream_t stream) {
+  auto a16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; };
+  if (!a16(A) || !a16(W) || !a16(gu) || !a16(act) || (K & 3) || (I % 128) != 0) return 1;
+  if (M < 256 || M > INT32_MAX || 2 * I > INT32_MAX || K > INT32_MAX || K < 1) return 1;
+  CUtensorMap ta, tb, tgu, tact;
+  int rc = make_map(&ta, A, K, M, K, BM, false, false);
+  if (rc == CTDK_OK) rc = make_map(&tb, W, K, 2 * I, K, 128, false, false);
+  if (rc == CTDK_OK) rc = make_map(&tgu, gu, 2 * I, M, 2 * I, 32, false, true);
+  if (rc == CTDK_OK) rc = make_map(&tact, act, I, M, I, 32, false, true);
+  if (rc != CTDK_OK) return rc;
+  int* st = device_status_word();
+  if (st == nullptr) return fail(CTDK_ELAUNCH, "gemm: no status word");
+  return gemm_tcgen05_2cta_swiglu(ta, tb, tgu, tact, static_cast<int>(M), static_cast<int>(I), static_cast<int>(K), st, stream);
+}
+
 // Returns CTDK_OK after enqueueing, or 1 when the shape/alignment is not eligible for the
 // tensor-core path (the caller then uses the SIMT kernel).
 int gemm_tcgen05(const float* A, const float* B, float* Cp, int64_t M, int64_t N, int64_t K,

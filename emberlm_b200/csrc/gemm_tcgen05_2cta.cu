@@ -53,6 +53,8 @@ struct Gemm2Args {
   int splits;  // K ranges per tile; >1: partial tiles are added to C with atomics
   int a3d, b3d;   // MN-major operand described by a 3-D map: one {32 x 32 x 4} box per k-block
   int tma_out;    // 1: C is written (2: added to) through TMA from shared-memory staging
+  int swiglu;     // 1: B = [gate rows; up rows] of an MLP ([2N, K]); C = packed gate|up [M, 2N] and a second
+                  //    output act = silu(gate) * up [M, N]: each tile holds 128 gate and the matching 128 up columns
   int* status;
 };
 
@@ -152,7 +154,8 @@ __device__ __forceinline__ void tile_coords2(int tile, int m_blocks, int n_block
 template <bool A_MN, bool B_MN>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
     gemm_tf32_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                          const __grid_constant__ CUtensorMap tmC, const Gemm2Args args) {
+                          const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmD,
+                          const Gemm2Args args) {
   extern __shared__ unsigned char smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   unsigned char* smem = smem_raw + ((1024u - (raw & 1023u)) & 1023u);
@@ -168,7 +171,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
   const uint32_t rank = cluster_rank();
   const bool leader = rank == 0;
   const int m_blocks = (args.M + 2 * BM2 - 1) / (2 * BM2);
-  const int n_blocks = (args.N + BN2 - 1) / BN2;
+  const int n_blocks = args.swiglu ? args.N / (BN2 / 2) : (args.N + BN2 - 1) / BN2;
   const int num_tiles = m_blocks * n_blocks;
   const int k_blocks = (args.K + BK2 - 1) / BK2;
   const int num_units = num_tiles * args.splits;  // unit u: tile u % num_tiles, k-range u / num_tiles
@@ -187,6 +190,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
     tma_prefetch_desc(&tmA);
     tma_prefetch_desc(&tmB);
     if (args.tma_out) tma_prefetch_desc(&tmC);
+    if (args.swiglu) tma_prefetch_desc(&tmD);
   }
   if (warp == 1) {
     tmem_alloc2(tmem_slot, 512);
@@ -210,7 +214,10 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
         int mb, nb;
         tile_coords2(unit % num_tiles, m_blocks, n_blocks, mb, nb);
         const int m0 = mb * 2 * BM2 + static_cast<int>(rank) * BM2;
-        const int n0 = nb * BN2 + static_cast<int>(rank) * (BN2 / 2);
+        // B rows of this CTA: its half of the 256 columns, or (fused SwiGLU) 128 gate rows in the
+        // even CTA and the matching 128 up rows, N rows further on, in the odd one
+        const int n0 = args.swiglu ? nb * (BN2 / 2) + static_cast<int>(rank) * args.N
+                                   : nb * BN2 + static_cast<int>(rank) * (BN2 / 2);
         const int split = unit / num_tiles;
         const int kb0 = static_cast<int>(static_cast<int64_t>(split) * k_blocks / args.splits);
         const int kb1 = static_cast<int>(static_cast<int64_t>(split + 1) * k_blocks / args.splits);
@@ -353,6 +360,41 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
       float* crow = args.C + grow * args.ldc;
       const float* xrow = args.aux != nullptr ? args.aux + grow * args.ldc : nullptr;
       const uint32_t t_row = tmem_base + static_cast<uint32_t>(acc * BN2) + (static_cast<uint32_t>(q * 32) << 16);
+      if (args.swiglu) {
+        // columns 0..127 of the accumulator are gate, 128..255 the matching up columns: three boxes
+        // per 32-column chunk (gate and up into the packed buffer, silu(gate)*up into the second
+        // output) through the two staging boxes in turn
+        const int r0 = mb * 2 * BM2 + static_cast<int>(rank) * BM2 + q * 32;
+        int n_sent = 0;
+        auto send = [&](const float (&v)[32], const CUtensorMap* map, int col) {
+          unsigned char* buf = epi_stage + (q * 2 + (n_sent & 1)) * kEpiBuf;
+          if (n_sent >= 2 && lane == 0) bulk_wait_read<1>();
+          __syncwarp();
+#pragma unroll
+          for (int c = 0; c < 8; ++c)
+            *reinterpret_cast<float4*>(buf + lane * 128 + ((c ^ (lane & 7)) << 4)) =
+                make_float4(v[4 * c], v[4 * c + 1], v[4 * c + 2], v[4 * c + 3]);
+          fence_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            if (r0 < args.M) tma_store_2d(map, buf, col, r0);
+            bulk_commit();
+          }
+          ++n_sent;
+        };
+#pragma unroll 1
+        for (int ch = 0; ch < BN2 / 64; ++ch) {
+          const int col = nb * (BN2 / 2) + ch * 32;
+          float g[32], u[32];
+          tmem_ld_32x32(t_row + static_cast<uint32_t>(ch * 32), g);
+          tmem_ld_32x32(t_row + static_cast<uint32_t>(BN2 / 2 + ch * 32), u);
+          send(g, &tmC, col);
+          send(u, &tmC, args.N + col);
+#pragma unroll
+          for (int i = 0; i < 32; ++i) g[i] = g[i] / (1.0f + __expf(-g[i])) * u[i];
+          send(g, &tmD, col);
+        }
+      } else
 #pragma unroll 1
       for (int ch = 0; ch < BN2 / 32; ++ch) {
         const int col0 = nb * BN2 + ch * 32;
@@ -455,15 +497,15 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
 }
 
 template <bool A_MN, bool B_MN>
-int launch2(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const Gemm2Args& args,
-            cudaStream_t stream) {
+int launch2(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const CUtensorMap& td,
+            const Gemm2Args& args, cudaStream_t stream) {
   auto* kern = gemm_tf32_2cta_kernel<A_MN, B_MN>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem2);
   if (e != cudaSuccess) return fail(CTDK_ELAUNCH, "gemm(2cta): shared memory opt-in failed: %s", cudaGetErrorString(e));
-  const int tiles = ((args.M + 255) / 256) * ((args.N + BN2 - 1) / BN2) * args.splits;
+  const int tiles = ((args.M + 255) / 256) * (args.swiglu ? args.N / (BN2 / 2) : (args.N + BN2 - 1) / BN2) * args.splits;
   int pairs = sm_count() / 2;
   if (tiles < pairs) pairs = tiles;
-  kern<<<2 * pairs, 192, kSmem2, stream>>>(ta, tb, tc, args);
+  kern<<<2 * pairs, 192, kSmem2, stream>>>(ta, tb, tc, td, args);
   return check_launch("ctdk_gemm(tcgen05, cta pair)");
 }
 
@@ -475,11 +517,20 @@ int launch2(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc,
 int gemm_tcgen05_2cta(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, bool a_mn, bool b_mn,
                       bool a3d, bool b3d, int tma_out, float* C, const float* aux, int64_t ldc, int M, int N, int K,
                       int epilogue, int vec_ok, int splits, int* status, cudaStream_t stream) {
-  Gemm2Args args{C, aux, ldc, M, N, K, epilogue, vec_ok, splits, a3d ? 1 : 0, b3d ? 1 : 0, tma_out, status};
-  if (!a_mn && !b_mn) return launch2<false, false>(ta, tb, tc, args, stream);
-  if (!a_mn && b_mn) return launch2<false, true>(ta, tb, tc, args, stream);
-  if (a_mn && !b_mn) return launch2<true, false>(ta, tb, tc, args, stream);
-  return launch2<true, true>(ta, tb, tc, args, stream);
+  Gemm2Args args{C, aux, ldc, M, N, K, epilogue, vec_ok, splits, a3d ? 1 : 0, b3d ? 1 : 0, tma_out, 0, status};
+  if (!a_mn && !b_mn) return launch2<false, false>(ta, tb, tc, tc, args, stream);
+  if (!a_mn && b_mn) return launch2<false, true>(ta, tb, tc, tc, args, stream);
+  if (a_mn && !b_mn) return launch2<true, false>(ta, tb, tc, tc, args, stream);
+  return launch2<true, true>(ta, tb, tc, tc, args, stream);
+}
+
+// Fused MLP input projection: gu[M, 2N] = A[M, K] * W[2N, K]^T (gate rows then up rows) and
+// act[M, N] = silu(gate) * up. ta: A, {32, 128} boxes; tb: W, {32, 128} boxes; tgu / tact: the two
+// outputs, {32, 32} boxes. N must be a multiple of 128.
+int gemm_tcgen05_2cta_swiglu(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tgu, const CUtensorMap& tact,
+                             int M, int N, int K, int* status, cudaStream_t stream) {
+  Gemm2Args args{nullptr, nullptr, 0, M, N, K, CTDK_EPI_STORE, 1, 1, 0, 0, 1, 1, status};
+  return launch2<false, false>(ta, tb, tgu, tact, args, stream);
 }
 
 }  // namespace ctdk

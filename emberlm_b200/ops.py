@@ -65,6 +65,21 @@ def silu_backward(x, g):
     return out
 
 
+def mlp_in(x, w_gate_up, I, precision=lib.GEMM_TF32):
+    """nn::MLP::forward up to the activation (include/ctd/nn/mlp.h:16-21) in one launch:
+    x [M, K], w_gate_up [2I, K] (gate_proj rows then up_proj rows). Returns (gu [M, 2I] = gate | up,
+    act [M, I] = silu(gate) * up)."""
+    _chk(x, "mlp_in"), _chk(w_gate_up, "mlp_in")
+    M, K = x.shape
+    if tuple(w_gate_up.shape) != (2 * I, K):
+        raise RuntimeError("mlp_in: weight must be [2I, K]")
+    gu = torch.empty(M, 2 * I, device=x.device, dtype=x.dtype)
+    act = torch.empty(M, I, device=x.device, dtype=x.dtype)
+    lib.call("ctdk_gemm_swiglu", x.data_ptr(), w_gate_up.data_ptr(), gu.data_ptr(), act.data_ptr(), M, I, K,
+             precision, _s())
+    return gu, act
+
+
 def swiglu(gu):
     _chk(gu, "swiglu")
     rows, two_i = gu.shape

@@ -78,6 +78,15 @@ int ctdk_gemm_ws(const float* A, const float* B, float* C, int64_t M, int64_t N,
                  int epilogue, const float* aux, float* workspace, int64_t workspace_floats,
                  void* stream);
 
+/* Fused MLP input projection (nn::MLP::forward, include/ctd/nn/mlp.h:16-21: gate_proj and up_proj
+ * matmuls followed by silu(gate) * up): W is the [2I, K] stack of the gate_proj rows and the up_proj
+ * rows (adjacent in the parameter arena); gu[M, 2I] receives gate | up (kept for the backward pass)
+ * and act[M, I] = silu(gate) * up, both from the accumulator of one paired-CTA GEMM, so the
+ * activation never re-reads gate and up from memory. Shapes the fused kernel does not take
+ * (I not a multiple of 128, M < 256, unaligned pointers, 3xTF32) run as ctdk_gemm + ctdk_swiglu_fwd. */
+int ctdk_gemm_swiglu(const float* A, const float* W, float* gu, float* act, int64_t M, int64_t I,
+                     int64_t K, int precision, void* stream);
+
 /* Batched variant with full-matrix strides, as cublasSgemmStridedBatched in
  * ops::bmm_impl (src/ops/matmul.cpp:51-93). */
 int ctdk_bmm(const float* A, const float* B, float* C, int64_t batch, int64_t M, int64_t N,

@@ -318,6 +318,22 @@ def test_cross_entropy_masked_identities_and_zero_sum(K):
         K.cross_entropy_masked(dev(z), dev(t), dev(np.zeros(5, F32)))
 
 
+@pytest.mark.parametrize("M,I,K", [(256, 128, 64), (1000, 256, 960), (4092, 2560, 960), (300, 96, 64), (100, 128, 32)])
+def test_fused_mlp_input_projection(M, I, K):
+    """gate|up GEMM with the SwiGLU activation in its epilogue against the two separate launches:
+    the accumulation order per element is the same, so the results are bit-identical; shapes the
+    fused kernel does not take (I % 128 != 0, M < 256) go through the same two launches."""
+    from emberlm_b200 import ops
+    x, w = dev(rnd((M, K), 61)), dev(rnd((2 * I, K), 62, -0.2, 0.2))
+    gu, act = ops.mlp_in(x, w, I)
+    gu_ref = ops.matmul(x, w, False, True)
+    act_ref = ops.swiglu(gu_ref)
+    assert torch.equal(gu, gu_ref) and torch.equal(act, act_ref)
+    g64 = host(x).astype(np.float64) @ host(w).astype(np.float64).T
+    want = g64[:, :I] / (1.0 + np.exp(-g64[:, :I])) * g64[:, I:]
+    assert np.abs(host(act) - want).max() <= 2e-2 * max(np.abs(want).max(), 1e-6)   # TF32 inputs
+
+
 @pytest.mark.parametrize("n,H", [(0, 64), (1, 4), (257, 960), (4099, 576)])
 def test_row_gather_scatter_and_ce_input_gather(n, H):
     from emberlm_b200 import lib
