@@ -304,6 +304,17 @@ __device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, float (&v)[32]) {
   for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
 }
 
+// d(gate), d(up) of act = silu(gate) * up for the upstream gradient d (MulBackward + SiluBackward of
+// the reference, emberlm src/ops/elementwise.cu:89-238) with one exp and one reciprocal on the
+// special-function pipe. Shared by swiglu_bwd_kernel and the GEMM epilogue that fuses it, so both
+// give the same bits.
+__device__ __forceinline__ void swiglu_bwd_elem(float d, float g, float u, float& dg, float& du) {
+  const float sg = __fdividef(1.0f, 1.0f + __expf(-g));
+  const float gs = g * sg;
+  dg = (d * u) * (sg + gs * (1.0f - sg));
+  du = d * gs;
+}
+
 // Packed two-wide fp32 arithmetic (one issue slot for two results) and three-input maximum.
 __device__ __forceinline__ void ffma2(float& d0, float& d1, float a0, float a1, float b0, float b1, float c0,
                                       float c1) {

@@ -142,14 +142,10 @@ __global__ void __launch_bounds__(256) swiglu_bwd_kernel(const float* __restrict
     const float4 u = gu4[r * 2 * I4 + I4 + c];
     const float4 d = da4[i];
     float4 dg, du;
-    dg.x = (d.x * u.x) * dsilu_f(g.x);
-    dg.y = (d.y * u.y) * dsilu_f(g.y);
-    dg.z = (d.z * u.z) * dsilu_f(g.z);
-    dg.w = (d.w * u.w) * dsilu_f(g.w);
-    du.x = d.x * silu_f(g.x);
-    du.y = d.y * silu_f(g.y);
-    du.z = d.z * silu_f(g.z);
-    du.w = d.w * silu_f(g.w);
+    swiglu_bwd_elem(d.x, g.x, u.x, dg.x, du.x);
+    swiglu_bwd_elem(d.y, g.y, u.y, dg.y, du.y);
+    swiglu_bwd_elem(d.z, g.z, u.z, dg.z, du.z);
+    swiglu_bwd_elem(d.w, g.w, u.w, dg.w, du.w);
     dgu4[r * 2 * I4 + c] = dg;
     dgu4[r * 2 * I4 + I4 + c] = du;
   }

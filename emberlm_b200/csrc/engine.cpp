@@ -296,9 +296,14 @@ int layer_backward(Engine& e, int l, int64_t B, int64_t T, int accumulate, void*
   const int wepi = accumulate ? CTDK_EPI_ACCUMULATE : CTDK_EPI_STORE;
 
   // MLP: y = hm + act Wd^T
-  TRY(gemm(e, e.dh, P + w.wd, e.dact, tok, I, hid, 0, 0, CTDK_EPI_STORE, nullptr, s));
-  TRY(gemm(e, e.dh, a.act, G + w.wd, hid, I, tok, 1, 0, wepi, nullptr, s));
-  TRY(ctdk_swiglu_bwd(a.gu, e.dact, e.dgu, tok, static_cast<int>(I), s));
+  if (c.precision == CTDK_GEMM_TF32) {
+    TRY(ctdk_gemm_swiglu_bwd(e.dh, P + w.wd, a.gu, e.dgu, e.dact, tok, I, hid, CTDK_GEMM_TF32, s));
+    TRY(gemm(e, e.dh, a.act, G + w.wd, hid, I, tok, 1, 0, wepi, nullptr, s));
+  } else {
+    TRY(gemm(e, e.dh, P + w.wd, e.dact, tok, I, hid, 0, 0, CTDK_EPI_STORE, nullptr, s));
+    TRY(gemm(e, e.dh, a.act, G + w.wd, hid, I, tok, 1, 0, wepi, nullptr, s));
+    TRY(ctdk_swiglu_bwd(a.gu, e.dact, e.dgu, tok, static_cast<int>(I), s));
+  }
   TRY(gemm(e, e.dgu, P + w.wg, e.dtmp, tok, hid, 2 * I, 0, 0, CTDK_EPI_STORE, nullptr, s));
   TRY(gemm(e, e.dgu, a.h2, G + w.wg, 2 * I, hid, tok, 1, 0, wepi, nullptr, s));
   TRY(ctdk_rmsnorm_bwd(e.dtmp, a.hm, P + w.w_post, e.dh, G + w.w_post, e.norm_scratch, tok,

@@ -109,11 +109,31 @@ __global__ void fill_rows_kernel(float* C, const float* aux, int64_t M, int64_t 
 namespace ctdk {
 int gemm_swiglu_tcgen05(const float* A, const float* W, float* gu, float* act, int64_t M, int64_t I, int64_t K,
                         cudaStream_t stream);
+int gemm_swiglu_bwd_tcgen05(const float* dy, const float* Wd, const float* gu, float* dgu, int64_t M, int64_t I, int64_t K,
+                            cudaStream_t stream);
 }  // namespace ctdk
 
 using namespace ctdk;
 
 extern "C" {
+
+int ctdk_gemm_swiglu_bwd(const float* dy, const float* Wd, const float* gu, float* dgu, float* dact_scratch, int64_t M,
+                         int64_t I, int64_t K, int precision, void* stream) {
+  CTDK_REQUIRE(M >= 0 && I > 0 && K > 0, "ctdk_gemm_swiglu_bwd: bad shape");
+  if (M == 0) return CTDK_OK;
+  CTDK_REQUIRE(dy && Wd && gu && dgu, "ctdk_gemm_swiglu_bwd: null pointer");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (precision == CTDK_GEMM_TF32) {
+    void* tok = prof_begin(CTDK_PROF_GEMM, 2.0 * static_cast<double>(M) * I * K, s);
+    const int rc = gemm_swiglu_bwd_tcgen05(dy, Wd, gu, dgu, M, I, K, s);
+    prof_end(tok, s);
+    if (rc <= 0) return rc;
+  }
+  CTDK_REQUIRE(dact_scratch != nullptr, "ctdk_gemm_swiglu_bwd: this shape needs the [M, I] scratch buffer");
+  int rc = ctdk_gemm(dy, Wd, dact_scratch, M, I, K, K, I, I, 0, 0, precision, CTDK_EPI_STORE, nullptr, stream);
+  if (rc != CTDK_OK) return rc;
+  return ctdk_swiglu_bwd(gu, dact_scratch, dgu, M, static_cast<int>(I), stream);
+}
 
 int ctdk_gemm_swiglu(const float* A, const float* W, float* gu, float* act, int64_t M, int64_t I, int64_t K,
                      int precision, void* stream) {

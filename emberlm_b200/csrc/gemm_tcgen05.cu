@@ -460,6 +460,33 @@ int gemm_swiglu_tcgen05(const float* A, const float* W, float* gu, float* act, i
   return gemm_tcgen05_2cta_swiglu(ta, tb, tgu, tact, static_cast<int>(M), static_cast<int>(I), static_cast<int>(K), st, stream);
 }
 
+int gemm_tcgen05_2cta_swiglu_bwd(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tgu, const CUtensorMap& tdgu,
+                                 bool b3d, int M, int N, int K, int* status, cudaStream_t stream);
+
+// dgu[M, 2I] = SwiGLU backward of (dy[M, K] * Wd[K, I]) against gu[M, 2I], in one paired-CTA launch.
+// Returns CTDK_OK after enqueueing, a negative status, or 1 when the shape is not eligible.
+int gemm_swiglu_bwd_tcgen05(const float* dy, const float* Wd, const float* gu, float* dgu, int64_t M, int64_t I, int64_t K,
+                            cudaStream_t stream) {
+  auto a16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; };
+  if (!a16(dy) || !a16(Wd) || !a16(gu) || !a16(dgu) || (K & 3) || (I % 32) != 0) return 1;
+  if (M < 256 || I < 256 || M > INT32_MAX || 2 * I > INT32_MAX || K > INT32_MAX || K < 1) return 1;
+  CUtensorMap ta, tb, tgu, tdgu;
+  int rc = make_map(&ta, dy, K, M, K, BM, false, false);
+  if (rc == CTDK_OK) {
+    const uint64_t dims[3] = {32u, static_cast<uint64_t>(K), static_cast<uint64_t>(I / 32)};
+    const uint64_t strides[2] = {static_cast<uint64_t>(I) * sizeof(float), 128u};
+    const uint32_t box[3] = {32u, 32u, 4u};
+    rc = encode_tensor_map(&tb, Wd, 3, dims, strides, box, true);
+  }
+  if (rc == CTDK_OK) rc = make_map(&tgu, gu, 2 * I, M, 2 * I, 32, false, true);
+  if (rc == CTDK_OK) rc = make_map(&tdgu, dgu, 2 * I, M, 2 * I, 32, false, true);
+  if (rc != CTDK_OK) return rc;
+  int* st = device_status_word();
+  if (st == nullptr) return fail(CTDK_ELAUNCH, "gemm: no status word");
+  return gemm_tcgen05_2cta_swiglu_bwd(ta, tb, tgu, tdgu, true, static_cast<int>(M), static_cast<int>(I), static_cast<int>(K), st,
+                                      stream);
+}
+
 // Returns CTDK_OK after enqueueing, or 1 when the shape/alignment is not eligible for the
 // tensor-core path (the caller then uses the SIMT kernel).
 int gemm_tcgen05(const float* A, const float* B, float* Cp, int64_t M, int64_t N, int64_t K,

@@ -26,7 +26,8 @@ constexpr int kStages2 = 6;
 constexpr int kChunk2 = 32 * BK2 * 4;    // one {32 x 32} box of an MN-major operand
 constexpr int kEpiBuf = 32 * 128;         // one {32 x 32} fp32 output box in transit
 constexpr int kEpiStage = 4 * 2 * kEpiBuf;  // 4 epilogue warps x 2 buffers
-constexpr int kSmem2 = kStages2 * kStage2 + kEpiStage + 1024 + 256;
+constexpr int kTiles2 = kStages2 * kStage2 + kEpiStage;   // operand ring + output staging: 224 KB, split per mode
+constexpr int kSmem2 = kTiles2 + 1024 + 256;
 constexpr uint32_t kPeerMask = 0xFEFFFFFFu;  // clears the CTA-rank bit of a shared::cluster address
 constexpr int kGroupM2 = 8;
 
@@ -55,6 +56,9 @@ struct Gemm2Args {
   int tma_out;    // 1: C is written (2: added to) through TMA from shared-memory staging
   int swiglu;     // 1: B = [gate rows; up rows] of an MLP ([2N, K]); C = packed gate|up [M, 2N] and a second
                   //    output act = silu(gate) * up [M, N]: each tile holds 128 gate and the matching 128 up columns
+                  // 2: the product is d(act) [M, N]; the epilogue reads gate|up [M, 2N] through map C and
+                  //    writes d(gate)|d(up) [M, 2N] through map D (SwiGLU backward), d(act) is never stored
+  int stages;     // operand ring depth: 6, or 5 when the epilogue needs 64 KB of staging (swiglu == 2)
   int* status;
 };
 
@@ -159,19 +163,21 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
   extern __shared__ unsigned char smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   unsigned char* smem = smem_raw + ((1024u - (raw & 1023u)) & 1023u);
-  unsigned char* epi_stage = smem + kStages2 * kStage2;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(epi_stage + kEpiStage);
+  const int n_stages = args.stages;
+  unsigned char* epi_stage = smem + n_stages * kStage2;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kTiles2);
   uint64_t* full = bars;                   // [kStages2]  used in the leader only
   uint64_t* empty = bars + kStages2;       // [kStages2]  one per CTA, signalled by multicast commit
   uint64_t* tfull = bars + 2 * kStages2;   // [2]         one per CTA, multicast commit
   uint64_t* tempty = tfull + 2;            // [2]         leader only, 8 arrivals (4 warps x 2 CTAs)
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 2);
+  uint64_t* ld_bar = tempty + 2;           // [4 warps][2 slots]  gate / up boxes of the SwiGLU-backward epilogue
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(ld_bar + 8);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = cluster_rank();
   const bool leader = rank == 0;
   const int m_blocks = (args.M + 2 * BM2 - 1) / (2 * BM2);
-  const int n_blocks = args.swiglu ? args.N / (BN2 / 2) : (args.N + BN2 - 1) / BN2;
+  const int n_blocks = args.swiglu == 1 ? args.N / (BN2 / 2) : (args.N + BN2 - 1) / BN2;
   const int num_tiles = m_blocks * n_blocks;
   const int k_blocks = (args.K + BK2 - 1) / BK2;
   const int num_units = num_tiles * args.splits;  // unit u: tile u % num_tiles, k-range u / num_tiles
@@ -186,6 +192,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
       mbar_init(&tfull[a], 1);
       mbar_init(&tempty[a], 8);
     }
+    for (int a = 0; a < 8; ++a) mbar_init(&ld_bar[a], 1);
     mbar_fence_init();
     tma_prefetch_desc(&tmA);
     tma_prefetch_desc(&tmB);
@@ -216,7 +223,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
         const int m0 = mb * 2 * BM2 + static_cast<int>(rank) * BM2;
         // B rows of this CTA: its half of the 256 columns, or (fused SwiGLU) 128 gate rows in the
         // even CTA and the matching 128 up rows, N rows further on, in the odd one
-        const int n0 = args.swiglu ? nb * (BN2 / 2) + static_cast<int>(rank) * args.N
+        const int n0 = args.swiglu == 1 ? nb * (BN2 / 2) + static_cast<int>(rank) * args.N
                                    : nb * BN2 + static_cast<int>(rank) * (BN2 / 2);
         const int split = unit / num_tiles;
         const int kb0 = static_cast<int>(static_cast<int64_t>(split) * k_blocks / args.splits);
@@ -258,7 +265,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
             tma_load_2d_pair(b_dst, &tmB, &full[s], k0, n0);
           }
           GP_ADD(1);
-          if (++s == kStages2) {
+          if (++s == n_stages) {
             s = 0;
             ph ^= 1u;
           }
@@ -321,7 +328,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
           }
           umma_commit_pair(&empty[s]);
           GP_ADD(5);
-          if (++s == kStages2) {
+          if (++s == n_stages) {
             s = 0;
             ph ^= 1u;
           }
@@ -337,6 +344,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
     const int row_in_tile = static_cast<int>(rank) * BM2 + q * 32 + lane;
     int it = 0;
     bool ok = true;
+    uint32_t chunk_cnt = 0;   // chunks this warp has fetched gate / up boxes for (SwiGLU backward)
     GP_DECL();
     for (int unit = pair; unit < num_units && ok; unit += n_pairs, ++it) {
       int mb, nb;
@@ -360,7 +368,65 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
       float* crow = args.C + grow * args.ldc;
       const float* xrow = args.aux != nullptr ? args.aux + grow * args.ldc : nullptr;
       const uint32_t t_row = tmem_base + static_cast<uint32_t>(acc * BN2) + (static_cast<uint32_t>(q * 32) << 16);
-      if (args.swiglu) {
+      if (args.swiglu == 2) {
+        // SwiGLU backward on the accumulator: d(act) stays in registers; gate and up boxes are
+        // fetched by TMA one chunk ahead into one of two box pairs, turned into d(gate) and
+        // d(up) in place and stored from there.
+        const int r0 = mb * 2 * BM2 + static_cast<int>(rank) * BM2 + q * 32;
+        int n_ch = (args.N - nb * BN2 + 31) / 32;
+        if (n_ch > BN2 / 32) n_ch = BN2 / 32;
+        unsigned char* boxes = epi_stage + q * (4 * kEpiBuf);   // [slot][gate, up]
+        auto fetch = [&](int ch) {   // lane 0 only
+          const uint32_t k = chunk_cnt + static_cast<uint32_t>(ch), slot = k & 1u;
+          const int col = nb * BN2 + ch * 32;
+          uint64_t* bar = &ld_bar[q * 2 + slot];
+          mbar_expect_tx(bar, 2 * kEpiBuf);
+          tma_load_2d(boxes + slot * 2 * kEpiBuf, &tmC, bar, col, r0);
+          tma_load_2d(boxes + slot * 2 * kEpiBuf + kEpiBuf, &tmC, bar, args.N + col, r0);
+        };
+        if (lane == 0) fetch(0);
+#pragma unroll 1
+        for (int ch = 0; ch < n_ch && ok; ++ch) {
+          const uint32_t k = chunk_cnt + static_cast<uint32_t>(ch), slot = k & 1u;
+          if (ch + 1 < n_ch && lane == 0) {
+            bulk_wait_read<0>();   // the other box pair was last read by the stores of chunk ch-1
+            fetch(ch + 1);
+          }
+          float v[32];
+          tmem_ld_32x32(t_row + static_cast<uint32_t>(ch * 32), v);
+          if (!mbar_wait_bounded(&ld_bar[q * 2 + slot], (k >> 1) & 1u, args.status, 65)) {
+            ok = false;
+            break;
+          }
+          unsigned char* bg = boxes + slot * 2 * kEpiBuf + lane * 128;
+          unsigned char* bu = bg + kEpiBuf;
+#pragma unroll
+          for (int c = 0; c < 8; ++c) {
+            const int off = (c ^ (lane & 7)) << 4;
+            const float4 g = *reinterpret_cast<const float4*>(bg + off);
+            const float4 u = *reinterpret_cast<const float4*>(bu + off);
+            float4 dg, du;
+            swiglu_bwd_elem(v[4 * c], g.x, u.x, dg.x, du.x);
+            swiglu_bwd_elem(v[4 * c + 1], g.y, u.y, dg.y, du.y);
+            swiglu_bwd_elem(v[4 * c + 2], g.z, u.z, dg.z, du.z);
+            swiglu_bwd_elem(v[4 * c + 3], g.w, u.w, dg.w, du.w);
+            *reinterpret_cast<float4*>(bg + off) = dg;
+            *reinterpret_cast<float4*>(bu + off) = du;
+          }
+          fence_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            const int col = nb * BN2 + ch * 32;
+            if (r0 < args.M) {
+              tma_store_2d(&tmD, boxes + slot * 2 * kEpiBuf, col, r0);
+              tma_store_2d(&tmD, boxes + slot * 2 * kEpiBuf + kEpiBuf, args.N + col, r0);
+            }
+            bulk_commit();
+          }
+          __syncwarp();
+        }
+        chunk_cnt += static_cast<uint32_t>(n_ch);
+      } else if (args.swiglu) {
         // columns 0..127 of the accumulator are gate, 128..255 the matching up columns: three boxes
         // per 32-column chunk (gate and up into the packed buffer, silu(gate)*up into the second
         // output) through the two staging boxes in turn
@@ -502,7 +568,7 @@ int launch2(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc,
   auto* kern = gemm_tf32_2cta_kernel<A_MN, B_MN>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem2);
   if (e != cudaSuccess) return fail(CTDK_ELAUNCH, "gemm(2cta): shared memory opt-in failed: %s", cudaGetErrorString(e));
-  const int tiles = ((args.M + 255) / 256) * (args.swiglu ? args.N / (BN2 / 2) : (args.N + BN2 - 1) / BN2) * args.splits;
+  const int tiles = ((args.M + 255) / 256) * (args.swiglu == 1 ? args.N / (BN2 / 2) : (args.N + BN2 - 1) / BN2) * args.splits;
   int pairs = sm_count() / 2;
   if (tiles < pairs) pairs = tiles;
   kern<<<2 * pairs, 192, kSmem2, stream>>>(ta, tb, tc, td, args);
@@ -517,7 +583,7 @@ int launch2(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc,
 int gemm_tcgen05_2cta(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, bool a_mn, bool b_mn,
                       bool a3d, bool b3d, int tma_out, float* C, const float* aux, int64_t ldc, int M, int N, int K,
                       int epilogue, int vec_ok, int splits, int* status, cudaStream_t stream) {
-  Gemm2Args args{C, aux, ldc, M, N, K, epilogue, vec_ok, splits, a3d ? 1 : 0, b3d ? 1 : 0, tma_out, 0, status};
+  Gemm2Args args{C, aux, ldc, M, N, K, epilogue, vec_ok, splits, a3d ? 1 : 0, b3d ? 1 : 0, tma_out, 0, kStages2, status};
   if (!a_mn && !b_mn) return launch2<false, false>(ta, tb, tc, tc, args, stream);
   if (!a_mn && b_mn) return launch2<false, true>(ta, tb, tc, tc, args, stream);
   if (a_mn && !b_mn) return launch2<true, false>(ta, tb, tc, tc, args, stream);
@@ -529,8 +595,16 @@ int gemm_tcgen05_2cta(const CUtensorMap& ta, const CUtensorMap& tb, const CUtens
 // outputs, {32, 32} boxes. N must be a multiple of 128.
 int gemm_tcgen05_2cta_swiglu(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tgu, const CUtensorMap& tact,
                              int M, int N, int K, int* status, cudaStream_t stream) {
-  Gemm2Args args{nullptr, nullptr, 0, M, N, K, CTDK_EPI_STORE, 1, 1, 0, 0, 1, 1, status};
+  Gemm2Args args{nullptr, nullptr, 0, M, N, K, CTDK_EPI_STORE, 1, 1, 0, 0, 1, 1, kStages2, status};
   return launch2<false, false>(ta, tb, tgu, tact, args, stream);
+}
+
+// Fused SwiGLU backward: d(act)[M, N] = A[M, K] * B[K, N] (B MN-major, 3-D map when b3d) stays in the
+// accumulator; tgu: gate|up [M, 2N] for loading, tdgu: d(gate)|d(up) [M, 2N] for storing, {32, 32} boxes.
+int gemm_tcgen05_2cta_swiglu_bwd(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tgu, const CUtensorMap& tdgu,
+                                 bool b3d, int M, int N, int K, int* status, cudaStream_t stream) {
+  Gemm2Args args{nullptr, nullptr, 0, M, N, K, CTDK_EPI_STORE, 1, 1, 0, b3d ? 1 : 0, 1, 2, kStages2 - 1, status};
+  return launch2<false, true>(ta, tb, tgu, tdgu, args, stream);
 }
 
 }  // namespace ctdk

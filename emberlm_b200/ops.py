@@ -80,6 +80,20 @@ def mlp_in(x, w_gate_up, I, precision=lib.GEMM_TF32):
     return gu, act
 
 
+def mlp_in_backward(dy, w_down, gu, precision=lib.GEMM_TF32):
+    """d(gate)|d(up) [M, 2I] from dy [M, hid], down_proj.weight [hid, I] and the saved gate|up [M, 2I]."""
+    _chk(dy, "mlp_in_backward"), _chk(w_down, "mlp_in_backward"), _chk(gu, "mlp_in_backward")
+    M, K = dy.shape
+    I = w_down.shape[1]
+    if w_down.shape[0] != K or tuple(gu.shape) != (M, 2 * I):
+        raise RuntimeError("mlp_in_backward: shape mismatch")
+    dgu = torch.empty_like(gu)
+    scratch = torch.empty(M, I, device=dy.device, dtype=dy.dtype)
+    lib.call("ctdk_gemm_swiglu_bwd", dy.data_ptr(), w_down.data_ptr(), gu.data_ptr(), dgu.data_ptr(),
+             scratch.data_ptr(), M, I, K, precision, _s())
+    return dgu
+
+
 def swiglu(gu):
     _chk(gu, "swiglu")
     rows, two_i = gu.shape

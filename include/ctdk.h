@@ -86,6 +86,16 @@ int ctdk_gemm_ws(const float* A, const float* B, float* C, int64_t M, int64_t N,
  * (I not a multiple of 128, M < 256, unaligned pointers, 3xTF32) run as ctdk_gemm + ctdk_swiglu_fwd. */
 int ctdk_gemm_swiglu(const float* A, const float* W, float* gu, float* act, int64_t M, int64_t I,
                      int64_t K, int precision, void* stream);
+/* The matching backward step: d(act)[M, I] = dy[M, K] * Wd[K, I] (the dX product of down_proj,
+ * MatmulBackward, src/ops/matmul.cpp:120-168) followed by MulBackward and SiluBackward
+ * (src/ops/elementwise.cu:89-238): dgu[M, 2I] = d(gate) | d(up) with d(gate) = d(act) * up *
+ * silu'(gate), d(up) = d(act) * silu(gate), gate | up read from gu[M, 2I]. In the fused kernel
+ * d(act) never leaves the accumulator: the epilogue fetches the gate / up boxes by TMA, rewrites
+ * them in place and stores them. Shapes it does not take run as ctdk_gemm into dact_scratch[M, I]
+ * + ctdk_swiglu_bwd (dact_scratch may be NULL only when the fused kernel is known to apply). */
+int ctdk_gemm_swiglu_bwd(const float* dy, const float* Wd, const float* gu, float* dgu,
+                         float* dact_scratch, int64_t M, int64_t I, int64_t K, int precision,
+                         void* stream);
 
 /* Batched variant with full-matrix strides, as cublasSgemmStridedBatched in
  * ops::bmm_impl (src/ops/matmul.cpp:51-93). */

@@ -334,6 +334,19 @@ def test_fused_mlp_input_projection(M, I, K):
     assert np.abs(host(act) - want).max() <= 2e-2 * max(np.abs(want).max(), 1e-6)   # TF32 inputs
 
 
+@pytest.mark.parametrize("M,I,K", [(256, 256, 64), (1000, 320, 960), (4092, 2560, 960), (300, 96, 64), (100, 256, 32)])
+def test_fused_mlp_input_backward(M, I, K):
+    """down_proj dX GEMM with the SwiGLU backward in its epilogue against GEMM + swiglu_backward:
+    same accumulation order and the same formulas, so bit-identical."""
+    from emberlm_b200 import ops
+    dy, wd = dev(rnd((M, K), 63)), dev(rnd((K, I), 64, -0.2, 0.2))
+    gu = dev(rnd((M, 2 * I), 65, -3, 3))
+    got = ops.mlp_in_backward(dy, wd, gu)
+    dact = ops.matmul(dy, wd, False, False)
+    want = ops.swiglu_backward(gu, dact)
+    assert torch.equal(got, want)
+
+
 @pytest.mark.parametrize("n,H", [(0, 64), (1, 4), (257, 960), (4099, 576)])
 def test_row_gather_scatter_and_ce_input_gather(n, H):
     from emberlm_b200 import lib
