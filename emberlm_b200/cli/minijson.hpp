@@ -246,6 +246,10 @@ class Line {
     items_[k] = quote(v);
     return *this;
   }
+  Line& add_bool(const std::string& k, bool v) {
+    items_[k] = v ? "true" : "false";
+    return *this;
+  }
   std::string dump() const {
     std::string out = "{";
     bool first = true;

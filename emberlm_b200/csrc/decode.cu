@@ -281,6 +281,7 @@ struct Decoder {
   int64_t* graph_out = nullptr;
   cudaStream_t graph_stream = nullptr;
   int64_t prompt_len = 0, generated = 0;
+  int64_t stepped = 0;   // tokens fed one by one through ctdk_decode_step since the prefill
 };
 
 struct Bump2 {
@@ -386,7 +387,7 @@ ctdk_rope_params decode_rope_params(const ctdk_model_config& c) {
 }
 
 // One token: embedding of *cur_token at position *pos -> logits -> argmax -> counters += 1.
-int enqueue_token_step(Decoder& d, int64_t* out_tokens, cudaStream_t s) {
+int enqueue_token_forward(Decoder& d, cudaStream_t s) {
   const ctdk_model_config& c = d.cfg;
   const int hid = c.hidden_size, I = c.intermediate_size, D = c.head_dim, H = c.num_attention_heads,
             Hk = c.num_key_value_heads;
@@ -409,12 +410,19 @@ int enqueue_token_step(Decoder& d, int64_t* out_tokens, cudaStream_t s) {
     DTRY(gemv(P + w.wg, d.hm, d.gu, nullptr, 2 * I, hid, s, kPreRmsNorm, P + w.w_post, c.rms_norm_eps));
     DTRY(gemv(P + w.wd, d.gu, d.x, d.hm, hid, I, s, kPreSwiglu));
   }
-  DTRY(gemv(P + d.embed, d.x, d.logits, nullptr, c.vocab_size, hid, s, kPreRmsNorm, P + d.norm, c.rms_norm_eps));
-  argmax_kernel<<<1, 1024, 0, s>>>(d.logits, c.vocab_size, d.cur_token, out_tokens, d.counters + 1);
+  return gemv(P + d.embed, d.x, d.logits, nullptr, c.vocab_size, hid, s, kPreRmsNorm, P + d.norm, c.rms_norm_eps);
+}
+
+int enqueue_token_step(Decoder& d, int64_t* out_tokens, cudaStream_t s) {
+  DTRY(enqueue_token_forward(d, s));
+  argmax_kernel<<<1, 1024, 0, s>>>(d.logits, d.cfg.vocab_size, d.cur_token, out_tokens, d.counters + 1);
   DTRY(check_launch("decode argmax"));
   bump_kernel<<<1, 1, 0, s>>>(d.counters, d.counters + 1);
   return check_launch("decode bump");
 }
+
+__global__ void set_token_kernel(int64_t* cur, int64_t value) { *cur = value; }
+__global__ void bump_position_kernel(int* position) { *position += 1; }
 
 }  // namespace
 }  // namespace ctdk
@@ -513,6 +521,7 @@ int ctdk_decode_prefill(void* decoder, const int64_t* ids, int64_t T, void* stre
   set_counters_kernel<<<1, 1, 0, s>>>(d.counters, d.counters + 1, static_cast<int>(T), 0);
   d.prompt_len = T;
   d.generated = 0;
+  d.stepped = 0;
   return check_launch("decode counters");
 }
 
@@ -522,11 +531,29 @@ int ctdk_decode_logits(void* decoder, const float** logits) {
   return CTDK_OK;
 }
 
+int ctdk_decode_step(void* decoder, int64_t token, void* stream) {
+  CTDK_REQUIRE(decoder != nullptr, "ctdk_decode_step: null decoder");
+  Decoder& d = *static_cast<Decoder*>(decoder);
+  CTDK_REQUIRE(d.prompt_len > 0, "ctdk_decode_step: call ctdk_decode_prefill first");
+  CTDK_REQUIRE(d.generated == 0, "ctdk_decode_step: cannot be mixed with ctdk_decode_greedy after one prefill");
+  CTDK_REQUIRE(token >= 0 && token < d.cfg.vocab_size, "ctdk_decode_step: token id out of range");
+  CTDK_REQUIRE(d.prompt_len + d.stepped < d.max_seq, "ctdk_decode_step: the cache is full (max_seq %d)", d.max_seq);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  set_token_kernel<<<1, 1, 0, s>>>(d.cur_token, token);
+  DTRY(check_launch("decode set token"));
+  DTRY(enqueue_token_forward(d, s));
+  bump_position_kernel<<<1, 1, 0, s>>>(d.counters);
+  DTRY(check_launch("decode bump"));
+  ++d.stepped;
+  return CTDK_OK;
+}
+
 int ctdk_decode_greedy(void* decoder, int64_t n_new, int64_t* out_tokens, void* stream) {
   CTDK_REQUIRE(decoder && out_tokens, "ctdk_decode_greedy: null pointer");
   CTDK_REQUIRE(n_new >= 0, "ctdk_decode_greedy: negative token count");
   Decoder& d = *static_cast<Decoder*>(decoder);
   CTDK_REQUIRE(d.prompt_len > 0, "ctdk_decode_greedy: call ctdk_decode_prefill first");
+  CTDK_REQUIRE(d.stepped == 0, "ctdk_decode_greedy: cannot be mixed with ctdk_decode_step after one prefill");
   CTDK_REQUIRE(d.prompt_len + d.generated + n_new <= d.max_seq,
                "ctdk_decode_greedy: %lld more tokens would exceed max_seq %d", static_cast<long long>(n_new),
                d.max_seq);

@@ -67,7 +67,7 @@ def step_gemm_shapes(cfg, tok):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("kernel", choices=["gemm", "gemm-step", "attn", "adamw", "rmsnorm", "ce"])
+    ap.add_argument("kernel", choices=["gemm", "gemm-step", "attn", "adamw", "rmsnorm", "ce", "mlp"])
     ap.add_argument("--m", type=int, default=32736)
     ap.add_argument("--n", type=int, default=2560)
     ap.add_argument("--k", type=int, default=960)
@@ -100,6 +100,21 @@ def main():
             tot_fl += 2.0 * m * n * k
             print(json.dumps(r))
         print(json.dumps(dict(kernel="gemm-step", layer_plus_head_ms=tot_ms, tflops=tot_fl / tot_ms / 1e9)))
+    elif a.kernel == "mlp":
+        # gate|up projection + SwiGLU and its backward through the down projection: fused GEMM
+        # epilogues against GEMM + elementwise kernel (same results)
+        M, I, K = a.tok, a.n, a.hid
+        x, w = torch.randn(M, K, device="cuda"), torch.randn(2 * I, K, device="cuda") * 0.05
+        dy, wd = torch.randn(M, K, device="cuda"), torch.randn(K, I, device="cuda") * 0.05
+        gu = torch.randn(M, 2 * I, device="cuda")
+        for name, fn, fl in (
+                ("mlp_in fused", lambda: ops.mlp_in(x, w, I), 4.0 * M * I * K),
+                ("mlp_in gemm + swiglu", lambda: ops.swiglu(ops.matmul(x, w, False, True)), 4.0 * M * I * K),
+                ("mlp_in_backward fused", lambda: ops.mlp_in_backward(dy, wd, gu), 2.0 * M * I * K),
+                ("mlp_in_backward gemm + swiglu_backward",
+                 lambda: ops.swiglu_backward(gu, ops.matmul(dy, wd, False, False)), 2.0 * M * I * K)):
+            ms = _time(fn, a.iters, a.warmup, a.flush)
+            print(json.dumps({"kernel": name, "M": M, "I": I, "K": K, "ms": ms, "tflops": fl / ms / 1e9}))
     elif a.kernel == "attn":
         B, T, H, Hk, D = a.b, a.t, a.h, a.hk, a.d
         qkv = torch.randn(B * T, (H + 2 * Hk) * D, device="cuda")

@@ -346,6 +346,9 @@ int ctdk_engine_set_forward_callback(void* engine, ctdk_layer_callback cb, void*
  *   greedy  : appends n_new tokens to out_tokens (device int64), continuing where the last call
  *             stopped; token ids stay on the device, one CUDA graph launch per token when `stream`
  *             is not the legacy default stream;
+ *   step    : feeds ONE token chosen by the caller (a sampler, a forced token) at the next
+ *             position and leaves the logits of that position behind; not to be mixed with
+ *             greedy after the same prefill;
  *   logits  : device pointer to the [vocab] logits of the last processed position.
  * ------------------------------------------------------------------------------------ */
 int64_t ctdk_decode_workspace_bytes(const ctdk_model_config* cfg, int64_t max_seq);
@@ -354,6 +357,7 @@ int ctdk_decode_create(const ctdk_model_config* cfg, const float* params, void* 
 int ctdk_decode_destroy(void* decoder);
 int ctdk_decode_prefill(void* decoder, const int64_t* ids, int64_t T, void* stream);
 int ctdk_decode_greedy(void* decoder, int64_t n_new, int64_t* out_tokens, void* stream);
+int ctdk_decode_step(void* decoder, int64_t token, void* stream);
 int ctdk_decode_logits(void* decoder, const float** logits);
 
 #ifdef __cplusplus

@@ -66,3 +66,30 @@ def test_weights_header_is_parsed_and_unknown_architecture_rejected(tmp_path):
     cfg.write_text(json.dumps({"init_weights": str(w3), "data_dir": str(tmp_path)}))
     r = run("--config", str(cfg))
     assert r.returncode == 1 and "short read" in r.stderr
+
+
+GEN = Path(build.HERE) / "ctd_generate"
+
+
+def run_gen(request, *args):
+    return subprocess.run([str(GEN), *args], input=request, capture_output=True, text=True, timeout=120)
+
+
+def test_generate_usage_and_errors(tmp_path):
+    """tools/ctd_generate/main.cpp:33-44, 186-191: usage -> exit 2; any error -> stderr message, a
+    {"done": true, "reason": "error"} line on stdout and exit 1."""
+    assert GEN.exists()
+    r = run_gen('{"input_ids": [1]}')
+    assert r.returncode == 2 and "usage:" in r.stderr and "--model" in r.stderr
+    r = run_gen("not json", "--model", "x")
+    assert r.returncode == 1 and "[ctd_generate] error: json:" in r.stderr
+    last = json.loads(r.stdout.strip().splitlines()[-1])
+    assert last["done"] is True and last["reason"] == "error" and "json" in last["error"]
+    r = run_gen('{"max_new_tokens": 4}', "--model", "x")
+    assert r.returncode == 1 and "input_ids" in r.stderr
+    r = run_gen('{"input_ids": [1, 2]}', "--model", str(tmp_path / "missing.safetensors"))
+    assert r.returncode == 1 and "cannot open" in r.stderr
+    w = tmp_path / "w.safetensors"
+    safetensors_io.save_safetensors([("model.embed_tokens.weight", np.zeros((10, 7), np.float32))], w)
+    r = run_gen('{"input_ids": [1, 2]}', "--model", str(w))
+    assert r.returncode == 1 and "autodetect_config: unsupported hidden_size=7 vocab_size=10" in r.stderr

@@ -95,3 +95,50 @@ def test_two_steps_match_the_engine_then_resume(tmp_path):
     assert abs(events[-1]["loss"] - met["loss"]) <= 1e-4 * abs(met["loss"])
     opt = safetensors_io.load_safetensors(str(run_dir / "final.safetensors") + ".opt.safetensors")
     assert float(opt["optimizer.step"][0]) == 3.0
+
+
+def test_generate_matches_the_python_decoder(tmp_path):
+    """ctd_generate on SmolLM2-135M with random weights: greedy tokens equal Decoder.generate; a
+    sampled request with top_k = 1 (only the maximum survives) goes through the one-token-at-a-time
+    path and must produce the same ids; eos and the thinking budget end / steer the stream."""
+    from emberlm_b200 import engine as E
+    build.build()
+    gen = Path(build.HERE) / "ctd_generate"
+    cfg = E.make_config(**E.PRESETS["smollm2_135m"])
+    eng = E.TrainEngine(cfg, 1, 8, train=False)
+    eng.init_parameters(seed=11)
+    w0 = tmp_path / "m.safetensors"
+    safetensors_io.save_safetensors([(n, v.cpu().numpy()) for n, v in eng.named_parameters().items()], w0)
+    prompt = [5, 17, 300, 4242, 9, 77, 12345]
+    dec = E.Decoder(cfg, 64, params=eng.params[:eng.layout.total])
+    want = dec.generate(prompt, 24).cpu().tolist()
+
+    def ask(**req):
+        r = subprocess.run([str(gen), "--model", str(w0)], input=json.dumps(dict(input_ids=prompt, max_seq_len=64, **req)),
+                           capture_output=True, text=True, timeout=600)
+        assert r.returncode == 0, r.stderr[-1500:]
+        lines = [json.loads(l) for l in r.stdout.strip().splitlines()]
+        return [l["token"] for l in lines[:-1]], lines[-1]
+
+    toks, done = ask(max_new_tokens=24, temperature=0.0)
+    assert toks == want and done == {"done": True, "reason": "max_tokens", "generated_tokens": 24}
+    toks, done = ask(max_new_tokens=24, temperature=0.7, top_k=1, seed=3)
+    assert toks == want and done["reason"] == "max_tokens"
+    toks, done = ask(max_new_tokens=24, temperature=0.0, eos_ids=[want[5]])
+    stop = want.index(want[5])
+    assert toks == want[:stop + 1] and done["reason"] == "eos" and done["generated_tokens"] == stop + 1
+    toks, done = ask(max_new_tokens=200, temperature=0.0)            # the cache (64 positions) ends the run
+    assert done["reason"] == "max_seq_len" and toks[:24] == want and len(toks) <= 64 - len(prompt)
+    # thinking budget (main.cpp:139-170): tokens after the open marker are counted (the count restarts
+    # whenever the marker shows up again); once it reaches the budget the close marker is forced
+    budget, close = 3, [7, 8]
+    toks, done = ask(max_new_tokens=16, temperature=0.0, thinking_token_budget=budget, think_open_ids=[want[0]],
+                     think_close_ids=close)
+    count, forced_at = 0, None
+    for i, t in enumerate(want):
+        count = 0 if t == want[0] else count + 1
+        if count >= budget:
+            forced_at = i + 1
+            break
+    assert forced_at is not None and forced_at + 2 <= 16
+    assert toks[:forced_at] == want[:forced_at] and toks[forced_at:forced_at + 2] == close
