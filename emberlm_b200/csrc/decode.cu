@@ -26,6 +26,29 @@ namespace {
 // (silu(g)*u, include/ctd/nn/mlp.h:16-21) so that no separate kernel has to run per token.
 enum { kPreNone = 0, kPreRmsNorm = 1, kPreSwiglu = 2 };
 
+// Programmatic dependent launch: the kernels of a token step are launched with the
+// programmatic-stream-serialization attribute, so each one may be scheduled as soon as all CTAs of
+// its predecessor have passed pdl_launch() (the first thing they do), fetch what does not depend on
+// the predecessor (weights), and then block in pdl_wait() until the predecessor has completed and
+// its writes are visible. Without the attribute both calls return at once.
+__device__ __forceinline__ void pdl_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+template <typename... KArgs, typename... Args>
+cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 template <int PRE>
 __global__ void __launch_bounds__(256)
     gemv_kernel(const float* __restrict__ W, const float* __restrict__ x, float* __restrict__ y,
@@ -33,6 +56,23 @@ __global__ void __launch_bounds__(256)
   extern __shared__ float xs[];
   __shared__ float red[8];
   const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+  const int warp0 = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int nwarps = (gridDim.x * blockDim.x) >> 5;
+  const int K4 = K >> 2;
+  // The first weights of this warp's first row are requested before the input vector is staged
+  // (and normalised), so the prologue runs under the first memory round trip instead of before it.
+  constexpr int kPre = 8;
+  float4 wpre[kPre];
+  pdl_launch();
+  {
+    const float4* w4 = reinterpret_cast<const float4*>(W + static_cast<int64_t>(warp0 < N ? warp0 : 0) * K);
+#pragma unroll
+    for (int j = 0; j < kPre; ++j) {
+      const int i = lane + 32 * j;
+      wpre[j] = (warp0 < N && i < K4) ? __ldcs(w4 + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+  }
+  pdl_wait();   // x (and the residual) come from the previous kernel
   if (PRE == kPreSwiglu) {
     for (int i = threadIdx.x; i < K; i += blockDim.x) {
       const float g = x[i];
@@ -56,15 +96,25 @@ __global__ void __launch_bounds__(256)
     }
   }
   __syncthreads();
-  const int warp0 = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
-  const int nwarps = (gridDim.x * blockDim.x) >> 5;
-  const int K4 = K >> 2;
   const float4* x4 = reinterpret_cast<const float4*>(xs);
   for (int n = warp0; n < N; n += nwarps) {
     const float4* w4 = reinterpret_cast<const float4*>(W + static_cast<int64_t>(n) * K);
     float acc = 0.0f;
-    for (int i = lane; i < K4; i += 32) {
-      const float4 a = w4[i], b = x4[i];
+    int i0 = lane;
+    if (n == warp0) {   // the prefetched part of the first row
+#pragma unroll
+      for (int j = 0; j < kPre; ++j) {
+        const int i = lane + 32 * j;
+        if (i < K4) {
+          const float4 a = wpre[j], b = x4[i];
+          acc += a.x * b.x + a.y * b.y + a.z * b.z + a.w * b.w;
+        }
+      }
+      i0 = lane + 32 * kPre;
+    }
+#pragma unroll 4
+    for (int i = i0; i < K4; i += 32) {
+      const float4 a = __ldcs(w4 + i), b = x4[i];
       acc += a.x * b.x + a.y * b.y + a.z * b.z + a.w * b.w;
     }
     acc = warp_sum(acc);
@@ -80,6 +130,8 @@ __global__ void __launch_bounds__(256)
                            const int* __restrict__ pos_ptr, float* __restrict__ q_out,
                            float* __restrict__ kcache, float* __restrict__ vcache, int H, int Hk, int D,
                            int max_seq, float eps) {
+  pdl_launch();
+  pdl_wait();
   const int lane = threadIdx.x & 31;
   const int slot = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   if (slot >= H + 2 * Hk) return;
@@ -132,25 +184,44 @@ __global__ void __launch_bounds__(256)
   }
 }
 
-// One CTA of 1024 threads per query head: one thread per key computes its score (keys beyond
-// 1024 in further passes), block-wide softmax, then thread (d, part) sums its slice of P*V.
-__global__ void __launch_bounds__(1024)
+constexpr int kAttnSplits = 8;   // key ranges per head in the decode attention
+
+// Attention of the single new row over the cache, split over key ranges: CTA (h, sp) scores the
+// keys [sp * n, (sp + 1) * n) of head h (n = ceil(L / kAttnSplits)), and leaves the range's maximum,
+// exp-sum and exp-weighted V sum (relative to that maximum) in part[h][sp] = {m, l, o[D]};
+// decode_attn_combine_kernel merges the ranges. One CTA per head kept 16 SMs busy and took longer
+// than streaming the layer's weights.
+__global__ void __launch_bounds__(256)
     decode_attn_kernel(const float* __restrict__ q, const float* __restrict__ kcache,
-                       const float* __restrict__ vcache, float* __restrict__ out,
+                       const float* __restrict__ vcache, float* __restrict__ part,
                        const int* __restrict__ pos_ptr, int H, int Hk, int D, int max_seq, float scale) {
-  extern __shared__ float sm[];  // [max_seq] scores, [D] q, [1024] reduction scratch
-  float* sc = sm;
-  float* qs = sm + max_seq;
-  float* red = qs + D;
-  const int h = blockIdx.x, hk = h / (H / Hk);
+  extern __shared__ float sm[];  // [keys per range] scores, [D] q, [256] reduction scratch
+  pdl_launch();
+  pdl_wait();
+  const int h = blockIdx.x, sp = blockIdx.y, hk = h / (H / Hk);
   const int L = *pos_ptr + 1;
+  const int per = (L + kAttnSplits - 1) / kAttnSplits;
+  const int j0 = sp * per, j1 = min(L, j0 + per);
+  const int cap = ((max_seq + kAttnSplits - 1) / kAttnSplits + 3) & ~3;   // keeps the q staging 16-byte aligned
+  float* sc = sm;
+  float* qs = sm + cap;
+  float* red = qs + D;
+  float* dst = part + (static_cast<int64_t>(h) * kAttnSplits + sp) * (D + 2);
+  if (j0 >= j1) {   // empty range
+    if (threadIdx.x == 0) {
+      dst[0] = -FLT_MAX;
+      dst[1] = 0.0f;
+    }
+    for (int i = threadIdx.x; i < D; i += blockDim.x) dst[2 + i] = 0.0f;
+    return;
+  }
   const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, nw = blockDim.x >> 5;
   for (int i = threadIdx.x; i < D; i += blockDim.x) qs[i] = q[static_cast<int64_t>(h) * D + i];
   __syncthreads();
   const float* kb = kcache + static_cast<int64_t>(hk) * max_seq * D;
   const float* vb = vcache + static_cast<int64_t>(hk) * max_seq * D;
   float mx = -FLT_MAX;
-  for (int j = threadIdx.x; j < L; j += blockDim.x) {
+  for (int j = j0 + threadIdx.x; j < j1; j += blockDim.x) {
     const float4* kr = reinterpret_cast<const float4*>(kb + static_cast<int64_t>(j) * D);
     const float4* q4 = reinterpret_cast<const float4*>(qs);
     float acc = 0.0f;
@@ -159,7 +230,7 @@ __global__ void __launch_bounds__(1024)
       acc += a.x * b.x + a.y * b.y + a.z * b.z + a.w * b.w;
     }
     acc *= scale;
-    sc[j] = acc;
+    sc[j - j0] = acc;
     mx = fmaxf(mx, acc);
   }
   mx = warp_max(mx);
@@ -169,9 +240,9 @@ __global__ void __launch_bounds__(1024)
   for (int i = 0; i < nw; ++i) mx = fmaxf(mx, red[i]);
   __syncthreads();
   float sum = 0.0f;
-  for (int j = threadIdx.x; j < L; j += blockDim.x) {
-    const float e = __expf(sc[j] - mx);
-    sc[j] = e;
+  for (int j = j0 + threadIdx.x; j < j1; j += blockDim.x) {
+    const float e = __expf(sc[j - j0] - mx);
+    sc[j - j0] = e;
     sum += e;
   }
   sum = warp_sum(sum);
@@ -179,77 +250,104 @@ __global__ void __launch_bounds__(1024)
   __syncthreads();
   sum = 0.0f;
   for (int i = 0; i < nw; ++i) sum += red[i];
-  const float inv = 1.0f / sum;
   __syncthreads();
-  const int d = threadIdx.x % D, part = threadIdx.x / D, nparts = blockDim.x / D;
+  const int d = threadIdx.x % D, pt = threadIdx.x / D, nparts = blockDim.x / D;
   float acc = 0.0f;
-  for (int j = part; j < L; j += nparts) acc += sc[j] * vb[static_cast<int64_t>(j) * D + d];
-  red[part * D + d] = acc;
+  for (int j = j0 + pt; j < j1; j += nparts) acc += sc[j - j0] * vb[static_cast<int64_t>(j) * D + d];
+  red[pt * D + d] = acc;
   __syncthreads();
   if (threadIdx.x < D) {
     float t = 0.0f;
     for (int p = 0; p < nparts; ++p) t += red[p * D + threadIdx.x];
-    out[static_cast<int64_t>(h) * D + threadIdx.x] = t * inv;
+    dst[2 + threadIdx.x] = t;
+  }
+  if (threadIdx.x == 0) {
+    dst[0] = mx;
+    dst[1] = sum;
   }
 }
 
-// First index of the maximum (the reference's greedy sampler); stores the token as the next input
-// and appends it to out_tokens[*count].
-__global__ void __launch_bounds__(1024)
-    argmax_kernel(const float* __restrict__ logits, int V, int64_t* __restrict__ cur_token,
-                  int64_t* __restrict__ out_tokens, const int* __restrict__ count) {
-  __shared__ float bv[32];
-  __shared__ int bi[32];
-  float best = -FLT_MAX;
-  int idx = 0x7fffffff;
-  for (int i = threadIdx.x; i < V; i += blockDim.x) {
-    const float v = logits[i];
-    if (v > best) {
-      best = v;
-      idx = i;
-    }
+// out[h][d] = sum_sp o_sp[d] e^(m_sp - M) / sum_sp l_sp e^(m_sp - M), M = max_sp m_sp.
+__global__ void __launch_bounds__(128)
+    decode_attn_combine_kernel(const float* __restrict__ part, float* __restrict__ out, int D) {
+  pdl_launch();
+  pdl_wait();
+  const int h = blockIdx.x;
+  const float* p = part + static_cast<int64_t>(h) * kAttnSplits * (D + 2);
+  float M = -FLT_MAX;
+#pragma unroll
+  for (int s = 0; s < kAttnSplits; ++s) M = fmaxf(M, p[s * (D + 2)]);
+  float l = 0.0f, w[kAttnSplits];
+#pragma unroll
+  for (int s = 0; s < kAttnSplits; ++s) {
+    w[s] = __expf(p[s * (D + 2)] - M);
+    l += p[s * (D + 2) + 1] * w[s];
+  }
+  const float inv = 1.0f / l;
+  for (int d = threadIdx.x; d < D; d += blockDim.x) {
+    float o = 0.0f;
+#pragma unroll
+    for (int s = 0; s < kAttnSplits; ++s) o += p[s * (D + 2) + 2 + d] * w[s];
+    out[static_cast<int64_t>(h) * D + d] = o * inv;
+  }
+}
+
+// First index of the maximum (the reference's greedy sampler, src/core/sampling.cpp:13-20) over
+// many CTAs: each reduces its share of the logits and folds (value, index) into one 64-bit word
+// with atomicMax. The key orders floats as unsigned integers in the high half and prefers the
+// smaller index in the low half; argmax_finish_kernel turns the word into the next input token.
+__device__ __forceinline__ unsigned long long argmax_key(float v, int idx) {
+  unsigned u = __float_as_uint(v);
+  u = (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+  return (static_cast<unsigned long long>(u) << 32) | (0xFFFFFFFFu - static_cast<unsigned>(idx));
+}
+__global__ void __launch_bounds__(256)
+    argmax_kernel(const float* __restrict__ logits, int V, unsigned long long* __restrict__ word) {
+  __shared__ unsigned long long best_s[8];
+  pdl_launch();
+  pdl_wait();
+  unsigned long long best = 0ull;
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < V; i += gridDim.x * blockDim.x) {
+    const unsigned long long k = argmax_key(logits[i], i);
+    best = k > best ? k : best;
   }
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) {
-    const float ov = __shfl_xor_sync(0xffffffffu, best, o);
-    const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
-    if (ov > best || (ov == best && oi < idx)) {
-      best = ov;
-      idx = oi;
-    }
+    const unsigned long long other = __shfl_xor_sync(0xffffffffu, best, o);
+    best = other > best ? other : best;
   }
   const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
-  if (lane == 0) {
-    bv[wid] = best;
-    bi[wid] = idx;
-  }
+  if (lane == 0) best_s[wid] = best;
   __syncthreads();
-  if (wid == 0) {
-    best = bv[lane];
-    idx = bi[lane];
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-      const float ov = __shfl_xor_sync(0xffffffffu, best, o);
-      const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
-      if (ov > best || (ov == best && oi < idx)) {
-        best = ov;
-        idx = oi;
-      }
-    }
-    if (lane == 0) {
-      *cur_token = idx;
-      if (out_tokens != nullptr) out_tokens[*count] = idx;
-    }
+  if (threadIdx.x == 0) {
+    for (int i = 1; i < (blockDim.x >> 5); ++i) best = best_s[i] > best ? best_s[i] : best;
+    atomicMax(word, best);
   }
+}
+// Stores the winning token as the next input, appends it to out_tokens[*count], clears the word and
+// advances the counters (pos may point at a scratch int when the position must not move).
+__global__ void argmax_finish_kernel(unsigned long long* word, int64_t* cur_token, int64_t* out_tokens, int* pos,
+                                     int* count) {
+  pdl_launch();
+  pdl_wait();
+  const int64_t idx = static_cast<int64_t>(0xFFFFFFFFu - static_cast<unsigned>(*word & 0xFFFFFFFFull));
+  *cur_token = idx;
+  if (out_tokens != nullptr) out_tokens[*count] = idx;
+  *word = 0ull;
+  *pos += 1;
+  *count += 1;
 }
 
 __global__ void bump_kernel(int* pos, int* count) {
+  pdl_launch();
+  pdl_wait();
   *pos += 1;
   *count += 1;
 }
 __global__ void set_counters_kernel(int* pos, int* count, int p, int c) {
   *pos = p;
   *count = c;
+  *reinterpret_cast<unsigned long long*>(pos + 4) = 0ull;   // the argmax word lives behind the counters
 }
 
 }  // namespace
@@ -274,6 +372,7 @@ struct Decoder {
   // workspace
   float *rope_table, *kcache, *vcache;  // caches: [L][Hk][max_seq][D]
   float *x, *h1, *qkv, *q, *attn, *hm, *gu, *act, *logits;
+  float* attn_part;   // [H][kAttnSplits][D + 2] partial results of the decode attention
   float *pa, *pb, *pqkv, *pattn, *plse, *pgu, *pact;  // prefill buffers ([max_seq, ...])
   int64_t* cur_token;
   int* counters;  // [0] = position of the next token, [1] = tokens generated
@@ -319,8 +418,9 @@ void carve_decoder(Decoder& d, Bump2& b) {
   d.plse = b.floats(H * S);
   d.pgu = b.floats(S * 2 * I);
   d.pact = b.floats(S * I);
+  d.attn_part = b.floats(static_cast<int64_t>(H) * kAttnSplits * (D + 2));
   d.cur_token = reinterpret_cast<int64_t*>(b.floats(2));
-  d.counters = reinterpret_cast<int*>(b.floats(4));  // position, count, scratch
+  d.counters = reinterpret_cast<int*>(b.floats(8));  // position, count, scratch, -, then the 64-bit argmax word
 }
 
 int init_decoder(Decoder& d, const ctdk_model_config* cfg, int64_t max_seq) {
@@ -371,9 +471,11 @@ int gemv(const float* W, const float* x, float* y, const float* residual, int N,
   const int64_t need = (N + 7) / 8;
   const int grid = static_cast<int>(need < cap ? need : cap);
   const size_t smem = K * sizeof(float);
-  if (pre == kPreRmsNorm) gemv_kernel<kPreRmsNorm><<<grid, 256, smem, s>>>(W, x, y, residual, nw, eps, N, K);
-  else if (pre == kPreSwiglu) gemv_kernel<kPreSwiglu><<<grid, 256, smem, s>>>(W, x, y, residual, nw, eps, N, K);
-  else gemv_kernel<kPreNone><<<grid, 256, smem, s>>>(W, x, y, residual, nw, eps, N, K);
+  cudaError_t e;
+  if (pre == kPreRmsNorm) e = launch_pdl(gemv_kernel<kPreRmsNorm>, grid, 256, smem, s, W, x, y, residual, nw, eps, N, K);
+  else if (pre == kPreSwiglu) e = launch_pdl(gemv_kernel<kPreSwiglu>, grid, 256, smem, s, W, x, y, residual, nw, eps, N, K);
+  else e = launch_pdl(gemv_kernel<kPreNone>, grid, 256, smem, s, W, x, y, residual, nw, eps, N, K);
+  if (e != cudaSuccess) return fail(CTDK_ELAUNCH, "decode gemv: %s", cudaGetErrorString(e));
   return check_launch("decode gemv");
 }
 
@@ -398,13 +500,19 @@ int enqueue_token_forward(Decoder& d, cudaStream_t s) {
   for (int l = 0; l < c.num_hidden_layers; ++l) {
     const LayerW& w = d.lw[l];
     DTRY(gemv(P + w.wq, d.x, d.qkv, nullptr, d.QKVN, hid, s, kPreRmsNorm, P + w.w_in, c.rms_norm_eps));
-    decode_qkv_post_kernel<<<ceil_div((H + 2 * Hk) * 32, 256), 256, 0, s>>>(
-        d.qkv, c.qk_norm ? P + w.wqn : nullptr, c.qk_norm ? P + w.wkn : nullptr,
-        reinterpret_cast<const float2*>(d.rope_table), d.counters, d.q, d.kcache + l * cache_layer,
-        d.vcache + l * cache_layer, H, Hk, D, d.max_seq, c.rms_norm_eps);
+    if (launch_pdl(decode_qkv_post_kernel, ceil_div((H + 2 * Hk) * 32, 256), 256, 0, s, d.qkv,
+                   c.qk_norm ? P + w.wqn : nullptr, c.qk_norm ? P + w.wkn : nullptr,
+                   reinterpret_cast<const float2*>(d.rope_table), d.counters, d.q, d.kcache + l * cache_layer,
+                   d.vcache + l * cache_layer, H, Hk, D, d.max_seq, c.rms_norm_eps) != cudaSuccess)
+      return fail(CTDK_ELAUNCH, "decode qkv post: launch failed");
     DTRY(check_launch("decode qkv post"));
-    decode_attn_kernel<<<H, 1024, (d.max_seq + D + 1024) * sizeof(float), s>>>(
-        d.q, d.kcache + l * cache_layer, d.vcache + l * cache_layer, d.attn, d.counters, H, Hk, D, d.max_seq, scale);
+    if (launch_pdl(decode_attn_kernel, dim3(H, kAttnSplits), 256,
+                   ((d.max_seq + kAttnSplits - 1) / kAttnSplits + 4 + D + 256) * sizeof(float), s, d.q,
+                   d.kcache + l * cache_layer, d.vcache + l * cache_layer, d.attn_part, d.counters, H, Hk, D, d.max_seq,
+                   scale) != cudaSuccess)
+      return fail(CTDK_ELAUNCH, "decode attention: launch failed");
+    if (launch_pdl(decode_attn_combine_kernel, H, 128, 0, s, d.attn_part, d.attn, D) != cudaSuccess)
+      return fail(CTDK_ELAUNCH, "decode attention combine: launch failed");
     DTRY(check_launch("decode attention"));
     DTRY(gemv(P + w.wo, d.attn, d.hm, d.x, hid, H * D, s));
     DTRY(gemv(P + w.wg, d.hm, d.gu, nullptr, 2 * I, hid, s, kPreRmsNorm, P + w.w_post, c.rms_norm_eps));
@@ -415,10 +523,13 @@ int enqueue_token_forward(Decoder& d, cudaStream_t s) {
 
 int enqueue_token_step(Decoder& d, int64_t* out_tokens, cudaStream_t s) {
   DTRY(enqueue_token_forward(d, s));
-  argmax_kernel<<<1, 1024, 0, s>>>(d.logits, d.cfg.vocab_size, d.cur_token, out_tokens, d.counters + 1);
+  unsigned long long* word = reinterpret_cast<unsigned long long*>(d.counters + 4);
+  if (launch_pdl(argmax_kernel, 64, 256, 0, s, d.logits, d.cfg.vocab_size, word) != cudaSuccess)
+    return fail(CTDK_ELAUNCH, "decode argmax: launch failed");
   DTRY(check_launch("decode argmax"));
-  bump_kernel<<<1, 1, 0, s>>>(d.counters, d.counters + 1);
-  return check_launch("decode bump");
+  if (launch_pdl(argmax_finish_kernel, 1, 1, 0, s, word, d.cur_token, out_tokens, d.counters, d.counters + 1) != cudaSuccess)
+    return fail(CTDK_ELAUNCH, "decode argmax finish: launch failed");
+  return check_launch("decode argmax finish");
 }
 
 __global__ void set_token_kernel(int64_t* cur, int64_t value) { *cur = value; }
@@ -451,8 +562,9 @@ int ctdk_decode_create(const ctdk_model_config* cfg, const float* params, void* 
     delete d;
     return rc;
   }
-  CTDK_REQUIRE((static_cast<int64_t>(max_seq) + cfg->head_dim + 1024) * 4 <= 200 * 1024,
-               "ctdk_decode_create: max_seq too large for the decode attention kernel");
+  const int64_t attn_smem = ((static_cast<int64_t>(max_seq) + kAttnSplits - 1) / kAttnSplits + 4 + cfg->head_dim + 256) * 4;
+  CTDK_REQUIRE(attn_smem <= 200 * 1024, "ctdk_decode_create: max_seq too large for the decode attention kernel");
+  CTDK_REQUIRE(cfg->head_dim <= 256 && 256 % cfg->head_dim == 0, "ctdk_decode_create: head_dim must divide 256");
   d->params = params;
   Bump2 b(workspace);
   carve_decoder(*d, b);
@@ -461,7 +573,7 @@ int ctdk_decode_create(const ctdk_model_config* cfg, const float* params, void* 
     return fail(CTDK_EINVAL, "ctdk_decode_create: workspace too small");
   }
   cudaError_t e = cudaFuncSetAttribute(decode_attn_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                       static_cast<int>((max_seq + cfg->head_dim + 1024) * 4));
+                                       static_cast<int>(attn_smem));
   if (e != cudaSuccess) {
     delete d;
     return fail(CTDK_ELAUNCH, "ctdk_decode_create: %s", cudaGetErrorString(e));
@@ -561,10 +673,12 @@ int ctdk_decode_greedy(void* decoder, int64_t n_new, int64_t* out_tokens, void* 
   int64_t todo = n_new;
   if (todo > 0 && d.generated == 0) {
     // the first new token comes from the prefill logits; its position is the prompt length
-    argmax_kernel<<<1, 1024, 0, s>>>(d.logits, d.cfg.vocab_size, d.cur_token, out_tokens, d.counters + 1);
+    unsigned long long* word = reinterpret_cast<unsigned long long*>(d.counters + 4);
+    argmax_kernel<<<64, 256, 0, s>>>(d.logits, d.cfg.vocab_size, word);
     DTRY(check_launch("decode argmax"));
-    bump_kernel<<<1, 1, 0, s>>>(d.counters + 2, d.counters + 1);  // count += 1 (position unchanged)
-    DTRY(check_launch("decode bump"));
+    // count += 1; the position is unchanged (a scratch int takes the increment)
+    argmax_finish_kernel<<<1, 1, 0, s>>>(word, d.cur_token, out_tokens, d.counters + 2, d.counters + 1);
+    DTRY(check_launch("decode argmax finish"));
     d.generated = 1;
     --todo;
   }
