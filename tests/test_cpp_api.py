@@ -1,0 +1,36 @@
+"""The C++ `ctd::` mirror (include/ctd_b200.hpp): it compiles and links against the C-ABI library
+on any host; on a B200 the case list in tests/cpp/test_ctd_api.cpp runs and must pass."""
+import os
+import subprocess
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+PKG = os.path.join(ROOT, "emberlm_b200")
+CUDA = os.environ.get("CUDA_HOME", "/usr/local/cuda")
+
+
+def _build(tmp_path):
+    exe = str(tmp_path / "test_ctd_api")
+    cmd = ["g++", "-std=c++17", "-O1", "-Wall", "-Wextra", "-Werror",
+           "-I", os.path.join(ROOT, "include"), "-I", os.path.join(CUDA, "include"),
+           os.path.join(ROOT, "tests", "cpp", "test_ctd_api.cpp"), "-o", exe,
+           "-L", PKG, "-lctdk", "-L", os.path.join(CUDA, "lib64"), "-lcudart",
+           "-Wl,-rpath," + PKG, "-Wl,-rpath," + os.path.join(CUDA, "lib64")]
+    res = subprocess.run(cmd, capture_output=True, text=True)
+    assert res.returncode == 0, res.stderr[-4000:]
+    return exe
+
+
+def test_header_compiles_and_links(tmp_path):
+    assert os.path.exists(os.path.join(PKG, "libctdk.so")), "build the library first: python -m emberlm_b200.build"
+    _build(tmp_path)
+
+
+@pytest.mark.gpu
+def test_cpp_cases_pass_on_gpu(tmp_path):
+    exe = _build(tmp_path)
+    res = subprocess.run([exe], capture_output=True, text=True, timeout=600)
+    print(res.stdout[-6000:])
+    assert res.returncode == 0, res.stdout[-6000:] + res.stderr[-2000:]
+    assert "0 failed" in res.stdout
