@@ -36,6 +36,8 @@ WORKLOADS = {
     # name: (preset, global rows, seq_len, micro-batch rows, grad-accum micro-batches, checkpointing)
     "smollm2_135m_b4x512": ("smollm2_135m", 4, 512, 4, 1, False),
     "smollm2_360m_b32x1024": ("smollm2_360m", 32, 1024, 4, 8, False),
+    # one rank's share of the 8-GPU step above (for single-GPU profiles of the small-M kernels)
+    "smollm2_360m_b4x1024": ("smollm2_360m", 4, 1024, 4, 1, False),
     "qwen3_0_6b_b16x2048": ("qwen3_0_6b", 16, 2048, 2, 8, False),
     "llama3_2_1b_b32x2048": ("llama3_2_1b", 32, 2048, 4, 8, True),
     "qwen3_1_7b_b64x4096": ("qwen3_1_7b", 64, 4096, 2, 32, True),
