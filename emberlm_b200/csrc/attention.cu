@@ -259,6 +259,8 @@ template <int D>
 __global__ void __launch_bounds__(256)
     attn_delta_kernel(const float* __restrict__ out, const float* __restrict__ dout,
                       float* __restrict__ delta, int64_t B, int T, int H) {
+  pdl_launch();
+  pdl_wait();
   constexpr int LP = D / 4;          // lanes per item: 16 (D = 64) or 32 (D = 128)
   constexpr int UN = 4;              // items in flight per lane group
   const int sub = threadIdx.x % LP;
@@ -609,9 +611,9 @@ int ctdk_attn_bwd_p(const float* qkv, const float* out, const float* dout, const
     const int64_t need = (items + (256 / lp) * 4 - 1) / ((256 / lp) * 4);
     const int grid = static_cast<int>(need < cap ? need : cap);
     if (D == 64)
-      attn_delta_kernel<64><<<grid, 256, 0, s>>>(out, dout, delta, B, static_cast<int>(T), H);
+      launch_pdl(attn_delta_kernel<64>, dim3(grid), dim3(256), 0, s, out, dout, delta, B, static_cast<int>(T), H);
     else
-      attn_delta_kernel<128><<<grid, 256, 0, s>>>(out, dout, delta, B, static_cast<int>(T), H);
+      launch_pdl(attn_delta_kernel<128>, dim3(grid), dim3(256), 0, s, out, dout, delta, B, static_cast<int>(T), H);
   }
   rc = check_launch("ctdk_attn_bwd(delta)");
   if (rc != CTDK_OK) return rc;

@@ -122,6 +122,7 @@ __global__ void __launch_bounds__(192, FwdCfg<D>::kCtasPerSm)
   using C = FwdCfg<D>;
   constexpr int NC = D / 32;  // 32-float chunks per row
   extern __shared__ unsigned char smem_raw[];
+  pdl_launch();
   const uint32_t raw = smem_u32(smem_raw);
   unsigned char* smem = smem_raw + ((1024u - (raw & 1023u)) & 1023u);
   unsigned char* q_s = smem;
@@ -169,6 +170,7 @@ __global__ void __launch_bounds__(192, FwdCfg<D>::kCtasPerSm)
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  pdl_wait();   // inputs come from earlier kernels in the stream
   const uint32_t tm_o = tmem_base + 128u;
   auto tm_s = [&](uint32_t g) { return tmem_base + (g & 1u) * static_cast<uint32_t>(TK); };
   // g = running count of key steps over all items of this CTA: stage g & 1, phase (g >> 1) & 1.
@@ -458,7 +460,7 @@ int launch_fwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& 
   cudaError_t e =
       cudaFuncSetAttribute(attn_fwd_tc_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmem);
   if (e != cudaSuccess) return fail(CTDK_ELAUNCH, "attn_fwd(tcgen05): shared memory opt-in failed: %s", cudaGetErrorString(e));
-  attn_fwd_tc_kernel<D><<<grid, 192, C::kSmem, s>>>(tq, tk, tv, a);
+  launch_pdl(attn_fwd_tc_kernel<D>, dim3(grid), dim3(192), C::kSmem, s, tq, tk, tv, a);
   return check_launch("ctdk_attn_fwd(tcgen05)");
 }
 

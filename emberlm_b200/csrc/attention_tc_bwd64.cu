@@ -143,6 +143,7 @@ __global__ void __launch_bounds__(320, 1)
                          const __grid_constant__ CUtensorMap tm_km,   // qkv  {32, 64, 2, 1}       32-byte swizzle: K
                          const Bwd64Args args) {
   extern __shared__ unsigned char smem_raw[];
+  pdl_launch();
   const uint32_t raw = smem_u32(smem_raw);
   unsigned char* smem = smem_raw + ((1024u - (raw & 1023u)) & 1023u);
   unsigned char* q_land = smem;                        // Q tile as it arrives
@@ -191,6 +192,7 @@ __global__ void __launch_bounds__(320, 1)
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  pdl_wait();   // inputs come from earlier kernels in the stream
   const uint32_t tm_qa = tmem_base, tm_doa = tmem_base + 64u;
   // two dQ accumulators (items alternate), so that an item's result is read and stored while the
   // next item's first MMAs are already running
@@ -454,6 +456,7 @@ __global__ void __launch_bounds__(320, 1)
                           const __grid_constant__ CUtensorMap tm_kvt,   // qkv  {32, 128, 2, 1} 16-byte swizzle (K, V tiles)
                           const Bwd64Args args) {
   extern __shared__ unsigned char smem_raw[];
+  pdl_launch();
   const uint32_t raw = smem_u32(smem_raw);
   unsigned char* smem = smem_raw + ((1024u - (raw & 1023u)) & 1023u);
   unsigned char* stages = smem;                                   // [3] x {Q, dO K-major, Q, dO MN-major}
@@ -510,6 +513,7 @@ __global__ void __launch_bounds__(320, 1)
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  pdl_wait();   // inputs come from earlier kernels in the stream
   const uint32_t tm_ka = tmem_base, tm_va = tmem_base + 64u, tm_dv = tmem_base + 128u, tm_dk = tmem_base + 192u;
   auto tm_s = [&](uint32_t g) { return tmem_base + 256u + (g & 1u) * 128u; };    // S^T, later P^T
   auto tm_dp = [&](uint32_t g) { return tmem_base + 320u + (g & 1u) * 128u; };   // dP^T, later dS^T
@@ -861,7 +865,7 @@ int attn_bwd_dq_tc64(const float* qkv, const float* dout, const float* lse, cons
   cudaError_t e = cudaFuncSetAttribute(attn_bwd_dq64_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kDqSmem);
   if (e != cudaSuccess) return fail(CTDK_ELAUNCH, "attn_bwd dq(tcgen05): shared memory opt-in failed: %s", cudaGetErrorString(e));
   const int sms = sm_count();
-  attn_bwd_dq64_kernel<<<a.n_items < sms ? a.n_items : sms, 320, kDqSmem, stream>>>(tq, tdo, tkv, tkm, a);
+  launch_pdl(attn_bwd_dq64_kernel, dim3(a.n_items < sms ? a.n_items : sms), dim3(320), kDqSmem, stream, tq, tdo, tkv, tkm, a);
   return check_launch("ctdk_attn_bwd(dq, tcgen05)");
 }
 
@@ -906,7 +910,7 @@ int attn_bwd_dkv_tc64(const float* qkv, const float* dout, const float* lse, con
   cudaError_t e = cudaFuncSetAttribute(attn_bwd_dkv64_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kKvSmem);
   if (e != cudaSuccess) return fail(CTDK_ELAUNCH, "attn_bwd dkv(tcgen05): shared memory opt-in failed: %s", cudaGetErrorString(e));
   const int sms = sm_count();
-  attn_bwd_dkv64_kernel<<<a.n_items < sms ? a.n_items : sms, 320, kKvSmem, stream>>>(tqk, tdok, tqm, tdom, tkvt, a);
+  launch_pdl(attn_bwd_dkv64_kernel, dim3(a.n_items < sms ? a.n_items : sms), dim3(320), kKvSmem, stream, tqk, tdok, tqm, tdom, tkvt, a);
   return check_launch("ctdk_attn_bwd(dkv, tcgen05)");
 }
 

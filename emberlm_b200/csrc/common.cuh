@@ -7,6 +7,8 @@
 #include <cuda.h>
 #include <stdint.h>
 
+#include <cstdlib>
+
 #include "../../include/ctdk.h"
 
 namespace ctdk {
@@ -400,4 +402,38 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr, uint32_t 
 
 #endif  // __CUDACC__
 
+// Programmatic dependent launch. A kernel launched through launch_pdl() may be scheduled as soon as
+// every CTA of the kernel before it in the stream has passed pdl_launch() (or exited): its CTAs set
+// up barriers, tensor memory and descriptors while the predecessor drains, then block in pdl_wait()
+// until the predecessor has completed and its writes are visible. Every kernel launched this way
+// calls pdl_wait() before it touches global memory and before any thread exits, so completion
+// stays ordered along the stream. In a kernel launched the ordinary way both calls return at once.
+// CTDK_PDL=0 in the environment turns the attribute off.
+__device__ __forceinline__ void pdl_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+inline bool pdl_enabled() {
+  static const bool on = [] {
+    const char* e = std::getenv("CTDK_PDL");
+    return !(e != nullptr && e[0] == '0');
+  }();
+  return on;
+}
+
+template <typename... KArgs, typename... Args>
+cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s, Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 }  // namespace ctdk
+

@@ -26,29 +26,8 @@ namespace {
 // (silu(g)*u, include/ctd/nn/mlp.h:16-21) so that no separate kernel has to run per token.
 enum { kPreNone = 0, kPreRmsNorm = 1, kPreSwiglu = 2 };
 
-// Programmatic dependent launch: the kernels of a token step are launched with the
-// programmatic-stream-serialization attribute, so each one may be scheduled as soon as all CTAs of
-// its predecessor have passed pdl_launch() (the first thing they do), fetch what does not depend on
-// the predecessor (weights), and then block in pdl_wait() until the predecessor has completed and
-// its writes are visible. Without the attribute both calls return at once.
-__device__ __forceinline__ void pdl_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
-__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
-
-template <typename... KArgs, typename... Args>
-cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s, Args... args) {
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = grid;
-  cfg.blockDim = block;
-  cfg.dynamicSmemBytes = smem;
-  cfg.stream = s;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[0].val.programmaticStreamSerializationAllowed = 1;
-  cfg.attrs = attr;
-  cfg.numAttrs = 1;
-  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
-}
-
+// The kernels of a token step are launched with launch_pdl(): each one fetches what does not depend
+// on its predecessor (weights) before pdl_wait().
 template <int PRE>
 __global__ void __launch_bounds__(256)
     gemv_kernel(const float* __restrict__ W, const float* __restrict__ x, float* __restrict__ y,

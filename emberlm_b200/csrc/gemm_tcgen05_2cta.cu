@@ -161,6 +161,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
                           const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmD,
                           const Gemm2Args args) {
   extern __shared__ unsigned char smem_raw[];
+  pdl_launch();   // the next kernel in the stream may set itself up while this one runs
   const uint32_t raw = smem_u32(smem_raw);
   unsigned char* smem = smem_raw + ((1024u - (raw & 1023u)) & 1023u);
   const int n_stages = args.stages;
@@ -208,6 +209,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
   cluster_sync_all();  // both CTAs' barriers are initialised before any remote signal
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  pdl_wait();     // operands (and C, when it is accumulated into) come from earlier kernels
 
   if (warp == 0) {
     // ---------------- TMA producer (both CTAs) ----------------
@@ -460,6 +462,54 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
           for (int i = 0; i < 32; ++i) g[i] = g[i] / (1.0f + __expf(-g[i])) * u[i];
           send(g, &tmD, col);
         }
+      } else if (args.epilogue == CTDK_EPI_RESIDUAL && !atomic && args.vec_ok && (args.N & 3) == 0) {
+        // C = acc + aux. Lane i holds row i of a chunk after tcgen05.ld; read and written like
+        // that, every 16-byte access would touch its own 128-byte line. So the chunk goes through
+        // a 4 KB shared-memory tile (128-byte rows, 16-byte pieces XORed with the row number) and
+        // comes back with 8 lanes covering one 128-byte row: coalesced loads of aux (fetched one
+        // chunk ahead) and coalesced stores of C.
+        const int r0 = mb * 2 * BM2 + static_cast<int>(rank) * BM2 + q * 32;
+        const int lr = lane >> 3, lc = lane & 7;   // after the transpose: rows j*4+lr, columns lc*4..+3
+        float* stage = reinterpret_cast<float*>(epi_stage + q * 2 * kEpiBuf);
+        float4 X[8], Xn[8];
+        auto fetch = [&](int ch, float4 (&x)[8]) {
+          const int col = nb * BN2 + ch * 32 + lc * 4;
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const int64_t row = r0 + j * 4 + lr;
+            x[j] = (row < args.M && col < args.N) ? __ldg(reinterpret_cast<const float4*>(args.aux + row * args.ldc + col))
+                                                  : make_float4(0.f, 0.f, 0.f, 0.f);
+          }
+        };
+        fetch(0, X);
+#pragma unroll 1
+        for (int ch = 0; ch < BN2 / 32; ++ch) {
+          const int col0 = nb * BN2 + ch * 32;
+          if (col0 >= args.N) break;
+          if (ch + 1 < BN2 / 32) fetch(ch + 1, Xn);
+          float v[32];
+          tmem_ld_32x32(t_row + static_cast<uint32_t>(ch * 32), v);
+          float* buf = stage + (ch & 1) * (kEpiBuf / 4);
+#pragma unroll
+          for (int c = 0; c < 8; ++c)
+            *reinterpret_cast<float4*>(buf + lane * 32 + ((c ^ (lane & 7)) << 2)) =
+                make_float4(v[4 * c], v[4 * c + 1], v[4 * c + 2], v[4 * c + 3]);
+          __syncwarp();
+          const int col = col0 + lc * 4;
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const int rl = j * 4 + lr;
+            const int64_t row = r0 + rl;
+            float4 o = *reinterpret_cast<const float4*>(buf + rl * 32 + ((lc ^ (rl & 7)) << 2));
+            o.x += X[j].x;
+            o.y += X[j].y;
+            o.z += X[j].z;
+            o.w += X[j].w;
+            if (row < args.M && col < args.N) *reinterpret_cast<float4*>(args.C + row * args.ldc + col) = o;
+          }
+#pragma unroll
+          for (int j = 0; j < 8; ++j) X[j] = Xn[j];
+        }
       } else
 #pragma unroll 1
       for (int ch = 0; ch < BN2 / 32; ++ch) {
@@ -571,7 +621,8 @@ int launch2(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc,
   const int tiles = ((args.M + 255) / 256) * (args.swiglu == 1 ? args.N / (BN2 / 2) : (args.N + BN2 - 1) / BN2) * args.splits;
   int pairs = sm_count() / 2;
   if (tiles < pairs) pairs = tiles;
-  kern<<<2 * pairs, 192, kSmem2, stream>>>(ta, tb, tc, td, args);
+  e = launch_pdl(kern, dim3(2 * pairs), dim3(192), kSmem2, stream, ta, tb, tc, td, args);
+  if (e != cudaSuccess) return fail(CTDK_ELAUNCH, "gemm(2cta): launch failed: %s", cudaGetErrorString(e));
   return check_launch("ctdk_gemm(tcgen05, cta pair)");
 }
 

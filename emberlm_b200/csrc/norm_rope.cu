@@ -50,6 +50,8 @@ __global__ void __launch_bounds__(256) rmsnorm_fwd_kernel(const float* __restric
                                                           float* __restrict__ rstd,
                                                           int64_t rows, int H4, float inv_H,
                                                           float eps) {
+  pdl_launch();
+  pdl_wait();
   __shared__ float red[2 * 1 * 32];
   const float4* w4 = reinterpret_cast<const float4*>(w);
   float4 wv[NV];
@@ -118,6 +120,8 @@ __global__ void __launch_bounds__(256)
                        const float* __restrict__ w, float* __restrict__ dx,
                        float* __restrict__ partial, int64_t rows, int H4, float inv_H,
                        float eps, int add_to_dx) {
+  pdl_launch();
+  pdl_wait();
   __shared__ float red[2 * 2 * 32];
   const float4* w4 = reinterpret_cast<const float4*>(w);
   float4 wv[NV], dwv[NV];
@@ -242,6 +246,8 @@ __global__ void __launch_bounds__(128) dw_finalize_kernel(const float* __restric
 __global__ void __launch_bounds__(256) dw_finalize_wide_kernel(const float* __restrict__ partial,
                                                                float* __restrict__ dw, int nparts,
                                                                int H, int accumulate) {
+  pdl_launch();
+  pdl_wait();
   __shared__ float red[8][33];
   const int cl = threadIdx.x & 31, rg = threadIdx.x >> 5;
   const int c = blockIdx.x * 32 + cl;
@@ -364,6 +370,8 @@ __global__ void __launch_bounds__(256)
                             float* __restrict__ rstd_q, float* __restrict__ rstd_k,
                             const float2* __restrict__ table, int64_t rows, int64_t T, int H,
                             int Hk, float eps) {
+  pdl_launch();
+  pdl_wait();
   constexpr int D = 64 * NP, Dh = 32 * NP, TPH = 8 * NP;  // threads per head slot
   const int HT = H + 2 * Hk;
   const int64_t items = rows * HT;
@@ -423,6 +431,8 @@ __global__ void __launch_bounds__(256)
                             const float* __restrict__ rstd_q, const float* __restrict__ rstd_k,
                             float* __restrict__ partial, const float2* __restrict__ table,
                             int64_t rows, int64_t T, int H, int Hk) {
+  pdl_launch();
+  pdl_wait();
   constexpr int D = 64 * NP, Dh = 32 * NP, TPH = 8 * NP;
   __shared__ float sdw[2][D];
   const int HT = H + 2 * Hk, HQK = H + Hk;
@@ -504,15 +514,15 @@ __global__ void __launch_bounds__(256)
 template <int NV>
 void launch_rmsnorm_fwd(const float* x, const float* w, float* y, float* rstd, int64_t rows,
                         int H, float eps, int threads, int grid, cudaStream_t s) {
-  rmsnorm_fwd_kernel<NV><<<grid, threads, 0, s>>>(x, w, y, rstd, rows, H / 4,
-                                                  1.0f / static_cast<float>(H), eps);
+  launch_pdl(rmsnorm_fwd_kernel<NV>, dim3(grid), dim3(threads), 0, s, x, w, y, rstd, rows, H / 4,
+             1.0f / static_cast<float>(H), eps);
 }
 template <int NV>
 void launch_rmsnorm_bwd(const float* dy, const float* x, const float* w, float* dx,
                         float* partial, int64_t rows, int H, float eps, int add, int threads,
                         int grid, cudaStream_t s) {
-  rmsnorm_bwd_kernel<NV><<<grid, threads, 0, s>>>(dy, x, w, dx, partial, rows, H / 4,
-                                                  1.0f / static_cast<float>(H), eps, add);
+  launch_pdl(rmsnorm_bwd_kernel<NV>, dim3(grid), dim3(threads), 0, s, dy, x, w, dx, partial, rows, H / 4,
+             1.0f / static_cast<float>(H), eps, add);
 }
 
 }  // namespace
@@ -594,7 +604,7 @@ int ctdk_rmsnorm_bwd(const float* dy, const float* x, const float* w, float* dx,
   }
   int rc = check_launch("ctdk_rmsnorm_bwd");
   if (rc != CTDK_OK) return rc;
-  dw_finalize_wide_kernel<<<ceil_div(H, 32), 256, 0, s>>>(dw_scratch, dw, grid, H, accumulate_dw);
+  launch_pdl(dw_finalize_wide_kernel, dim3(ceil_div(H, 32)), dim3(256), 0, s, dw_scratch, dw, grid, H, accumulate_dw);
   return check_launch("ctdk_rmsnorm_bwd(finalize)");
 }
 
@@ -737,11 +747,11 @@ int ctdk_qk_norm_rope_fwd(const float* qkv, float* qkv_out, const float* wq, con
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const float2* tb = reinterpret_cast<const float2*>(rope_table);
   if (D == 64)
-    qk_norm_rope_fwd_kernel<1><<<grid, 256, 0, s>>>(qkv, qkv_out, wq, wk, rstd_q, rstd_k, tb,
-                                                    rows, T, H, Hk, eps);
+    launch_pdl(qk_norm_rope_fwd_kernel<1>, dim3(grid), dim3(256), 0, s, qkv, qkv_out, wq, wk, rstd_q, rstd_k, tb, rows, T, H,
+               Hk, eps);
   else
-    qk_norm_rope_fwd_kernel<2><<<grid, 256, 0, s>>>(qkv, qkv_out, wq, wk, rstd_q, rstd_k, tb,
-                                                    rows, T, H, Hk, eps);
+    launch_pdl(qk_norm_rope_fwd_kernel<2>, dim3(grid), dim3(256), 0, s, qkv, qkv_out, wq, wk, rstd_q, rstd_k, tb, rows, T, H,
+               Hk, eps);
   return check_launch("ctdk_qk_norm_rope_fwd");
 }
 
@@ -780,11 +790,11 @@ int ctdk_qk_norm_rope_bwd(float* dqkv, const float* qkv_pre, const float* wq, co
   const int grid = static_cast<int>(need < cap ? need : cap);
   const float2* tb = reinterpret_cast<const float2*>(rope_table);
   if (D == 64)
-    qk_norm_rope_bwd_kernel<1><<<grid, 256, 0, s>>>(dqkv, qkv_pre, wq, wk, rstd_q, rstd_k,
-                                                    scratch, tb, rows, T, H, Hk);
+    launch_pdl(qk_norm_rope_bwd_kernel<1>, dim3(grid), dim3(256), 0, s, dqkv, qkv_pre, wq, wk, rstd_q, rstd_k, scratch, tb,
+               rows, T, H, Hk);
   else
-    qk_norm_rope_bwd_kernel<2><<<grid, 256, 0, s>>>(dqkv, qkv_pre, wq, wk, rstd_q, rstd_k,
-                                                    scratch, tb, rows, T, H, Hk);
+    launch_pdl(qk_norm_rope_bwd_kernel<2>, dim3(grid), dim3(256), 0, s, dqkv, qkv_pre, wq, wk, rstd_q, rstd_k, scratch, tb,
+               rows, T, H, Hk);
   int rc = check_launch("ctdk_qk_norm_rope_bwd");
   if (rc != CTDK_OK || !has_norm) return rc;
   qk_dw_finalize_kernel<<<ceil_div(2 * D, 128), 128, 0, s>>>(scratch, dwq, dwk, grid, D,
