@@ -499,7 +499,7 @@ int attn_fwd_tcgen05(const float* qkv, float* out, float* lse, int64_t B, int64_
   a.status = device_status_word();
   if (a.status == nullptr) return fail(CTDK_ELAUNCH, "attn_fwd(tcgen05): no status word");
   // persistent CTAs: as many as fit on the device at once
-  const int64_t slots = static_cast<int64_t>(sm_count()) * (D == 64 ? 2 : 1);
+  const int64_t slots = static_cast<int64_t>(sm_budget()) * (D == 64 ? 2 : 1);
   dim3 grid(static_cast<unsigned>(items < slots ? items : slots));
   return D == 64 ? launch_fwd<64>(tq, tk, tv, a, grid, stream) : launch_fwd<128>(tq, tk, tv, a, grid, stream);
 }

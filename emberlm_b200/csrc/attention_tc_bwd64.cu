@@ -864,7 +864,7 @@ int attn_bwd_dq_tc64(const float* qkv, const float* dout, const float* lse, cons
   if (rc != CTDK_OK) return rc;
   cudaError_t e = cudaFuncSetAttribute(attn_bwd_dq64_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kDqSmem);
   if (e != cudaSuccess) return fail(CTDK_ELAUNCH, "attn_bwd dq(tcgen05): shared memory opt-in failed: %s", cudaGetErrorString(e));
-  const int sms = sm_count();
+  const int sms = sm_budget();
   launch_pdl(attn_bwd_dq64_kernel, dim3(a.n_items < sms ? a.n_items : sms), dim3(320), kDqSmem, stream, tq, tdo, tkv, tkm, a);
   return check_launch("ctdk_attn_bwd(dq, tcgen05)");
 }
@@ -909,7 +909,7 @@ int attn_bwd_dkv_tc64(const float* qkv, const float* dout, const float* lse, con
   if (rc != CTDK_OK) return rc;
   cudaError_t e = cudaFuncSetAttribute(attn_bwd_dkv64_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kKvSmem);
   if (e != cudaSuccess) return fail(CTDK_ELAUNCH, "attn_bwd dkv(tcgen05): shared memory opt-in failed: %s", cudaGetErrorString(e));
-  const int sms = sm_count();
+  const int sms = sm_budget();
   launch_pdl(attn_bwd_dkv64_kernel, dim3(a.n_items < sms ? a.n_items : sms), dim3(320), kKvSmem, stream, tqk, tdok, tqm, tdom, tkvt, a);
   return check_launch("ctdk_attn_bwd(dkv, tcgen05)");
 }

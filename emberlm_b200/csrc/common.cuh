@@ -21,6 +21,7 @@ int check_launch(const char* what);
 
 // Number of SMs of the current device (cached per device).
 int sm_count();
+int sm_budget();   // sm_count() less the SMs set aside by ctdk_reserve_sms()
 
 // Device status word shared by all kernels that contain bounded waits. It is a
 // 4-int array in global memory: [0] = first error code, [1] = where, [2..3] = detail.

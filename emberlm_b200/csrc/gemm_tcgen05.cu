@@ -503,7 +503,7 @@ int gemm_tcgen05(const float* A, const float* B, float* Cp, int64_t M, int64_t N
   // unit x relative cost of a k-block (a 128-wide tile does half the work of a 256-wide one
   // but moves 2/3 of the operand bytes, hence the 0.6). Splitting K only pays when the output
   // tiles alone cannot fill the SMs (weight gradients: few tiles, K = all tokens).
-  const int sms = sm_count();
+  const int sms = sm_budget();
   const int64_t m_blocks = (M + BM - 1) / BM;
   const int64_t k_blocks = (K + BK - 1) / BK;
   int bn = 64, splits = 1;

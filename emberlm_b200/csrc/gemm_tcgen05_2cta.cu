@@ -619,7 +619,7 @@ int launch2(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc,
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem2);
   if (e != cudaSuccess) return fail(CTDK_ELAUNCH, "gemm(2cta): shared memory opt-in failed: %s", cudaGetErrorString(e));
   const int tiles = ((args.M + 255) / 256) * (args.swiglu == 1 ? args.N / (BN2 / 2) : (args.N + BN2 - 1) / BN2) * args.splits;
-  int pairs = sm_count() / 2;
+  int pairs = sm_budget() / 2;
   if (tiles < pairs) pairs = tiles;
   e = launch_pdl(kern, dim3(2 * pairs), dim3(192), kSmem2, stream, ta, tb, tc, td, args);
   if (e != cudaSuccess) return fail(CTDK_ELAUNCH, "gemm(2cta): launch failed: %s", cudaGetErrorString(e));

@@ -242,24 +242,35 @@ __global__ void __launch_bounds__(128) dw_finalize_kernel(const float* __restric
   dw[c] = accumulate ? dw[c] + acc : acc;
 }
 
-// Same column sum for many partial rows: 256 threads = 8 row groups x 32 columns per CTA.
-__global__ void __launch_bounds__(256) dw_finalize_wide_kernel(const float* __restrict__ partial,
-                                                               float* __restrict__ dw, int nparts,
-                                                               int H, int accumulate) {
+// Same column sum for many partial rows: 1024 threads = 32 row groups x 32 columns per CTA, four
+// independent running sums per thread so that four loads are in flight (the pass is latency-bound:
+// a few MB read by H / 32 CTAs).
+__global__ void __launch_bounds__(1024) dw_finalize_wide_kernel(const float* __restrict__ partial,
+                                                                float* __restrict__ dw, int nparts,
+                                                                int H, int accumulate) {
   pdl_launch();
   pdl_wait();
-  __shared__ float red[8][33];
+  __shared__ float red[32][33];
   const int cl = threadIdx.x & 31, rg = threadIdx.x >> 5;
   const int c = blockIdx.x * 32 + cl;
-  float acc = 0.0f;
-  if (c < H)
-    for (int p = rg; p < nparts; p += 8) acc += partial[static_cast<int64_t>(p) * H + c];
-  red[rg][cl] = acc;
+  float a0 = 0.0f, a1 = 0.0f, a2 = 0.0f, a3 = 0.0f;
+  if (c < H) {
+    const float* src = partial + c;
+    int p = rg;
+    for (; p + 96 < nparts; p += 128) {
+      a0 += src[static_cast<int64_t>(p) * H];
+      a1 += src[static_cast<int64_t>(p + 32) * H];
+      a2 += src[static_cast<int64_t>(p + 64) * H];
+      a3 += src[static_cast<int64_t>(p + 96) * H];
+    }
+    for (; p < nparts; p += 32) a0 += src[static_cast<int64_t>(p) * H];
+  }
+  red[rg][cl] = (a0 + a1) + (a2 + a3);
   __syncthreads();
   if (rg == 0 && c < H) {
     float t = 0.0f;
 #pragma unroll
-    for (int r = 0; r < 8; ++r) t += red[r][cl];
+    for (int r = 0; r < 32; ++r) t += red[r][cl];
     dw[c] = accumulate ? dw[c] + t : t;
   }
 }
@@ -604,7 +615,7 @@ int ctdk_rmsnorm_bwd(const float* dy, const float* x, const float* w, float* dx,
   }
   int rc = check_launch("ctdk_rmsnorm_bwd");
   if (rc != CTDK_OK) return rc;
-  launch_pdl(dw_finalize_wide_kernel, dim3(ceil_div(H, 32)), dim3(256), 0, s, dw_scratch, dw, grid, H, accumulate_dw);
+  launch_pdl(dw_finalize_wide_kernel, dim3(ceil_div(H, 32)), dim3(1024), 0, s, dw_scratch, dw, grid, H, accumulate_dw);
   return check_launch("ctdk_rmsnorm_bwd(finalize)");
 }
 

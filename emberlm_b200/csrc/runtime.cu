@@ -90,6 +90,14 @@ int sm_count() {
   return g_sm_count[dev];
 }
 
+// SMs left to the persistent tensor-core kernels (one CTA, or one CTA pair, per SM): all of them,
+// less what ctdk_reserve_sms() set aside for kernels of other streams.
+static int g_reserved_sms = 0;
+int sm_budget() {
+  const int n = sm_count() - g_reserved_sms;
+  return n < 2 ? 2 : n;
+}
+
 int* device_status_word() {
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return nullptr;
@@ -124,6 +132,11 @@ extern "C" {
 const char* ctdk_last_error(void) { return ctdk::g_err; }
 
 int ctdk_sm_count(void) { return ctdk::sm_count(); }
+int ctdk_reserve_sms(int n) {
+  if (n < 0 || n >= ctdk::sm_count()) return ctdk::fail(CTDK_EINVAL, "ctdk_reserve_sms: n out of range");
+  ctdk::g_reserved_sms = n & ~1;   // whole CTA pairs
+  return CTDK_OK;
+}
 
 long long ctdk_launch_count(void) { return ctdk::g_launches.load(); }
 

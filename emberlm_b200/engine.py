@@ -258,6 +258,10 @@ class TrainEngine:
             self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
         else:
             self.world, self.rank = 1, 0
+        if self.world > 1:
+            # The collectives run beside the backward pass on their own stream and hold a few SMs
+            # while they do; a persistent GEMM that wants every SM would then run in two waves.
+            lib.check(_L.ctdk_reserve_sms(int(os.environ.get("CTDK_DP_RESERVED_SMS", "0"))))
         self.layout = model_layout(cfg)
         # arena padded so that it splits evenly over ranks in 64-float units
         self.total = padded_total(self.layout.total, self.world)

@@ -92,6 +92,8 @@ for _name, _args in _SIGS.items():
 _lib.ctdk_last_error.restype = C.c_char_p
 _lib.ctdk_last_error.argtypes = []
 _lib.ctdk_sm_count.restype = C.c_int
+_lib.ctdk_reserve_sms.restype = C.c_int
+_lib.ctdk_reserve_sms.argtypes = [C.c_int]
 _lib.ctdk_launch_count.restype = C.c_longlong
 _lib.ctdk_launch_count.argtypes = []
 _lib.ctdk_prof_enable.restype = C.c_int

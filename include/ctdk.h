@@ -31,6 +31,11 @@ const char* ctdk_last_error(void);
  * `stream`. Returns 0 or CTDK_ETIMEOUT; where[0..3] (optional) receives the raw words. */
 int ctdk_device_status(void* stream, int* where);
 int ctdk_sm_count(void);
+/* Leaves n SMs (rounded down to whole pairs) out of the grids of the persistent tensor-core kernels
+ * (GEMM, attention), for kernels that run beside them on other streams: a collective that takes a few
+ * SMs while a one-wave persistent GEMM wants all of them makes that GEMM run in two waves. 0 restores
+ * the default. Process-wide; set it before the step loop, not between launches in flight. */
+int ctdk_reserve_sms(int n);
 /* Number of kernel launches this library has enqueued in this process. */
 long long ctdk_launch_count(void);
 /* Optional live timing: while enabled, every launch of a profiled class is bracketed by CUDA
