@@ -50,6 +50,7 @@ _lib = load()
 
 _p, _i, _l, _f = C.c_void_p, C.c_int, C.c_int64, C.c_float
 _SIGS = {
+    "ctdk_reserve_sms": [_i],
     "ctdk_gemm": [_p, _p, _p, _l, _l, _l, _l, _l, _l, _i, _i, _i, _i, _p, _p],
     "ctdk_gemm_ws": [_p, _p, _p, _l, _l, _l, _l, _l, _l, _i, _i, _i, _i, _p, _p, _l, _p],
     "ctdk_attn_fwd_p": [_p, _p, _p, _l, _l, _i, _i, _i, _i, _p],
@@ -92,8 +93,6 @@ for _name, _args in _SIGS.items():
 _lib.ctdk_last_error.restype = C.c_char_p
 _lib.ctdk_last_error.argtypes = []
 _lib.ctdk_sm_count.restype = C.c_int
-_lib.ctdk_reserve_sms.restype = C.c_int
-_lib.ctdk_reserve_sms.argtypes = [C.c_int]
 _lib.ctdk_launch_count.restype = C.c_longlong
 _lib.ctdk_launch_count.argtypes = []
 _lib.ctdk_prof_enable.restype = C.c_int
