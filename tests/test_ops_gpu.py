@@ -219,6 +219,18 @@ def test_gemm_epilogues_and_fallbacks(K):
     assert np.array_equal(host(c5), (ref5 + base5).astype(F32))
     c6 = K.matmul(dev(a5), dev(b5), True, False, epilogue=lib.EPI_RESIDUAL, aux=dev(base5))
     assert np.array_equal(host(c6), (ref5 + base5).astype(F32))
+    # paired-CTA kernel: few tiles with long K (split-K) and a partly empty last round, every epilogue
+    for (m7, n7, k7, ta7, tb7) in [(512, 512, 4096, True, False), (4092, 960, 960, False, True), (4092, 1600, 960, False, False)]:
+        a7 = ints((k7, m7) if ta7 else (m7, k7), 43)
+        b7 = ints((n7, k7) if tb7 else (k7, n7), 44)
+        base7 = ints((m7, n7), 45)
+        ref7 = (a7.T if ta7 else a7).astype(np.float64) @ (b7.T if tb7 else b7).astype(np.float64)
+        assert np.array_equal(host(K.matmul(dev(a7), dev(b7), ta7, tb7)), ref7.astype(F32))
+        c7 = dev(base7.copy())
+        K.matmul(dev(a7), dev(b7), ta7, tb7, out=c7, epilogue=lib.EPI_ACCUMULATE)
+        assert np.array_equal(host(c7), (ref7 + base7).astype(F32))
+        c8 = K.matmul(dev(a7), dev(b7), ta7, tb7, epilogue=lib.EPI_RESIDUAL, aux=dev(base7))
+        assert np.array_equal(host(c8), (ref7 + base7).astype(F32))
     # SIMT path: odd leading dimensions, exact fp32 (tests/test_matmul.cpp tolerance 1e-4)
     a3, b3 = rnd((5, 7), 27), rnd((7, 6), 28)
     np.testing.assert_allclose(host(K.matmul(dev(a3), dev(b3))), a3 @ b3, atol=1e-5)
