@@ -111,18 +111,18 @@ def test_shard_segments_cover_every_tensor_once():
     for world in (1, 2, 4, 8):
         total = E.padded_total(layout.total, world)
         assert total % (64 * world) == 0 and total >= layout.total
-        wd = np.full(total, -1.0)
+        wd = np.full(total, -1, np.int8)   # per element: -1 unowned, 1 decayed, 0 not decayed
         for r in range(world):
             lo, hi = E.shard_bounds(total, world, r)
             ends, wds = E.build_segments(layout, 0.01, lo, hi)
             assert ends[-1] == hi - lo and all(e % 4 == 0 for e in ends) and ends == sorted(ends)
             start = 0
             for e, w in zip(ends, wds):
-                wd[lo + start:lo + e] = w
+                wd[lo + start:lo + e] = 1 if w > 0 else 0
                 start = e
         assert (wd >= 0).all()
         for o, k, d in zip(layout.offsets, layout.numels, layout.decay):
-            assert (wd[o:o + k] == (0.01 if d else 0.0)).all()
+            assert (wd[o:o + k] == (1 if d else 0)).all()
 
 
 def test_buckets_partition_the_arena_and_know_when_they_are_complete():
@@ -145,7 +145,7 @@ def test_buckets_partition_the_arena_and_know_when_they_are_complete():
                             if o < hi and o + k > lo]
                 assert ready == min(touching)
             # slices of all ranks tile every bucket; per-slice decay segments match the tensors
-            wd = np.full(total, -1.0)
+            wd = np.full(total, -1, np.int8)
             owned = 0
             for r in range(world):
                 for lo, hi, _ in buckets:
@@ -155,12 +155,12 @@ def test_buckets_partition_the_arena_and_know_when_they_are_complete():
                     assert ends[-1] == b - a
                     start = 0
                     for e, w in zip(ends, wds):
-                        assert (wd[a + start:a + e] == -1.0).all()
-                        wd[a + start:a + e] = w
+                        assert (wd[a + start:a + e] == -1).all()
+                        wd[a + start:a + e] = 1 if w > 0 else 0
                         start = e
             assert owned == total and (wd >= 0).all()
             for o, k, d in zip(layout.offsets, layout.numels, layout.decay):
-                assert (wd[o:o + k] == (0.01 if d else 0.0)).all()
+                assert (wd[o:o + k] == (1 if d else 0)).all()
     assert E.tensor_layer("model.layers.17.mlp.up_proj.weight", 32) == 17
     assert E.tensor_layer("model.norm.weight", 32) == 32 and E.tensor_layer("model.embed_tokens.weight", 32) == -1
 
