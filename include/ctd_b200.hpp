@@ -4,10 +4,13 @@
 // include/ctd/ops/*.h and include/ctd/optim.h, so code and tests written against `ctd::ops::*_impl`,
 // `ctd::optim::AdamW` and `ctd::optim::clip_grad_norm_` compile against this header unchanged.
 //
-// What it is not: there is no autograd tape here. The un-suffixed functions (ops::matmul, ops::add,
-// ...) are the forward computations only; training runs through the step engine (ctdk_engine_*),
-// which owns the fixed forward / backward schedule of the decoder. Gradients for the optimizer are
-// attached with Tensor::set_grad. Every op allocates its output with cudaMalloc, as the reference's
+// What it is not: there is no general autograd tape here. The un-suffixed functions (ops::matmul,
+// ops::add, ...) are the forward computations only; training runs through the step engine
+// (ctdk_engine_*), which owns the fixed forward / backward schedule of the decoder. The one graph
+// this layer does record is the one the reference's training loop builds
+// (tools/ctd_train/main.cpp:359-361): the loss of nn::Model::forward_train_masked (ctd_b200_nn.hpp),
+// optionally scaled by ops::mul_scalar, then backward(). Elsewhere gradients are attached with
+// Tensor::set_grad. Every op allocates its output with cudaMalloc, as the reference's
 // allocator does (src/core/allocator.cpp:14-30); this layer is the compatibility surface, not the
 // hot path. Header-only; link with -lctdk -lcudart.
 #pragma once
@@ -15,6 +18,7 @@
 #include <cmath>
 #include <cstdint>
 #include <cstring>
+#include <functional>
 #include <memory>
 #include <stdexcept>
 #include <string>
@@ -46,7 +50,18 @@ constexpr size_t dtype_size(DType dt) {
   return dt == DType::kFloat32 || dt == DType::kInt32 ? 4 : (dt == DType::kInt64 ? 8 : 2);
 }
 
+class Tensor;
+
 namespace detail {
+// The deferred model pass behind a loss tensor: backward(dy) runs forward + backward in one fused
+// pass of the step engine and leaves the loss in `value`; forward() runs the loss alone, for a
+// caller that reads the loss without ever calling backward().
+struct LossNode {
+  std::function<void(float)> backward;
+  std::function<void()> forward;
+  float value = 0.0f;
+  bool have_value = false, backward_done = false;
+};
 inline void cuda_ok(cudaError_t e, const char* what) {
   if (e != cudaSuccess) throw std::runtime_error(std::string(what) + ": " + cudaGetErrorString(e));
 }
@@ -93,7 +108,23 @@ class Tensor {
     else std::memcpy(t.data_ptr(), host, t.nbytes());
     return t;
   }
+  // A tensor over memory owned by `owner` (a slice of a larger allocation).
+  static Tensor view(std::shared_ptr<void> owner, void* ptr, std::vector<int64_t> shape, DType dtype, Device device) {
+    Tensor t;
+    t.impl_ = std::make_shared<Impl>();
+    t.impl_->storage = std::shared_ptr<void>(std::move(owner), ptr);
+    t.impl_->shape = std::move(shape);
+    t.impl_->dtype = dtype;
+    t.impl_->device = device;
+    return t;
+  }
   void copy_to_host(void* dst) const {   // blocking, like the reference's (tensor.cpp:132-142)
+    if (impl_->node) {   // a loss (times a constant) whose model pass may not have run yet
+      if (!impl_->node->have_value) impl_->node->forward();
+      const float v = impl_->node->value * impl_->node_scale;
+      std::memcpy(dst, &v, sizeof v);
+      return;
+    }
     if (device().is_cuda()) detail::cuda_ok(cudaMemcpy(dst, data_ptr(), nbytes(), cudaMemcpyDeviceToHost), "Tensor::copy_to_host");
     else std::memcpy(dst, data_ptr(), nbytes());
   }
@@ -127,6 +158,25 @@ class Tensor {
   void set_grad(const Tensor& g) { impl_->grad = std::make_shared<Tensor>(g); }
   void zero_grad_() { impl_->grad.reset(); }
 
+  // Loss tensors only (the reference's Tensor::backward walks a tape, src/core/autograd.cu:158-237;
+  // here the only recorded graph is model loss x constant). Runs the fused forward + backward pass
+  // with this tensor's scale as the upstream gradient; the parameters' grad() then point into the
+  // model's gradient arena. Like the reference's tape, a graph can be walked once.
+  void backward() {
+    detail::require(impl_ && impl_->node, "backward: this build records no graph for this tensor (only model losses)");
+    detail::require(!impl_->node->backward_done, "backward: the graph of this loss has already been consumed");
+    impl_->node->backward_done = true;
+    impl_->node->backward(impl_->node_scale);
+  }
+  bool has_loss_node() const { return impl_ && impl_->node; }
+  static Tensor loss_of(std::shared_ptr<detail::LossNode> node, float scale, Device device) {
+    Tensor t = empty({1}, DType::kFloat32, device);
+    t.impl_->node = std::move(node);
+    t.impl_->node_scale = scale;
+    return t;
+  }
+  Tensor scaled_loss(float c) const { return loss_of(impl_->node, impl_->node_scale * c, impl_->device); }
+
  private:
   struct Impl {
     std::shared_ptr<void> storage;
@@ -134,6 +184,8 @@ class Tensor {
     DType dtype = DType::kFloat32;
     Device device{};
     std::shared_ptr<Tensor> grad;
+    std::shared_ptr<detail::LossNode> node;   // set for model losses only
+    float node_scale = 1.0f;
   };
   std::shared_ptr<Impl> impl_;
 };
@@ -191,7 +243,7 @@ inline Tensor silu_backward_impl(const Tensor& x, const Tensor& g) {
 inline Tensor add(const Tensor& a, const Tensor& b) { return add_impl(a, b); }
 inline Tensor mul(const Tensor& a, const Tensor& b) { return mul_impl(a, b); }
 inline Tensor silu(const Tensor& x) { return silu_impl(x); }
-inline Tensor mul_scalar(const Tensor& x, float c) { return mul_scalar_impl(x, c); }
+inline Tensor mul_scalar(const Tensor& x, float c) { return x.has_loss_node() ? x.scaled_loss(c) : mul_scalar_impl(x, c); }
 
 // ---- matmul / bmm (include/ctd/ops/matmul.h; semantics src/ops/matmul.cpp:13-49) ----
 inline Tensor matmul_impl(const Tensor& a, const Tensor& b, bool transa, bool transb) {

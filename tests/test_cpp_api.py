@@ -1,5 +1,6 @@
-"""The C++ `ctd::` mirror (include/ctd_b200.hpp): it compiles and links against the C-ABI library
-on any host; on a B200 the case list in tests/cpp/test_ctd_api.cpp runs and must pass."""
+"""The C++ `ctd::` mirror (include/ctd_b200.hpp, ctd_b200_nn.hpp): it compiles and links against the
+C-ABI library on any host; on a B200 the case lists in tests/cpp/ (the reference's op tests, and its
+training-loop idiom against the step engine) run and must pass."""
 import os
 import subprocess
 
@@ -10,11 +11,14 @@ PKG = os.path.join(ROOT, "emberlm_b200")
 CUDA = os.environ.get("CUDA_HOME", "/usr/local/cuda")
 
 
-def _build(tmp_path):
-    exe = str(tmp_path / "test_ctd_api")
+PROGRAMS = ["test_ctd_api", "test_ctd_train_loop"]
+
+
+def _build(tmp_path, name):
+    exe = str(tmp_path / name)
     cmd = ["g++", "-std=c++17", "-O1", "-Wall", "-Wextra", "-Werror",
            "-I", os.path.join(ROOT, "include"), "-I", os.path.join(CUDA, "include"),
-           os.path.join(ROOT, "tests", "cpp", "test_ctd_api.cpp"), "-o", exe,
+           os.path.join(ROOT, "tests", "cpp", name + ".cpp"), "-o", exe,
            "-L", PKG, "-lctdk", "-L", os.path.join(CUDA, "lib64"), "-lcudart",
            "-Wl,-rpath," + PKG, "-Wl,-rpath," + os.path.join(CUDA, "lib64")]
     res = subprocess.run(cmd, capture_output=True, text=True)
@@ -22,14 +26,16 @@ def _build(tmp_path):
     return exe
 
 
-def test_header_compiles_and_links(tmp_path):
+@pytest.mark.parametrize("name", PROGRAMS)
+def test_header_compiles_and_links(tmp_path, name):
     assert os.path.exists(os.path.join(PKG, "libctdk.so")), "build the library first: python -m emberlm_b200.build"
-    _build(tmp_path)
+    _build(tmp_path, name)
 
 
 @pytest.mark.gpu
-def test_cpp_cases_pass_on_gpu(tmp_path):
-    exe = _build(tmp_path)
+@pytest.mark.parametrize("name", PROGRAMS)
+def test_cpp_cases_pass_on_gpu(tmp_path, name):
+    exe = _build(tmp_path, name)
     res = subprocess.run([exe], capture_output=True, text=True, timeout=600)
     print(res.stdout[-6000:])
     assert res.returncode == 0, res.stdout[-6000:] + res.stderr[-2000:]
