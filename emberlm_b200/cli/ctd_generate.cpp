@@ -29,9 +29,9 @@
 #include <cuda_runtime.h>
 
 #include "../../include/ctdk.h"
-#include "minijson.hpp"
+#include "../../include/ctdk_util/minijson.hpp"
 #include "model_desc.hpp"
-#include "safetensors.hpp"
+#include "../../include/ctdk_util/safetensors.hpp"
 
 namespace {
 

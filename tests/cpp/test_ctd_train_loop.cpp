@@ -15,7 +15,7 @@
 #include <string>
 #include <vector>
 
-#include "ctd_b200_nn.hpp"
+#include "ctd_b200_io.hpp"
 
 using namespace ctd;
 
@@ -245,6 +245,30 @@ void case_loop_learns_and_forward_only() {
   CHECK_THROWS(el.backward());  // ... and its backward throws, as the reference's does
 }
 
+void case_safetensors_round_trip() {
+  const nn::LlamaConfig c = tiny_config();
+  nn::Model model = nn::build_model(random_weights(c, 4), c);
+  auto named = model.collect_parameters();
+  const std::string path = "/tmp/ctd_b200_round_trip.safetensors";
+  save_safetensors(named.all, path);
+  TensorDict back = load_safetensors(path, kCUDA0);
+  CHECK(back.size() == named.all.size());
+  for (const auto& kv : named.all) {
+    auto it = back.find(kv.first);
+    CHECK(it != back.end());
+    if (it == back.end()) continue;
+    CHECK(it->second.shape() == kv.second.shape() && host(it->second) == host(kv.second));
+  }
+  nn::Model again = nn::build_model(back, c);
+  Batch b = make_batch(2, 48, c.vocab_size, 30);
+  float l0 = 0.0f, l1 = 1.0f;
+  model.forward_train_masked(b.input_ids, b.targets, b.loss_mask).copy_to_host(&l0);
+  again.forward_train_masked(b.input_ids, b.targets, b.loss_mask).copy_to_host(&l1);
+  CHECK(std::fabs(l0 - l1) <= 2e-6f * std::fabs(l0));
+  CHECK_THROWS(load_safetensors("/tmp/ctd_b200_no_such_file.safetensors", kCUDA0));
+  std::remove(path.c_str());
+}
+
 }  // namespace
 
 int main() {
@@ -253,7 +277,8 @@ int main() {
     void (*fn)();
   } cases[] = {{"Model_CollectParametersAndBuildErrors", case_parameters},
                {"TrainLoop_GradientsMatchEngine", case_gradients_match_engine},
-               {"TrainLoop_LearnsFixedBatch_ForwardOnlyLoss_EmptyMask", case_loop_learns_and_forward_only}};
+               {"TrainLoop_LearnsFixedBatch_ForwardOnlyLoss_EmptyMask", case_loop_learns_and_forward_only},
+               {"Safetensors_SaveLoadBuildRoundTrip", case_safetensors_round_trip}};
   int failed = 0;
   for (auto& c : cases) {
     const int before = g_fail;
@@ -266,6 +291,6 @@ int main() {
     std::printf("%s %s\n", g_fail == before ? "[ OK ]" : "[FAIL]", c.name);
     failed += g_fail == before ? 0 : 1;
   }
-  std::printf("%d cases, %d failed\n", 3, failed);
+  std::printf("%d cases, %d failed\n", 4, failed);
   return failed ? 1 : 0;
 }
