@@ -45,6 +45,7 @@ WORKLOADS = {
 DEFAULT_WORKLOAD = "smollm2_360m_b32x1024"
 HP = dict(lr=1e-4, beta1=0.9, beta2=0.999, eps=1e-8, weight_decay=0.01, clip=1.0)
 METRIC = "train tokens/s (fwd+bwd+AdamW)"
+NCU_GEMM_DRAM_BYTES_PER_FLOP = (74.0e6 + 115.7e6) / (2.0 * 16384 * 2560 * 960)
 
 
 def algorithmic_flops_per_step(cfg: dict, rows: int, T: int) -> float:
@@ -301,7 +302,11 @@ def run_ours(args) -> dict:
                      "peak_source": f"{peaks['source']}: bf16_tflops_sustained/2 (TF32 = half the bf16 rate)",
                      "launches": int(gemm_n), "avg_launch_ms": gemm_ms / gemm_n if gemm_n else None,
                      "share_of_step": gemm_ms / ms_prof, "profiled_ms_per_step": ms_prof / args.steps,
-                     "traffic": None},
+                     # DRAM bytes per average launch, scaled by FLOPs from the one ncu capture of this
+                     # kernel (16384 x 2560 x 960: 74.0 MB read + 115.7 MB written for 80.5 GFLOP)
+                     "traffic": (NCU_GEMM_DRAM_BYTES_PER_FLOP * gemm_flops / gemm_n) if gemm_n else None,
+                     "traffic_source": "ncu dram__bytes_read+write of gemm_tf32_2cta_kernel at 16384x2560x960, "
+                                       "scaled to the average launch by FLOPs"},
         "kernel_classes": {k: {"ms_per_step": v[0] / args.steps, "launches_per_step": v[2] / args.steps,
                                "achieved": (v[1] / (v[0] / 1e3) / (1e12 if k in ("gemm", "attn") else 1e9)) if v[0] > 0 else None,
                                "unit": "TFLOP/s" if k in ("gemm", "attn") else "GB/s"} for k, v in prof.items()},
