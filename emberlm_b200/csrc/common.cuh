@@ -31,6 +31,7 @@ int read_device_status(cudaStream_t stream);
 
 // Optional CUDA-event timing of one launch on its stream (no-ops unless ctdk_prof_enable(1)):
 // cls is a CTDK_PROF_* class, work its algorithmic FLOPs or bytes.
+bool prof_enabled();
 void* prof_begin(int cls, double work, cudaStream_t s);
 void prof_end(void* token, cudaStream_t s);
 

@@ -13,6 +13,7 @@
 //     re-run inside the backward (the reference's CheckpointNode, autograd.cu:324-363).
 // All device memory belongs to the caller; this object only holds pointers into it.
 #include <cmath>
+#include <cstdlib>
 #include <cstring>
 #include <new>
 #include <vector>
@@ -139,6 +140,24 @@ struct Engine {
   void* cb_user = nullptr;
   ctdk_layer_callback fcb = nullptr;   // before each part of the forward pass
   void* fcb_user = nullptr;
+  // Weight-gradient GEMMs on a second stream. In the backward pass dW = dY^T X of a linear layer
+  // feeds nothing before the optimizer, while dX = dY W is the next link of the dependency chain.
+  // The kernels of the chain leave SMs idle — most with few rows per GPU: a 64-tile GEMM on 74 CTA
+  // pairs, set-up and last-epilogue phases, small attention grids — and the dW GEMMs of a layer, on
+  // their own stream, fill those gaps. slot: 0 down-proj, 1 gate|up, 2 o-proj, 3 qkv; done[slot] is
+  // recorded behind the GEMM and the main stream waits for it only where a buffer the GEMM reads is
+  // about to be overwritten.
+  cudaStream_t side = nullptr;
+  cudaEvent_t side_ready = nullptr;
+  cudaEvent_t side_done[4] = {nullptr, nullptr, nullptr, nullptr};
+  bool side_pending[4] = {false, false, false, false};
+  bool side_on = false;   // decided per pass
+  ~Engine() {
+    for (cudaEvent_t ev : side_done)
+      if (ev != nullptr) cudaEventDestroy(ev);
+    if (side_ready != nullptr) cudaEventDestroy(side_ready);
+    if (side != nullptr) cudaStreamDestroy(side);
+  }
 };
 
 int64_t pick_head_rows(const ctdk_model_config& c, int64_t tok) {
@@ -254,6 +273,33 @@ int gemm(const Engine& e, const float* A, const float* B, float* C, int64_t M, i
   return ctdk_gemm(A, B, C, M, N, K, lda, ldb, N, ta, tb, e.cfg.precision, epi, aux, s);
 }
 
+// A weight-gradient GEMM: on the side stream when the pass uses it, behind everything enqueued on
+// the main stream so far.
+int dw_gemm(Engine& e, int slot, const float* A, const float* B, float* C, int64_t M, int64_t N, int64_t K, int epi,
+            void* s) {
+  if (!e.side_on) return gemm(e, A, B, C, M, N, K, 1, 0, epi, nullptr, s);
+  if (cudaEventRecord(e.side_ready, static_cast<cudaStream_t>(s)) != cudaSuccess ||
+      cudaStreamWaitEvent(e.side, e.side_ready, 0) != cudaSuccess)
+    return fail(CTDK_ELAUNCH, "engine: side-stream dependency failed: %s", cudaGetErrorString(cudaGetLastError()));
+  TRY(gemm(e, A, B, C, M, N, K, 1, 0, epi, nullptr, e.side));
+  if (cudaEventRecord(e.side_done[slot], e.side) != cudaSuccess)
+    return fail(CTDK_ELAUNCH, "engine: side-stream event failed: %s", cudaGetErrorString(cudaGetLastError()));
+  e.side_pending[slot] = true;
+  return CTDK_OK;
+}
+// The main stream goes on only after the dW GEMM of `slot` has finished (no-op when none is pending).
+int dw_wait(Engine& e, int slot, void* s) {
+  if (!e.side_pending[slot]) return CTDK_OK;
+  e.side_pending[slot] = false;
+  if (cudaStreamWaitEvent(static_cast<cudaStream_t>(s), e.side_done[slot], 0) != cudaSuccess)
+    return fail(CTDK_ELAUNCH, "engine: side-stream wait failed: %s", cudaGetErrorString(cudaGetLastError()));
+  return CTDK_OK;
+}
+int dw_wait_all(Engine& e, void* s) {
+  for (int slot = 0; slot < 4; ++slot) TRY(dw_wait(e, slot, s));
+  return CTDK_OK;
+}
+
 // Forward of layer l: reads xs[l], writes xs[l+1] and the activation set `a`.
 int layer_forward(Engine& e, int l, int64_t B, int64_t T, void* s) {
   const ctdk_model_config& c = e.cfg;
@@ -296,31 +342,61 @@ int layer_backward(Engine& e, int l, int64_t B, int64_t T, int accumulate, void*
   const int wepi = accumulate ? CTDK_EPI_ACCUMULATE : CTDK_EPI_STORE;
 
   // MLP: y = hm + act Wd^T
+  TRY(dw_wait(e, 1, s));   // the layer above's gate|up dW still reads dgu
   if (c.precision == CTDK_GEMM_TF32) {
     TRY(ctdk_gemm_swiglu_bwd(e.dh, P + w.wd, a.gu, e.dgu, e.dact, tok, I, hid, CTDK_GEMM_TF32, s));
-    TRY(gemm(e, e.dh, a.act, G + w.wd, hid, I, tok, 1, 0, wepi, nullptr, s));
+    TRY(dw_gemm(e, 0, e.dh, a.act, G + w.wd, hid, I, tok, wepi, s));
   } else {
     TRY(gemm(e, e.dh, P + w.wd, e.dact, tok, I, hid, 0, 0, CTDK_EPI_STORE, nullptr, s));
     TRY(gemm(e, e.dh, a.act, G + w.wd, hid, I, tok, 1, 0, wepi, nullptr, s));
     TRY(ctdk_swiglu_bwd(a.gu, e.dact, e.dgu, tok, static_cast<int>(I), s));
   }
   TRY(gemm(e, e.dgu, P + w.wg, e.dtmp, tok, hid, 2 * I, 0, 0, CTDK_EPI_STORE, nullptr, s));
-  TRY(gemm(e, e.dgu, a.h2, G + w.wg, 2 * I, hid, tok, 1, 0, wepi, nullptr, s));
+  TRY(dw_gemm(e, 1, e.dgu, a.h2, G + w.wg, 2 * I, hid, tok, wepi, s));
+  TRY(dw_wait(e, 0, s));   // dh is rewritten next; the down-proj dW reads it
   TRY(ctdk_rmsnorm_bwd(e.dtmp, a.hm, P + w.w_post, e.dh, G + w.w_post, e.norm_scratch, tok,
                        static_cast<int>(hid), c.rms_norm_eps, accumulate, 1, s));
   // attention: hm = x + attn Wo^T
   TRY(gemm(e, e.dh, P + w.wo, e.dattn, tok, HD, hid, 0, 0, CTDK_EPI_STORE, nullptr, s));
-  TRY(gemm(e, e.dh, a.attn, G + w.wo, hid, HD, tok, 1, 0, wepi, nullptr, s));
+  TRY(dw_gemm(e, 2, e.dh, a.attn, G + w.wo, hid, HD, tok, wepi, s));
+  TRY(dw_wait(e, 3, s));   // the layer above's qkv dW still reads dqkv
   TRY(ctdk_attn_bwd_p(a.qkv, a.attn, e.dattn, a.lse, e.delta, e.dqkv, B, T, H, Hk, D, c.precision, s));
   TRY(ctdk_qk_norm_rope_bwd(e.dqkv, a.qkv_pre, c.qk_norm ? P + w.wqn : nullptr,
                             c.qk_norm ? P + w.wkn : nullptr, a.rstd_q, a.rstd_k,
                             c.qk_norm ? G + w.wqn : nullptr, c.qk_norm ? G + w.wkn : nullptr,
                             e.qk_scratch, e.rope_table, B, T, H, Hk, D, accumulate, s));
   TRY(gemm(e, e.dqkv, P + w.wq, e.dtmp, tok, hid, e.QKVN, 0, 0, CTDK_EPI_STORE, nullptr, s));
-  TRY(gemm(e, e.dqkv, a.h1, G + w.wq, e.QKVN, hid, tok, 1, 0, wepi, nullptr, s));
+  TRY(dw_gemm(e, 3, e.dqkv, a.h1, G + w.wq, e.QKVN, hid, tok, wepi, s));
+  TRY(dw_wait(e, 2, s));   // dh is rewritten next; the o-proj dW reads it
   TRY(ctdk_rmsnorm_bwd(e.dtmp, e.xs[l], P + w.w_in, e.dh, G + w.w_in, e.norm_scratch, tok,
                        static_cast<int>(hid), c.rms_norm_eps, accumulate, 1, s));
   return CTDK_OK;
+}
+
+// Measured on SmolLM2-360M: 4 x 1023 rows per GPU 26.6 -> 25.7 ms per pass + update, 32 x 1023 rows
+// 168.2 -> 166.3 ms. Off while launches are being timed one by one (ctdk_prof_enable): kernels that
+// share the GPU would each be charged the other's time. CTDK_ENGINE_SIDE_STREAM=0 turns it off.
+bool use_side_stream(Engine& e) {
+  static const bool off = [] {
+    const char* v = std::getenv("CTDK_ENGINE_SIDE_STREAM");
+    return v != nullptr && v[0] == '0';
+  }();
+  if (e.cfg.precision != CTDK_GEMM_TF32) return false;   // the operand-split workspace of 3xTF32 is one per engine
+  if (off || prof_enabled()) return false;
+  if (e.side == nullptr) {
+    if (cudaStreamCreateWithFlags(&e.side, cudaStreamNonBlocking) != cudaSuccess) {
+      e.side = nullptr;
+      cudaGetLastError();
+      return false;
+    }
+    bool ok = cudaEventCreateWithFlags(&e.side_ready, cudaEventDisableTiming) == cudaSuccess;
+    for (int i = 0; i < 4 && ok; ++i) ok = cudaEventCreateWithFlags(&e.side_done[i], cudaEventDisableTiming) == cudaSuccess;
+    if (!ok) {
+      cudaGetLastError();
+      return false;
+    }
+  }
+  return e.side_ready != nullptr && e.side_done[3] != nullptr;
 }
 
 int prepare(Engine& e, int64_t B, int64_t T, void* s) {
@@ -408,11 +484,24 @@ int run(Engine& e, const int64_t* ids, const int64_t* targets, const float* loss
                        e.norm_scratch, tok, static_cast<int>(hid), c.rms_norm_eps, accumulate, 0,
                        s));
   if (e.cb) e.cb(L, e.cb_user);
+  e.side_on = use_side_stream(e);
   for (int l = L - 1; l >= 0; --l) {
-    if (c.gradient_checkpointing) TRY(layer_forward(e, l, B, T, s));
+    if (c.gradient_checkpointing) {
+      TRY(dw_wait_all(e, s));   // the recomputation overwrites the one activation set the dW GEMMs read
+      TRY(layer_forward(e, l, B, T, s));
+    }
     TRY(layer_backward(e, l, B, T, accumulate, s));
-    if (e.cb) e.cb(l, e.cb_user);
+    // With the side stream, layer l's weight gradients are ordered before the main stream only one
+    // layer later (layer l-1 waits for each of them before it reuses a buffer), so the callback of a
+    // layer is made then.
+    if (e.cb) {
+      if (!e.side_on) e.cb(l, e.cb_user);
+      else if (l + 1 < L) e.cb(l + 1, e.cb_user);
+    }
   }
+  TRY(dw_wait_all(e, s));
+  if (e.cb && e.side_on) e.cb(0, e.cb_user);
+  e.side_on = false;
   TRY(ctdk_embedding_bwd(ids, e.dh, dE, tok, static_cast<int>(hid), V, s));
   if (e.cb) e.cb(-1, e.cb_user);
   return CTDK_OK;

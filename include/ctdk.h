@@ -329,9 +329,15 @@ int ctdk_engine_set_active_rows(void* engine, const int32_t* rows, int64_t n);
 int ctdk_engine_forward_loss(void* engine, const int64_t* ids, const int64_t* targets,
                              const float* loss_mask, int64_t B, int64_t T, float* loss_sums,
                              void* stream);
-/* Optional host callback invoked right after the backward kernels of layer `layer` have been
- * enqueued (layer == num_hidden_layers: final norm + LM head; -1: embedding, i.e. all done),
- * so the caller can start reducing that layer's gradients while earlier layers still run. */
+/* Optional host callback invoked once everything that writes the gradients of layer `layer` is
+ * ordered before the caller's stream at this point of the enqueue (layer == num_hidden_layers:
+ * final norm + LM head; -1: embedding, i.e. all done), so the caller can start reducing that
+ * layer's gradients while earlier layers still run. Layers come in descending order. The engine
+ * runs the weight-gradient GEMMs of the TF32 path on a stream of its own (they feed nothing before
+ * the optimizer and fill SMs the dependency chain leaves idle) and joins them one layer later, so
+ * the callback of layer l is made after layer l-1 has been enqueued; when the pass returns, all
+ * of its work is ordered before the caller's stream again. CTDK_ENGINE_SIDE_STREAM=0 in the
+ * environment keeps everything on the caller's stream. */
 typedef void (*ctdk_layer_callback)(int layer, void* user);
 int ctdk_engine_set_layer_callback(void* engine, ctdk_layer_callback cb, void* user);
 /* Optional host callback invoked right BEFORE the forward kernels that first read a part of the
