@@ -293,6 +293,7 @@ def run_ours(args) -> dict:
         "step_tflops_per_gpu": flops_step / (ms_total / args.steps / 1e3) / 1e12 / world,
         "step_frac_of_tf32_peak": flops_step / (ms_total / args.steps / 1e3) / 1e12 / world / tf32_peak,
         "loss": metrics["loss"], "grad_norm": metrics["grad_norm"],
+        "device_status": eng.device_status,     # 0: no bounded device-side wait gave up (checked every read_metrics)
         "e2e": {"value": e2e_value, "unit": "tokens/s", "ms_per_step": ms_e2e / args.steps,
                 "h2d_bytes_per_step": my_rows * S * 5 + 4 * act_mean, "d2h_bytes_per_step": 24},
         "gpu_launches": int(launches),

@@ -138,7 +138,7 @@ int main(int argc, char** argv) try {
   sampler.temperature = static_cast<float>(req.value("temperature", 1.0));
   sampler.top_k = static_cast<int>(req.value("top_k", 0.0));
   sampler.top_p = static_cast<float>(req.value("top_p", 0.0));
-  const uint64_t seed = static_cast<uint64_t>(req.value("seed", 0.0));
+  const uint64_t seed = req.contains("seed") ? req.at("seed").as_uint64() : 0;
   const std::vector<int64_t> eos_list = id_list(req, "eos_ids");
   const std::set<int64_t> eos(eos_list.begin(), eos_list.end());
   const int budget = static_cast<int>(req.value("thinking_token_budget", 0.0));

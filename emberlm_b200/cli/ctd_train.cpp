@@ -10,29 +10,47 @@
 // state in a sibling .opt.safetensors (main.cpp:211-235, 409-420) and resume (main.cpp:300-315).
 // Messages go to stderr with the "[ctd_train]" prefix; errors exit 1, usage errors exit 2.
 //
-// What differs: the grad_accum_steps micro-batches of a step run as ONE fused pass through
-// ctdk_engine_forward_backward (per-row weights mask / (A * sum(mask of the row's micro-batch))
-// reproduce mul_scalar(loss, 1/A) + backward per micro-batch); clip and AdamW are the fused
-// kernels behind ctdk_sumsq / ctdk_clip_scale / ctdk_adamw; there is one host sync per step (to log).
-// "offload_optimizer" is accepted and ignored (m / v stay in HBM).
+// What differs: the grad_accum_steps micro-batches of a step run as fused passes through the
+// library's trainer (ctdk_trainer_*; per-row weights mask / (A * sum(mask of the row's micro-batch))
+// reproduce mul_scalar(loss, 1/A) + backward per micro-batch); clip and AdamW are fused kernels;
+// there is one host sync per step (to log). "offload_optimizer" is accepted and ignored (m / v stay
+// in HBM, sharded over the ranks).
+//
+// Several GPUs: start one process per GPU with RANK, WORLD_SIZE and LOCAL_RANK in the environment
+// (what torchrun / torch.distributed.run set). Every rank draws the same document sequence and keeps
+// micro-batches rank, rank + WORLD_SIZE, ... (grad_accum_steps must divide by WORLD_SIZE); gradients
+// are reduce-scattered, AdamW's m / v are sharded ZeRO-1 style, parameters all-gathered (NCCL). Rank 0
+// makes the NCCL unique id and leaves it in a file the others wait for (CTDK_NCCL_ID_FILE, default
+// <run dir>/.nccl_id.<parent pid>); rank 0 alone writes loss.jsonl and the checkpoints, with the
+// m / v slices gathered for it.
+//
+// Data feed: the step's rows go to pinned memory as they are in the bins (int32 tokens, int8 masks:
+// 5 bytes per token instead of the 24 of int64 ids / targets and fp32 masks), are copied on a copy
+// stream and widened on the device (ctdk_batch_widen); the next step's rows are staged and copied
+// while the current step runs. Checkpoints move through two pinned buffers so that the file and
+// the PCIe link work at the same time (include/ctdk_util/device_io.hpp).
 #include <algorithm>
 #include <chrono>
 #include <cmath>
 #include <cstdint>
 #include <cstring>
 #include <filesystem>
+#include <memory>
 #include <fstream>
 #include <iostream>
 #include <random>
 #include <sstream>
+#include <thread>
 #include <string>
 #include <vector>
 
 #include <cuda_runtime.h>
+#include <unistd.h>
 
 #include "../../include/ctdk.h"
 #include "../../include/ctdk_util/minijson.hpp"
 #include "model_desc.hpp"
+#include "../../include/ctdk_util/device_io.hpp"
 #include "../../include/ctdk_util/safetensors.hpp"
 
 namespace fs = std::filesystem;
@@ -94,7 +112,7 @@ Config load_config(const fs::path& path) {
   c.val_every = geti("val_every", c.val_every);
   c.save_every = geti("save_every", c.save_every);
   c.log_every = geti("log_every", c.log_every);
-  c.seed = static_cast<uint64_t>(j.value("seed", static_cast<double>(c.seed)));
+  if (j.contains("seed")) c.seed = j.at("seed").as_uint64();
   c.offload_optimizer = j.value("offload_optimizer", c.offload_optimizer);
   c.gradient_checkpointing = j.value("gradient_checkpointing", c.gradient_checkpointing);
   const std::string prec = j.value("precision", std::string("tf32"));
@@ -154,63 +172,91 @@ struct DeviceBuf {
   explicit DeviceBuf(size_t count) { alloc(count); }
   DeviceBuf(const DeviceBuf&) = delete;
   DeviceBuf& operator=(const DeviceBuf&) = delete;
-  void alloc(size_t count) {
+  void alloc(size_t count) {   // zero-filled
     n = count;
     CUDA_OK(cudaMalloc(reinterpret_cast<void**>(&p), std::max<size_t>(count, 1) * sizeof(T)));
+    CUDA_OK(cudaMemset(p, 0, std::max<size_t>(count, 1) * sizeof(T)));
   }
   ~DeviceBuf() {
     if (p) cudaFree(p);
   }
 };
 
-// Host-built device inputs of one fused pass over `rows` documents.
-struct HostBatch {
-  std::vector<int64_t> ids, targets;
-  std::vector<float> mask, weight;
-  std::vector<int32_t> active;   // flattened positions whose mask is 1
-  double sum_mask = 0.0;
+template <typename T>
+struct PinnedBuf {
+  T* p = nullptr;
+  explicit PinnedBuf(size_t count) {
+    CUDA_OK(cudaMallocHost(reinterpret_cast<void**>(&p), std::max<size_t>(count, 1) * sizeof(T)));
+  }
+  PinnedBuf(const PinnedBuf&) = delete;
+  PinnedBuf& operator=(const PinnedBuf&) = delete;
+  ~PinnedBuf() {
+    if (p) cudaFreeHost(p);
+  }
 };
 
-// rows_docs: the documents of consecutive micro-batches of `micro` rows each; a micro-batch whose
-// mask is empty contributes nothing (main.cpp:350). accum = micro-batches in the whole step.
-void build_batch(const Split& split, const std::vector<int64_t>& rows_docs, int micro, int accum, int seq_len,
-                 HostBatch* out) {
-  const int T = seq_len - 1;
-  const size_t rows = rows_docs.size(), n = rows * static_cast<size_t>(T);
-  out->ids.resize(n);
-  out->targets.resize(n);
-  out->mask.resize(n);
-  out->weight.assign(n, 0.0f);
-  out->active.clear();
-  out->sum_mask = 0.0;
-  for (size_t r0 = 0; r0 < rows; r0 += static_cast<size_t>(micro)) {
-    double sm = 0.0;
-    const size_t r1 = std::min(rows, r0 + static_cast<size_t>(micro));
-    for (size_t r = r0; r < r1; ++r) {
-      const int32_t* tok = split.tokens.data() + rows_docs[r] * seq_len;
-      const int8_t* msk = split.masks.data() + rows_docs[r] * seq_len;
-      for (int t = 0; t < T; ++t) {
-        const size_t i = r * static_cast<size_t>(T) + static_cast<size_t>(t);
-        out->ids[i] = tok[t];
-        out->targets[i] = tok[t + 1];
-        out->mask[i] = static_cast<float>(msk[t + 1]);
-        sm += out->mask[i];
-      }
-    }
-    if (sm <= 0.0) {   // skipped micro-batch: no loss, no gradient, not counted in the logged mean
-      for (size_t i = r0 * static_cast<size_t>(T); i < r1 * static_cast<size_t>(T); ++i) out->mask[i] = 0.0f;
-      continue;
-    }
-    const float w = static_cast<float>(1.0 / (static_cast<double>(accum) * sm));
-    for (size_t i = r0 * static_cast<size_t>(T); i < r1 * static_cast<size_t>(T); ++i) {
-      if (out->mask[i] != 0.0f) {
-        out->weight[i] = out->mask[i] * w;
-        out->active.push_back(static_cast<int32_t>(i));
-      }
-    }
-    out->sum_mask += sm;
+// One fused pass inside a staged set of rows.
+struct Pass {
+  int64_t row0 = 0, rows = 0;       // rows of the staging buffers
+  int64_t act0 = 0, n_active = 0;   // its supervised positions (relative to the pass) in the active list
+};
+
+// The rows of one step (or one block of validation rows) of this rank as they lie in the bins, in
+// pinned memory and, after copy(), on the device.
+struct Staging {
+  PinnedBuf<int32_t> h_tok;
+  PinnedBuf<int8_t> h_msk;
+  PinnedBuf<int32_t> h_act;
+  DeviceBuf<int32_t> d_tok, d_act;
+  DeviceBuf<int8_t> d_msk;
+  std::vector<Pass> passes;
+  cudaEvent_t ready = nullptr;
+  int64_t rows = 0, n_act = 0;
+  Staging(int64_t max_rows, int S)
+      : h_tok(max_rows * S), h_msk(max_rows * S), h_act(max_rows * S), d_tok(max_rows * S), d_act(max_rows * S),
+        d_msk(max_rows * S) {
+    CUDA_OK(cudaEventCreateWithFlags(&ready, cudaEventDisableTiming));
   }
-}
+  Staging(const Staging&) = delete;
+  Staging& operator=(const Staging&) = delete;
+  ~Staging() {
+    if (ready) cudaEventDestroy(ready);
+  }
+  // docs: the documents of consecutive passes of at most pass_rows rows each. A pass whose mask is
+  // empty is dropped (main.cpp:350: such a micro-batch contributes nothing).
+  void fill(const Split& split, const std::vector<int64_t>& docs, int64_t pass_rows, int S) {
+    const int T = S - 1;
+    passes.clear();
+    rows = static_cast<int64_t>(docs.size());
+    n_act = 0;
+    for (int64_t r = 0; r < rows; ++r) {
+      std::memcpy(h_tok.p + r * S, split.tokens.data() + docs[r] * S, static_cast<size_t>(S) * 4);
+      std::memcpy(h_msk.p + r * S, split.masks.data() + docs[r] * S, static_cast<size_t>(S));
+    }
+    for (int64_t r0 = 0; r0 < rows; r0 += pass_rows) {
+      Pass ps;
+      ps.row0 = r0;
+      ps.rows = std::min(pass_rows, rows - r0);
+      ps.act0 = n_act;
+      for (int64_t r = 0; r < ps.rows; ++r) {
+        const int8_t* m = h_msk.p + (r0 + r) * S;
+        for (int t = 0; t < T; ++t)
+          if (m[t + 1] != 0) h_act.p[n_act++] = static_cast<int32_t>(r * T + t);
+      }
+      ps.n_active = n_act - ps.act0;
+      if (ps.n_active > 0) passes.push_back(ps);
+    }
+  }
+  void copy(int S, cudaStream_t copy_stream) {
+    if (rows > 0) {
+      CUDA_OK(cudaMemcpyAsync(d_tok.p, h_tok.p, static_cast<size_t>(rows) * S * 4, cudaMemcpyHostToDevice, copy_stream));
+      CUDA_OK(cudaMemcpyAsync(d_msk.p, h_msk.p, static_cast<size_t>(rows) * S, cudaMemcpyHostToDevice, copy_stream));
+    }
+    if (n_act > 0)
+      CUDA_OK(cudaMemcpyAsync(d_act.p, h_act.p, static_cast<size_t>(n_act) * 4, cudaMemcpyHostToDevice, copy_stream));
+    CUDA_OK(cudaEventRecord(ready, copy_stream));
+  }
+};
 
 fs::path opt_path_for(const fs::path& weights) { return weights.string() + ".opt.safetensors"; }
 
@@ -226,16 +272,55 @@ std::string parse_config_path(int argc, char** argv) {
   return cfg;
 }
 
+int env_int(const char* name, int fallback) {
+  const char* v = std::getenv(name);
+  return (v != nullptr && *v != '\0') ? std::atoi(v) : fallback;
+}
+
+// Rank 0 writes the 128-byte NCCL unique id to `path` (through a temporary name, so a reader never
+// sees half of it); the other ranks wait for the file.
+void exchange_nccl_id(const fs::path& path, int rank, unsigned char id[128]) {
+  if (rank == 0) {
+    CTDK_OK_OR_THROW(ctdk_trainer_unique_id(id));
+    const fs::path tmp = path.string() + ".tmp";
+    {
+      std::ofstream f(tmp, std::ios::binary | std::ios::trunc);
+      f.write(reinterpret_cast<const char*>(id), 128);
+      if (!f) throw std::runtime_error("cannot write " + tmp.string());
+    }
+    fs::rename(tmp, path);
+    return;
+  }
+  for (int tries = 0; tries < 1200; ++tries) {   // up to two minutes
+    std::error_code ec;
+    if (fs::exists(path, ec) && fs::file_size(path, ec) == 128) {
+      std::ifstream f(path, std::ios::binary);
+      if (f.read(reinterpret_cast<char*>(id), 128)) return;
+    }
+    std::this_thread::sleep_for(std::chrono::milliseconds(100));
+  }
+  throw std::runtime_error("rank 0's NCCL id never appeared at " + path.string());
+}
+
 }  // namespace
 
 int main(int argc, char** argv) try {
   const std::string cfg_path = parse_config_path(argc, argv);
   const Config cfg = load_config(cfg_path);
-  fs::create_directories(cfg.run_dir);
-  std::cerr << "[ctd_train] run=" << cfg.run_name << " dir=" << cfg.run_dir << "\n";
+  const int rank = env_int("RANK", 0), world = std::max(1, env_int("WORLD_SIZE", 1)), local = env_int("LOCAL_RANK", rank);
+  if (rank < 0 || rank >= world) throw std::runtime_error("RANK must be in [0, WORLD_SIZE)");
+  if (cfg.grad_accum_steps % world != 0)
+    throw std::runtime_error("grad_accum_steps (" + std::to_string(cfg.grad_accum_steps) + ") must divide by WORLD_SIZE (" +
+                             std::to_string(world) + "): whole micro-batches are dealt to the ranks");
+  const bool chief = rank == 0;
+  auto say = [&](const std::string& msg) {
+    if (chief) std::cerr << "[ctd_train] " << msg << "\n";
+  };
+  if (chief) fs::create_directories(cfg.run_dir);
+  say("run=" + cfg.run_name + " dir=\"" + cfg.run_dir.string() + "\"" + (world > 1 ? " ranks=" + std::to_string(world) : ""));
   const bool resuming = !cfg.resume_from.empty();
   const fs::path weights_path = resuming ? cfg.resume_from : cfg.init_weights;
-  std::cerr << "[ctd_train] " << (resuming ? "resuming from " : "loading init weights ") << weights_path << "\n";
+  say(std::string(resuming ? "resuming from " : "loading init weights ") + "\"" + weights_path.string() + "\"");
 
   st::File wfile(weights_path.string());
   const st::Entry& emb = wfile.entry("model.embed_tokens.weight");
@@ -243,64 +328,46 @@ int main(int argc, char** argv) try {
   ctdk_model_config mc = cli::autodetect_config(emb.shape[0], emb.shape[1]);
   mc.gradient_checkpointing = cfg.gradient_checkpointing ? 1 : 0;
   mc.precision = cfg.precision;
-  std::cerr << "[ctd_train] arch: hidden=" << mc.hidden_size << " layers=" << mc.num_hidden_layers
-            << " heads=" << mc.num_attention_heads << "\n";
-  if (cfg.gradient_checkpointing) std::cerr << "[ctd_train] gradient checkpointing enabled\n";
-  if (cfg.offload_optimizer) std::cerr << "[ctd_train] offload_optimizer ignored: optimizer state stays in HBM\n";
+  say("arch: hidden=" + std::to_string(mc.hidden_size) + " layers=" + std::to_string(mc.num_hidden_layers) +
+      " heads=" + std::to_string(mc.num_attention_heads));
+  if (cfg.gradient_checkpointing) say("gradient checkpointing enabled");
+  if (cfg.offload_optimizer) say("offload_optimizer ignored: optimizer state stays in HBM");
 
-  int64_t arena = 0;
-  const std::vector<cli::ParamDesc> params = cli::describe_parameters(mc, &arena);
+  int64_t layout_floats = 0;
+  const std::vector<cli::ParamDesc> params = cli::describe_parameters(mc, &layout_floats);
   size_t n_decay = 0;
   for (const auto& p : params) n_decay += p.decay ? 1 : 0;
-  std::cerr << "[ctd_train] parameters: " << n_decay << " decay + " << (params.size() - n_decay) << " no_decay\n";
+  say("parameters: " + std::to_string(n_decay) + " decay + " + std::to_string(params.size() - n_decay) + " no_decay");
 
-  // ---- device state: parameter / gradient arenas, AdamW moments, workspace ----
-  CUDA_OK(cudaSetDevice(0));
-  cudaStream_t stream;
-  CUDA_OK(cudaStreamCreate(&stream));
-  DeviceBuf<float> d_params(arena), d_grads(arena), d_m(arena), d_v(arena);
-  CUDA_OK(cudaMemset(d_params.p, 0, arena * sizeof(float)));
-  CUDA_OK(cudaMemset(d_m.p, 0, arena * sizeof(float)));
-  CUDA_OK(cudaMemset(d_v.p, 0, arena * sizeof(float)));
-  std::vector<float> h_arena(static_cast<size_t>(arena), 0.0f);
-  for (const auto& p : params) wfile.read_f32(p.name, h_arena.data() + p.offset, p.numel);
-  CUDA_OK(cudaMemcpy(d_params.p, h_arena.data(), arena * sizeof(float), cudaMemcpyHostToDevice));
-
-  int64_t step_count = 0;
-  if (resuming) {
-    const fs::path op = opt_path_for(cfg.resume_from);
-    if (fs::exists(op)) {
-      std::cerr << "[ctd_train] loading optimizer state " << op << "\n";
-      st::File ofile(op.string());
-      std::vector<float> hm(static_cast<size_t>(arena), 0.0f), hv(static_cast<size_t>(arena), 0.0f);
-      for (const auto& p : params) {
-        if (!ofile.has("optimizer.m." + p.name) || !ofile.has("optimizer.v." + p.name))
-          throw std::runtime_error("resume: missing optimizer.m." + p.name + " or optimizer.v." + p.name);
-        ofile.read_f32("optimizer.m." + p.name, hm.data() + p.offset, p.numel);
-        ofile.read_f32("optimizer.v." + p.name, hv.data() + p.offset, p.numel);
-      }
-      if (!ofile.has("optimizer.step")) throw std::runtime_error("resume: missing optimizer.step");
-      float sf = 0.0f;
-      ofile.read_f32("optimizer.step", &sf, 1);
-      step_count = static_cast<int64_t>(sf);
-      CUDA_OK(cudaMemcpy(d_m.p, hm.data(), arena * sizeof(float), cudaMemcpyHostToDevice));
-      CUDA_OK(cudaMemcpy(d_v.p, hv.data(), arena * sizeof(float), cudaMemcpyHostToDevice));
-      std::cerr << "[ctd_train] resumed at step " << step_count << "\n";
-    } else {
-      std::cerr << "[ctd_train] no optimizer state at " << op << " — continuing with fresh m/v (warmup will restart)\n";
-    }
+  // ---- device state: parameter / gradient arenas, this rank's slices of AdamW's moments ----
+  CUDA_OK(cudaSetDevice(local));
+  cudaStream_t stream, copy_stream;
+  CUDA_OK(cudaStreamCreateWithFlags(&stream, cudaStreamNonBlocking));
+  CUDA_OK(cudaStreamCreateWithFlags(&copy_stream, cudaStreamNonBlocking));
+  const int64_t arena = ctdk_dp_arena_floats(&mc, world);
+  if (arena < layout_floats) throw std::runtime_error(ctdk_last_error());
+  const int64_t shard = arena / world;
+  DeviceBuf<float> d_params(arena), d_grads(arena), d_m(shard), d_v(shard);   // all zero-filled
+  st::PinnedPipe pipe;
+  {
+    std::FILE* f = std::fopen(weights_path.c_str(), "rb");
+    if (!f) throw std::runtime_error("cannot open " + weights_path.string());
+    for (const auto& p : params)
+      st::read_f32_to_device(wfile, weights_path.string(), f, p.name, d_params.p + p.offset, p.numel, pipe);
+    pipe.synchronize();
+    std::fclose(f);
   }
-  const int64_t start_step = step_count;
 
-  std::cerr << "[ctd_train] loading data from " << cfg.data_dir << "\n";
+  say("loading data from \"" + cfg.data_dir.string() + "\"");
   const Split train = load_split(cfg.data_dir / "train.bin", cfg.data_dir / "train_mask.bin", cfg.seq_len);
   const Split val = load_split(cfg.data_dir / "val.bin", cfg.data_dir / "val_mask.bin", cfg.seq_len);
-  std::cerr << "[ctd_train] train=" << train.docs << " val=" << val.docs << "\n";
+  say("train=" + std::to_string(train.docs) + " val=" + std::to_string(val.docs));
   if (train.docs < 1) throw std::runtime_error("train split is empty");
 
-  // Micro-batches fused per pass: all of the step's if the workspace fits in free memory, else halved.
-  const int T = cfg.seq_len - 1;
-  int fused = cfg.grad_accum_steps;
+  // Micro-batches of this rank fused per pass: all of them if the workspace fits in free memory, else halved.
+  const int T = cfg.seq_len - 1, S = cfg.seq_len;
+  const int my_accum = cfg.grad_accum_steps / world;
+  int fused = my_accum;
   int64_t ws_bytes = 0;
   for (;; fused = (fused + 1) / 2) {
     ws_bytes = ctdk_engine_workspace_bytes(&mc, static_cast<int64_t>(fused) * cfg.batch_size, T);
@@ -310,168 +377,229 @@ int main(int argc, char** argv) try {
     if (static_cast<double>(ws_bytes) < 0.9 * static_cast<double>(free_b) || fused == 1) break;
   }
   const int64_t pass_rows = static_cast<int64_t>(fused) * cfg.batch_size;
-  std::cerr << "[ctd_train] " << fused << " of " << cfg.grad_accum_steps << " micro-batches per pass, workspace "
-            << (ws_bytes >> 20) << " MiB\n";
-  DeviceBuf<unsigned char> d_ws(static_cast<size_t>(ws_bytes));
-  void* engine = nullptr;
-  CTDK_OK_OR_THROW(ctdk_engine_create(&mc, d_params.p, d_grads.p, d_ws.p, ws_bytes, pass_rows, T, &engine));
+  const int64_t step_rows = static_cast<int64_t>(my_accum) * cfg.batch_size;
+  say(std::to_string(fused) + " of " + std::to_string(my_accum) + " micro-batches per pass, workspace " +
+      std::to_string(ws_bytes >> 20) + " MiB");
+  unsigned char* d_ws = nullptr;   // scratch: not zero-filled
+  CUDA_OK(cudaMalloc(reinterpret_cast<void**>(&d_ws), static_cast<size_t>(ws_bytes)));
+
+  unsigned char nccl_id[128] = {0};
+  fs::path id_file;
+  if (world > 1) {
+    const char* named = std::getenv("CTDK_NCCL_ID_FILE");
+    id_file = named != nullptr ? fs::path(named)
+                               : cfg.run_dir / (".nccl_id." + std::to_string(static_cast<long>(getppid())));
+    exchange_nccl_id(id_file, rank, nccl_id);
+  }
+  ctdk_trainer_hparams hp{};
+  hp.lr = cfg.lr;
+  hp.beta1 = cfg.beta1;
+  hp.beta2 = cfg.beta2;
+  hp.eps = cfg.eps;
+  hp.weight_decay = cfg.weight_decay;
+  hp.clip = cfg.clip_grad_norm;
+  hp.layers_per_bucket = -1;
+  void* trainer = nullptr;
+  CTDK_OK_OR_THROW(ctdk_trainer_create(&mc, d_params.p, d_grads.p, d_m.p, d_v.p, d_ws, ws_bytes, pass_rows, T, rank, world,
+                                       world > 1 ? nccl_id : nullptr, &hp, &trainer));
+  void* engine = ctdk_trainer_engine(trainer);
+
+  int64_t step_count = 0;
+  if (resuming) {
+    const fs::path op = opt_path_for(cfg.resume_from);
+    if (fs::exists(op)) {
+      say("loading optimizer state \"" + op.string() + "\"");
+      st::File ofile(op.string());
+      std::FILE* f = std::fopen(op.c_str(), "rb");
+      if (!f) throw std::runtime_error("cannot open " + op.string());
+      // each of m, v: the whole arena-order array into the gradient arena, then this rank's slices out of it
+      for (int which = 0; which < 2; ++which) {
+        const std::string prefix = which == 0 ? "optimizer.m." : "optimizer.v.";
+        CUDA_OK(cudaMemsetAsync(d_grads.p, 0, static_cast<size_t>(arena) * sizeof(float), pipe.stream()));
+        for (const auto& p : params) {
+          if (!ofile.has(prefix + p.name)) throw std::runtime_error("resume: missing " + prefix + p.name);
+          st::read_f32_to_device(ofile, op.string(), f, prefix + p.name, d_grads.p + p.offset, p.numel, pipe);
+        }
+        pipe.synchronize();
+        CTDK_OK_OR_THROW(ctdk_trainer_scatter_state(trainer, d_grads.p, which == 0 ? d_m.p : d_v.p, stream));
+        CUDA_OK(cudaStreamSynchronize(stream));
+      }
+      std::fclose(f);
+      if (!ofile.has("optimizer.step")) throw std::runtime_error("resume: missing optimizer.step");
+      float sf = 0.0f;
+      ofile.read_f32("optimizer.step", &sf, 1);
+      step_count = static_cast<int64_t>(sf);
+      CTDK_OK_OR_THROW(ctdk_trainer_set_step_count(trainer, step_count));
+      say("resumed at step " + std::to_string(step_count));
+    } else {
+      say("no optimizer state at \"" + op.string() + "\" — continuing with fresh m/v (warmup will restart)");
+    }
+  }
+  const int64_t start_step = step_count;
 
   const size_t pass_n = static_cast<size_t>(pass_rows) * static_cast<size_t>(T);
   DeviceBuf<int64_t> d_ids(pass_n), d_tgt(pass_n);
-  DeviceBuf<float> d_mask(pass_n), d_w(pass_n), d_scal(8);   // scal: [0..1] loss sums, [2] sumsq, [3] scale, [4] norm
-  DeviceBuf<int32_t> d_active(pass_n);
+  DeviceBuf<float> d_mask(pass_n), d_w(pass_n), d_sums(static_cast<size_t>(pass_rows) + 1);
+  const int64_t stage_rows = std::max<int64_t>(step_rows, pass_rows);
+  Staging slot_a(stage_rows, S), slot_b(stage_rows, S);
+  Staging* slots[2] = {&slot_a, &slot_b};
 
-  // weight-decay segments of the arena: runs of equal decay in parameter order, padding with its tensor
-  std::vector<int64_t> seg_end;
-  std::vector<float> seg_wd;
-  for (size_t i = 0; i < params.size(); ++i) {
-    const float wd = params[i].decay ? cfg.weight_decay : 0.0f;
-    const int64_t end = i + 1 < params.size() ? params[i + 1].offset : arena;
-    if (!seg_wd.empty() && seg_wd.back() == wd) seg_end.back() = end;
-    else {
-      seg_end.push_back(end);
-      seg_wd.push_back(wd);
-    }
-  }
-  DeviceBuf<int64_t> d_seg_end(seg_end.size());
-  DeviceBuf<float> d_seg_wd(seg_wd.size());
-  CUDA_OK(cudaMemcpy(d_seg_end.p, seg_end.data(), seg_end.size() * sizeof(int64_t), cudaMemcpyHostToDevice));
-  CUDA_OK(cudaMemcpy(d_seg_wd.p, seg_wd.data(), seg_wd.size() * sizeof(float), cudaMemcpyHostToDevice));
-
-  HostBatch hb;
-  auto upload = [&](const HostBatch& b) {
-    const size_t n = b.ids.size();
-    CUDA_OK(cudaMemcpyAsync(d_ids.p, b.ids.data(), n * sizeof(int64_t), cudaMemcpyHostToDevice, stream));
-    CUDA_OK(cudaMemcpyAsync(d_tgt.p, b.targets.data(), n * sizeof(int64_t), cudaMemcpyHostToDevice, stream));
-    CUDA_OK(cudaMemcpyAsync(d_mask.p, b.mask.data(), n * sizeof(float), cudaMemcpyHostToDevice, stream));
-    CUDA_OK(cudaMemcpyAsync(d_w.p, b.weight.data(), n * sizeof(float), cudaMemcpyHostToDevice, stream));
-    if (!b.active.empty())
-      CUDA_OK(cudaMemcpyAsync(d_active.p, b.active.data(), b.active.size() * sizeof(int32_t), cudaMemcpyHostToDevice, stream));
-    CUDA_OK(cudaStreamSynchronize(stream));   // the host vectors are reused by the next pass
+  // Widens one staged pass on the device and names its supervised rows to the engine.
+  auto widen_pass = [&](const Staging& st, const Pass& ps, int micro_rows, int accum_total) {
+    CTDK_OK_OR_THROW(ctdk_batch_widen(st.d_tok.p + ps.row0 * S, st.d_msk.p + ps.row0 * S, ps.rows, S, micro_rows,
+                                      accum_total, d_ids.p, d_tgt.p, d_mask.p, d_w.p, d_sums.p, stream));
+    CTDK_OK_OR_THROW(ctdk_engine_set_active_rows(engine, st.d_act.p + ps.act0, ps.n_active));
   };
 
   auto save_checkpoint = [&](const fs::path& ckpt) {
-    CUDA_OK(cudaMemcpy(h_arena.data(), d_params.p, arena * sizeof(float), cudaMemcpyDeviceToHost));
-    std::vector<st::Item> items;
-    for (const auto& p : params) items.push_back({p.name, p.shape, h_arena.data() + p.offset});
-    st::save(items, ckpt.string());
-    std::vector<float> hm(static_cast<size_t>(arena)), hv(static_cast<size_t>(arena));
-    CUDA_OK(cudaMemcpy(hm.data(), d_m.p, arena * sizeof(float), cudaMemcpyDeviceToHost));
-    CUDA_OK(cudaMemcpy(hv.data(), d_v.p, arena * sizeof(float), cudaMemcpyDeviceToHost));
-    std::vector<st::Item> opt;
-    for (int pass = 0; pass < 2; ++pass)   // decay group first, then no-decay (main.cpp:218-226)
-      for (const auto& p : params) {
-        if (p.decay != (pass == 0)) continue;
-        opt.push_back({"optimizer.m." + p.name, p.shape, hm.data() + p.offset});
-        opt.push_back({"optimizer.v." + p.name, p.shape, hv.data() + p.offset});
-      }
-    const float sf = static_cast<float>(step_count);
-    opt.push_back({"optimizer.step", {1}, &sf});
-    st::save(opt, opt_path_for(ckpt).string());
+    // the all-gathers of the last step must have landed before the parameters are read
+    CTDK_OK_OR_THROW(ctdk_trainer_wait_parameters(trainer, stream));
+    CUDA_OK(cudaStreamSynchronize(stream));
+    std::vector<st::Item> witems, oitems;
+    for (const auto& p : params) witems.push_back({p.name, p.shape, nullptr});
+    // optimizer file: all m tensors (decay group first, then no-decay, main.cpp:218-226), then all v
+    // tensors, then the step counter; offsets are in the header, so any reader finds them by name
+    std::vector<const cli::ParamDesc*> order;
+    for (int pass = 0; pass < 2; ++pass)
+      for (const auto& p : params)
+        if (p.decay == (pass == 0)) order.push_back(&p);
+    for (const char* prefix : {"optimizer.m.", "optimizer.v."})
+      for (const cli::ParamDesc* p : order) oitems.push_back({prefix + p->name, p->shape, nullptr});
+    oitems.push_back({"optimizer.step", {1}, nullptr});
+    if (chief) {
+      st::DeviceWriter w(ckpt.string(), witems, pipe);
+      for (const auto& p : params) w.append_device(d_params.p + p.offset);
+      w.close();
+    }
+    std::unique_ptr<st::DeviceWriter> ow;
+    if (chief) ow = std::make_unique<st::DeviceWriter>(opt_path_for(ckpt).string(), oitems, pipe);
+    for (int which = 0; which < 2; ++which) {
+      // every rank's slices, assembled in arena order in the gradient arena (free between steps)
+      CTDK_OK_OR_THROW(ctdk_trainer_gather_state(trainer, which == 0 ? d_m.p : d_v.p, d_grads.p, stream));
+      CUDA_OK(cudaStreamSynchronize(stream));
+      if (chief)
+        for (const cli::ParamDesc* p : order) ow->append_device(d_grads.p + p->offset);
+    }
+    if (chief) {
+      const float sf = static_cast<float>(step_count);
+      ow->append_host(&sf);
+      ow->close();
+    }
   };
 
   auto run_val = [&]() -> float {
-    double sum_loss = 0.0, sum_mask = 0.0;
-    for (int64_t d0 = 0; d0 < val.docs; d0 += pass_rows) {
+    // validation rows in blocks of pass_rows; block k belongs to rank k % world; one all-reduce at the end
+    CTDK_OK_OR_THROW(ctdk_trainer_zero_loss(trainer, stream));
+    Staging& st = *slots[0];
+    int64_t block = 0;
+    for (int64_t d0 = 0; d0 < val.docs; d0 += pass_rows, ++block) {
+      if (block % world != rank) continue;
       std::vector<int64_t> docs;
       for (int64_t d = d0; d < std::min(val.docs, d0 + pass_rows); ++d) docs.push_back(d);
-      build_batch(val, docs, 1, 1, cfg.seq_len, &hb);
-      if (hb.sum_mask <= 0.0) continue;
-      upload(hb);
-      CUDA_OK(cudaMemsetAsync(d_scal.p, 0, 2 * sizeof(float), stream));
-      CTDK_OK_OR_THROW(ctdk_engine_set_active_rows(engine, d_active.p, static_cast<int64_t>(hb.active.size())));
-      CTDK_OK_OR_THROW(ctdk_engine_forward_loss(engine, d_ids.p, d_tgt.p, d_mask.p, static_cast<int64_t>(docs.size()), T, d_scal.p, stream));
-      float ls[2];
-      CUDA_OK(cudaMemcpyAsync(ls, d_scal.p, sizeof ls, cudaMemcpyDeviceToHost, stream));
-      CUDA_OK(cudaStreamSynchronize(stream));
-      sum_loss += ls[0];
-      sum_mask += ls[1];
+      CUDA_OK(cudaStreamSynchronize(stream));   // the previous block has consumed the staging buffers
+      st.fill(val, docs, pass_rows, S);
+      st.copy(S, copy_stream);
+      CUDA_OK(cudaStreamWaitEvent(stream, st.ready, 0));
+      for (const Pass& ps : st.passes) {
+        widen_pass(st, ps, 1, 1);
+        CTDK_OK_OR_THROW(ctdk_trainer_forward_loss(trainer, d_ids.p, d_tgt.p, d_mask.p, ps.rows, T, stream));
+      }
     }
-    return sum_mask > 0.0 ? static_cast<float>(sum_loss / sum_mask) : 0.0f;
+    CTDK_OK_OR_THROW(ctdk_trainer_allreduce_loss(trainer, stream));
+    float m5[5];
+    CTDK_OK_OR_THROW(ctdk_trainer_read_metrics(trainer, m5, stream));
+    return m5[1] > 0.0f ? m5[0] / m5[1] : 0.0f;
   };
 
   std::mt19937_64 rng(cfg.seed + static_cast<uint64_t>(start_step));
   std::uniform_int_distribution<int64_t> pick(0, train.docs - 1);
+  // The step's documents, drawn micro-batch by micro-batch, row by row, identically on every rank
+  // (main.cpp:347-349); this rank keeps micro-batches rank, rank + world, ...
+  auto stage_step = [&](Staging& st) {
+    std::vector<int64_t> mine;
+    for (int mb = 0; mb < cfg.grad_accum_steps; ++mb)
+      for (int r = 0; r < cfg.batch_size; ++r) {
+        const int64_t d = pick(rng);
+        if (mb % world == rank) mine.push_back(d);
+      }
+    st.fill(train, mine, pass_rows, S);
+    st.copy(S, copy_stream);
+  };
+
   const fs::path log_path = cfg.run_dir / "loss.jsonl";
-  std::ofstream log(log_path, resuming ? (std::ios::out | std::ios::app) : (std::ios::out | std::ios::trunc));
-  if (!log) throw std::runtime_error("cannot open log " + log_path.string());
+  std::ofstream log;
+  if (chief) {
+    log.open(log_path, resuming ? (std::ios::out | std::ios::app) : (std::ios::out | std::ios::trunc));
+    if (!log) throw std::runtime_error("cannot open log " + log_path.string());
+  }
   const auto t_run = std::chrono::steady_clock::now();
 
-  for (int step = static_cast<int>(start_step) + 1; step <= cfg.total_steps; ++step) {
+  const int first_step = static_cast<int>(start_step) + 1;
+  if (first_step <= cfg.total_steps) stage_step(*slots[first_step & 1]);
+  for (int step = first_step; step <= cfg.total_steps; ++step) {
     const auto t_step = std::chrono::steady_clock::now();
-    // the step's documents, drawn micro-batch by micro-batch, row by row
-    std::vector<int64_t> docs(static_cast<size_t>(cfg.grad_accum_steps) * cfg.batch_size);
-    for (auto& d : docs) d = pick(rng);
-    CUDA_OK(cudaMemsetAsync(d_scal.p, 0, 8 * sizeof(float), stream));
-    bool first_pass = true;
-    for (int mb0 = 0; mb0 < cfg.grad_accum_steps; mb0 += fused) {
-      const int nmb = std::min(fused, cfg.grad_accum_steps - mb0);
-      const std::vector<int64_t> sub(docs.begin() + static_cast<int64_t>(mb0) * cfg.batch_size,
-                                     docs.begin() + static_cast<int64_t>(mb0 + nmb) * cfg.batch_size);
-      build_batch(train, sub, cfg.batch_size, cfg.grad_accum_steps, cfg.seq_len, &hb);
-      if (hb.sum_mask <= 0.0) continue;
-      upload(hb);
-      CTDK_OK_OR_THROW(ctdk_engine_set_active_rows(engine, d_active.p, static_cast<int64_t>(hb.active.size())));
-      CTDK_OK_OR_THROW(ctdk_engine_forward_backward(engine, d_ids.p, d_tgt.p, d_mask.p, d_w.p, static_cast<int64_t>(sub.size()), T,
-                                                    first_pass ? 0 : 1, d_scal.p, stream));
-      first_pass = false;
+    Staging& st = *slots[step & 1];
+    CUDA_OK(cudaStreamWaitEvent(stream, st.ready, 0));
+    CTDK_OK_OR_THROW(ctdk_trainer_zero_loss(trainer, stream));
+    for (size_t i = 0; i < st.passes.size(); ++i) {
+      widen_pass(st, st.passes[i], cfg.batch_size, cfg.grad_accum_steps);
+      CTDK_OK_OR_THROW(ctdk_trainer_forward_backward(trainer, d_ids.p, d_tgt.p, d_mask.p, d_w.p, st.passes[i].rows, T,
+                                                     i == 0 ? 0 : 1, i + 1 == st.passes.size() ? 1 : 0, stream));
     }
-    if (first_pass) CUDA_OK(cudaMemsetAsync(d_grads.p, 0, arena * sizeof(float), stream));   // every mask was empty
-
+    if (st.passes.empty())   // every mask of this rank's rows was empty
+      CUDA_OK(cudaMemsetAsync(d_grads.p, 0, static_cast<size_t>(arena) * sizeof(float), stream));
     const float lr = lr_at_step(step, cfg);
-    CTDK_OK_OR_THROW(ctdk_sumsq(d_grads.p, arena, d_scal.p + 2, stream));
-    CTDK_OK_OR_THROW(ctdk_clip_scale(d_scal.p + 2, cfg.clip_grad_norm, 1e-6f, d_scal.p + 3, d_scal.p + 4, stream));
+    CTDK_OK_OR_THROW(ctdk_trainer_optimizer_step(trainer, lr, stream));
     ++step_count;
-    ctdk_adamw_params hp{};
-    hp.lr = lr;
-    hp.beta1 = cfg.beta1;
-    hp.beta2 = cfg.beta2;
-    hp.eps = cfg.eps;
-    hp.wd = 0.0f;
-    hp.bc1 = 1.0f - std::pow(cfg.beta1, static_cast<float>(step_count));
-    hp.bc2 = 1.0f - std::pow(cfg.beta2, static_cast<float>(step_count));
-    CTDK_OK_OR_THROW(ctdk_adamw(d_params.p, d_grads.p, d_m.p, d_v.p, arena, &hp, d_scal.p + 3, d_seg_end.p, d_seg_wd.p,
-                                static_cast<int>(seg_end.size()), stream));
-    float sc[5];
-    CUDA_OK(cudaMemcpyAsync(sc, d_scal.p, sizeof sc, cudaMemcpyDeviceToHost, stream));
-    CUDA_OK(cudaStreamSynchronize(stream));
-    int dev_status[4] = {0, 0, 0, 0};
-    if (ctdk_device_status(stream, dev_status) != CTDK_OK) throw std::runtime_error(ctdk_last_error());
+    // the next step's rows are staged and copied while this step runs
+    const bool val_now = cfg.val_every > 0 && step % cfg.val_every == 0;
+    if (step < cfg.total_steps && !val_now) stage_step(*slots[(step + 1) & 1]);
+    float m5[5];
+    CTDK_OK_OR_THROW(ctdk_trainer_read_metrics(trainer, m5, stream));   // the step's one host sync
 
     const auto t_end = std::chrono::steady_clock::now();
     const double step_s = std::chrono::duration<double>(t_end - t_step).count();
     const double wall_s = std::chrono::duration<double>(t_end - t_run).count();
-    const float train_loss = sc[1] > 0.0f ? sc[0] / sc[1] : 0.0f;
-    const double tps = static_cast<double>(sc[1]) / std::max(step_s, 1e-9);
-    if (cfg.log_every > 0 && step % cfg.log_every == 0) {
+    const float train_loss = m5[1] > 0.0f ? m5[0] / m5[1] : 0.0f;
+    const double tps = static_cast<double>(m5[1]) / std::max(step_s, 1e-9);
+    if (chief && cfg.log_every > 0 && step % cfg.log_every == 0) {
       log << minijson::Line().add("step", static_cast<long long>(step)).add("phase", std::string("train")).add("loss", train_loss)
-                 .add("lr", lr).add("grad_norm", sc[4]).add("tokens_per_sec", tps).add("wall_s", wall_s).dump()
+                 .add("lr", lr).add("grad_norm", m5[4]).add("tokens_per_sec", tps).add("wall_s", wall_s).dump()
           << "\n";
       log.flush();
-      std::cerr << "[step " << step << "/" << cfg.total_steps << "] loss=" << train_loss << " lr=" << lr << " |g|=" << sc[4]
+      std::cerr << "[step " << step << "/" << cfg.total_steps << "] loss=" << train_loss << " lr=" << lr << " |g|=" << m5[4]
                 << " tok/s=" << static_cast<long long>(tps) << "\n";
     }
-    if (cfg.val_every > 0 && step % cfg.val_every == 0) {
+    if (val_now) {
       const auto t_val = std::chrono::steady_clock::now();
       const float vl = run_val();
       const auto now = std::chrono::steady_clock::now();
-      log << minijson::Line().add("step", static_cast<long long>(step)).add("phase", std::string("val")).add("loss", vl)
-                 .add("wall_s", std::chrono::duration<double>(now - t_run).count()).dump()
-          << "\n";
-      log.flush();
-      std::cerr << "[step " << step << "] val_loss=" << vl << " (" << std::chrono::duration<double>(now - t_val).count() << "s)\n";
+      if (chief) {
+        log << minijson::Line().add("step", static_cast<long long>(step)).add("phase", std::string("val")).add("loss", vl)
+                   .add("wall_s", std::chrono::duration<double>(now - t_run).count()).dump()
+            << "\n";
+        log.flush();
+        std::cerr << "[step " << step << "] val_loss=" << vl << " (" << std::chrono::duration<double>(now - t_val).count() << "s)\n";
+      }
+      if (step < cfg.total_steps) stage_step(*slots[(step + 1) & 1]);   // validation used a staging slot
     }
     if (cfg.save_every > 0 && step % cfg.save_every == 0) {
       const fs::path ckpt = cfg.run_dir / ("ckpt_step_" + std::to_string(step) + ".safetensors");
       save_checkpoint(ckpt);
-      std::cerr << "[step " << step << "] saved " << ckpt << " (+ optimizer)\n";
+      if (chief) std::cerr << "[step " << step << "] saved " << ckpt << " (+ optimizer)\n";
     }
   }
 
   const fs::path final_ckpt = cfg.run_dir / "final.safetensors";
   save_checkpoint(final_ckpt);
-  std::cerr << "[ctd_train] done. final → " << final_ckpt << " (+ optimizer)\n";
-  ctdk_engine_destroy(engine);
+  say("done. final → \"" + final_ckpt.string() + "\" (+ optimizer)");
+  ctdk_trainer_destroy(trainer);
+  if (chief && !id_file.empty()) {
+    std::error_code ec;
+    fs::remove(id_file, ec);
+  }
+  cudaFree(d_ws);
+  cudaStreamDestroy(copy_stream);
   cudaStreamDestroy(stream);
   return 0;
 } catch (const std::exception& e) {

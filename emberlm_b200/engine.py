@@ -244,12 +244,107 @@ _L.ctdk_engine_set_layer_callback.restype = C.c_int
 _L.ctdk_engine_set_layer_callback.argtypes = [C.c_void_p, LAYER_CALLBACK, C.c_void_p]
 
 
+class TrainerHParams(C.Structure):
+    """ctdk_trainer_hparams."""
+    _fields_ = [("lr", C.c_float), ("beta1", C.c_float), ("beta2", C.c_float), ("eps", C.c_float),
+                ("weight_decay", C.c_float), ("clip", C.c_float), ("layers_per_bucket", C.c_int)]
+
+
+_L.ctdk_dp_arena_floats.restype = C.c_int64
+_L.ctdk_dp_arena_floats.argtypes = [C.POINTER(ModelConfig), C.c_int]
+_L.ctdk_dp_num_buckets.restype = C.c_int
+_L.ctdk_dp_num_buckets.argtypes = [C.POINTER(ModelConfig), C.c_int, C.c_int]
+_L.ctdk_dp_buckets.restype = C.c_int
+_L.ctdk_dp_buckets.argtypes = [C.POINTER(ModelConfig), C.c_int, C.c_int, C.c_int] + [C.POINTER(C.c_int64)] * 5 + [
+    C.POINTER(C.c_int)]
+_L.ctdk_dp_segments.restype = C.c_int
+_L.ctdk_dp_segments.argtypes = [C.POINTER(ModelConfig), C.c_float, C.c_int64, C.c_int64, C.POINTER(C.c_int64),
+                                C.POINTER(C.c_float), C.c_int]
+_L.ctdk_trainer_unique_id.restype = C.c_int
+_L.ctdk_trainer_unique_id.argtypes = [C.c_void_p]
+_L.ctdk_trainer_create.restype = C.c_int
+_L.ctdk_trainer_create.argtypes = [C.POINTER(ModelConfig), C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
+                                   C.c_int64, C.c_int64, C.c_int64, C.c_int, C.c_int, C.c_void_p,
+                                   C.POINTER(TrainerHParams), C.POINTER(C.c_void_p)]
+_L.ctdk_trainer_destroy.restype = C.c_int
+_L.ctdk_trainer_destroy.argtypes = [C.c_void_p]
+_L.ctdk_trainer_engine.restype = C.c_void_p
+_L.ctdk_trainer_engine.argtypes = [C.c_void_p]
+_L.ctdk_trainer_set_layer_callback.restype = C.c_int
+_L.ctdk_trainer_set_layer_callback.argtypes = [C.c_void_p, LAYER_CALLBACK, C.c_void_p]
+_L.ctdk_trainer_step.restype = C.c_int
+_L.ctdk_trainer_step.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64,
+                                 C.c_void_p, C.c_int64, C.c_float, C.c_void_p]
+_L.ctdk_trainer_zero_loss.restype = C.c_int
+_L.ctdk_trainer_zero_loss.argtypes = [C.c_void_p, C.c_void_p]
+_L.ctdk_trainer_forward_backward.restype = C.c_int
+_L.ctdk_trainer_forward_backward.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64,
+                                             C.c_int64, C.c_int, C.c_int, C.c_void_p]
+_L.ctdk_trainer_forward_loss.restype = C.c_int
+_L.ctdk_trainer_forward_loss.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_void_p]
+_L.ctdk_trainer_optimizer_step.restype = C.c_int
+_L.ctdk_trainer_optimizer_step.argtypes = [C.c_void_p, C.c_float, C.c_void_p]
+_L.ctdk_trainer_allreduce_loss.restype = C.c_int
+_L.ctdk_trainer_allreduce_loss.argtypes = [C.c_void_p, C.c_void_p]
+_L.ctdk_trainer_wait_parameters.restype = C.c_int
+_L.ctdk_trainer_wait_parameters.argtypes = [C.c_void_p, C.c_void_p]
+_L.ctdk_trainer_read_metrics.restype = C.c_int
+_L.ctdk_trainer_read_metrics.argtypes = [C.c_void_p, C.POINTER(C.c_float), C.c_void_p]
+_L.ctdk_trainer_loss_sums.restype = C.c_void_p
+_L.ctdk_trainer_loss_sums.argtypes = [C.c_void_p]
+_L.ctdk_trainer_step_count.restype = C.c_int64
+_L.ctdk_trainer_step_count.argtypes = [C.c_void_p]
+_L.ctdk_trainer_set_step_count.restype = C.c_int
+_L.ctdk_trainer_set_step_count.argtypes = [C.c_void_p, C.c_int64]
+_L.ctdk_trainer_gather_state.restype = C.c_int
+_L.ctdk_trainer_gather_state.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]
+_L.ctdk_trainer_scatter_state.restype = C.c_int
+_L.ctdk_trainer_scatter_state.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]
+_L.ctdk_batch_widen.restype = C.c_int
+_L.ctdk_batch_widen.argtypes = [C.c_void_p, C.c_void_p, C.c_int64, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p,
+                                C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]
+
+
+def dp_plan(cfg: ModelConfig, world: int, rank: int, layers_per_bucket: int = 4):
+    """The library's bucket plan (ctdk_dp_buckets) as a list of dicts: lo, hi, a, b (the slice `rank`
+    owns), state (offset of that slice in the rank's m / v), ready."""
+    n = _L.ctdk_dp_num_buckets(C.byref(cfg), world, layers_per_bucket)
+    if n < 0:
+        raise lib.CtdkError(-1, lib.last_error())
+    arr = [(C.c_int64 * n)() for _ in range(5)]
+    ready = (C.c_int * n)()
+    lib.check(_L.ctdk_dp_buckets(C.byref(cfg), world, rank, layers_per_bucket, *arr, ready))
+    return [dict(lo=arr[0][i], hi=arr[1][i], a=arr[2][i], b=arr[3][i], state=arr[4][i], ready=ready[i])
+            for i in range(n)]
+
+
+def dp_segments(cfg: ModelConfig, weight_decay: float, lo: int, hi: int):
+    """The library's weight-decay segments of the arena range [lo, hi) (ctdk_dp_segments)."""
+    n = _L.ctdk_dp_segments(C.byref(cfg), weight_decay, lo, hi, None, None, 0)
+    if n < 0:
+        raise lib.CtdkError(-1, lib.last_error())
+    ends, wds = (C.c_int64 * n)(), (C.c_float * n)()
+    _L.ctdk_dp_segments(C.byref(cfg), weight_decay, lo, hi, ends, wds, n)
+    return list(ends), list(wds)
+
+
+def nccl_unique_id() -> bytes:
+    """128-byte NCCL unique id (rank 0 makes it, every rank passes the same bytes to TrainEngine)."""
+    buf = C.create_string_buffer(128)
+    lib.check(_L.ctdk_trainer_unique_id(buf))
+    return buf.raw
+
+
 class TrainEngine:
-    """One rank's training state: parameter / gradient arenas, ZeRO-1 shard of AdamW m/v,
-    workspace, and the step. `group` is a torch.distributed process group (None = 1 GPU)."""
+    """One rank's training state on top of the library's data-parallel trainer (ctdk_trainer_*):
+    torch owns the device memory (parameter / gradient arenas, this rank's ZeRO-1 slices of AdamW's
+    m / v, the workspace); the step, the bucketed reduce-scatter / all-gather over NCCL and the
+    optimizer run inside libctdk.so. `group` is a torch.distributed process group (None = 1 GPU),
+    used only to hand rank 0's NCCL unique id to the other ranks; pass `nccl_id` to do that yourself."""
 
     def __init__(self, cfg: ModelConfig, batch: int, seq: int, device="cuda:0", group=None,
-                 lr=1e-4, beta1=0.9, beta2=0.999, eps=1e-8, weight_decay=0.01, clip=1.0, train=True):
+                 lr=1e-4, beta1=0.9, beta2=0.999, eps=1e-8, weight_decay=0.01, clip=1.0, train=True,
+                 rank=None, world=None, nccl_id: bytes | None = None):
         self.cfg, self.B, self.T = cfg, batch, seq
         self.device = torch.device(device)
         self.group = group
@@ -257,14 +352,20 @@ class TrainEngine:
             import torch.distributed as dist
             self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
         else:
-            self.world, self.rank = 1, 0
+            self.world, self.rank = (world or 1), (rank or 0)
         if self.world > 1:
             # The collectives run beside the backward pass on their own stream and hold a few SMs
             # while they do; a persistent GEMM that wants every SM would then run in two waves.
             lib.check(_L.ctdk_reserve_sms(int(os.environ.get("CTDK_DP_RESERVED_SMS", "0"))))
+            if nccl_id is None:
+                import torch.distributed as dist
+                box = [nccl_unique_id() if self.rank == 0 else None]
+                dist.broadcast_object_list(box, src=dist.get_global_rank(group, 0), group=group)
+                nccl_id = box[0]
         self.layout = model_layout(cfg)
         # arena padded so that it splits evenly over ranks in 64-float units
-        self.total = padded_total(self.layout.total, self.world)
+        self.total = _L.ctdk_dp_arena_floats(C.byref(cfg), self.world)
+        assert self.total == padded_total(self.layout.total, self.world)
         self.shard = self.total // self.world
         self.params = torch.zeros(self.total, dtype=torch.float32, device=self.device)
         self.grads = torch.zeros(self.total, dtype=torch.float32, device=self.device) if train else None
@@ -272,33 +373,54 @@ class TrainEngine:
         if ws < 0:
             raise lib.CtdkError(-1, lib.last_error())
         self.workspace = torch.empty(ws, dtype=torch.uint8, device=self.device)
-        self._h = C.c_void_p()
-        lib.check(_L.ctdk_engine_create(C.byref(cfg), self.params.data_ptr(),
-                                        self.grads.data_ptr() if train else None,
-                                        self.workspace.data_ptr(), ws, batch, seq, C.byref(self._h)))
-        self.loss_sums = torch.zeros(2, dtype=torch.float32, device=self.device)
         self.hp = dict(lr=lr, beta1=beta1, beta2=beta2, eps=eps, weight_decay=weight_decay, clip=clip)
-        self.step_count = 0
+        self._t = None
+        self._h = C.c_void_p()
         self._cb = None
-        self._user_cb = None
+        self.device_status = 0
         if train:
             self.m = torch.zeros(self.shard, dtype=torch.float32, device=self.device)
             self.v = torch.zeros(self.shard, dtype=torch.float32, device=self.device)
-            self._scalars = torch.zeros(4, dtype=torch.float32, device=self.device)  # sumsq, scale, norm
-            self._build_segments()
-            if self.world > 1:
-                self._install_bucket_callback()
+            per = int(os.environ.get("CTDK_DP_BUCKET_LAYERS", "4"))
+            thp = TrainerHParams(lr, beta1, beta2, eps, weight_decay, clip, per)
+            self._t = C.c_void_p()
+            with torch.cuda.device(self.device):
+                lib.check(_L.ctdk_trainer_create(C.byref(cfg), self.params.data_ptr(), self.grads.data_ptr(),
+                                                 self.m.data_ptr(), self.v.data_ptr(), self.workspace.data_ptr(), ws,
+                                                 batch, seq, self.rank, self.world, nccl_id, C.byref(thp),
+                                                 C.byref(self._t)))
+            self._h = C.c_void_p(_L.ctdk_trainer_engine(self._t))
+            self.buckets = dp_plan(cfg, self.world, self.rank, per if self.world > 1 else 0)
+            # device float[2] {sum mask*loss, sum mask} the passes add to (inside the trainer)
+            self.loss_sums = _view_device_floats(_L.ctdk_trainer_loss_sums(self._t), 2, self.device)
+        else:
+            lib.check(_L.ctdk_engine_create(C.byref(cfg), self.params.data_ptr(), None,
+                                            self.workspace.data_ptr(), ws, batch, seq, C.byref(self._h)))
+            self.buckets = []
+            self.loss_sums = torch.zeros(2, dtype=torch.float32, device=self.device)
 
     def __del__(self):
-        h = getattr(self, "_h", None)
-        if h and _L is not None:
+        t, h = getattr(self, "_t", None), getattr(self, "_h", None)
+        if _L is None:
+            return
+        if t:
+            _L.ctdk_trainer_destroy(t)
+            self._t = self._h = None
+        elif h:
             _L.ctdk_engine_destroy(h)
             self._h = None
 
+    @property
+    def step_count(self) -> int:
+        return int(_L.ctdk_trainer_step_count(self._t)) if self._t else 0
+
+    @step_count.setter
+    def step_count(self, n: int) -> None:
+        lib.check(_L.ctdk_trainer_set_step_count(self._t, int(n)))
+
     # ---- parameters -------------------------------------------------------------------
     def named_parameters(self) -> dict:
-        if getattr(self, "buckets", None):
-            self.wait_parameters()
+        self.wait_parameters()
         lo = self.layout
         return {n: self.params[o:o + k].view(s) for n, s, o, k in zip(lo.names, lo.shapes, lo.offsets, lo.numels)}
 
@@ -326,84 +448,30 @@ class TrainEngine:
             else:
                 v.fill_(1.0)
 
-    def _build_segments(self) -> None:
-        """One rank: one segment table over the whole arena. Several ranks: the arena is cut into
-        buckets (make_buckets), rank r owns slice r of each; m / v hold the slices back to back and
-        every slice has its own weight-decay segment table."""
-        wd = self.hp["weight_decay"]
-        if self.world == 1:
-            ends, wds = build_segments(self.layout, wd, 0, self.total)
-            self.seg_end = torch.tensor(ends, dtype=torch.int64, device=self.device)
-            self.seg_wd = torch.tensor(wds, dtype=torch.float32, device=self.device)
-            self.buckets = []
-            return
-        self.buckets = []
-        pos = 0
-        per = int(os.environ.get("CTDK_DP_BUCKET_LAYERS", "4"))
-        for lo, hi, ready in make_buckets(self.layout, self.total, self.world, self.cfg.num_hidden_layers, per):
-            a, b = bucket_slice(lo, hi, self.world, self.rank)
-            ends, wds = build_segments(self.layout, wd, a, b)
-            self.buckets.append(dict(
-                lo=lo, hi=hi, ready=ready, a=a, b=b, state=pos,
-                seg_end=torch.tensor(ends, dtype=torch.int64, device=self.device),
-                seg_wd=torch.tensor(wds, dtype=torch.float32, device=self.device), work=None))
-            pos += b - a
-        assert pos == self.shard
-
-    def _install_bucket_callback(self) -> None:
-        """Reduce-scatter of a bucket starts as soon as the backward kernels of the last layer it
-        needs have been enqueued: the collective runs on the process group's own stream behind an
-        event on the compute stream, so it overlaps the backward of the layers below."""
-        import torch.distributed as dist
-
-        def on_layer(layer: int) -> None:
-            if self._user_cb is not None:
-                self._user_cb(layer)
-            if not self._reduce_in_backward:
-                return
-            for bk in self.buckets:
-                if bk["ready"] == layer and bk["work"] is None:
-                    bk["work"] = dist.reduce_scatter_tensor(self.grads[bk["a"]:bk["b"]], self.grads[bk["lo"]:bk["hi"]],
-                                                            op=dist.ReduceOp.SUM, group=self.group, async_op=True)
-
-        self._reduce_in_backward = False
-        self._cb = LAYER_CALLBACK(lambda layer, _u: on_layer(layer))
-        lib.check(_L.ctdk_engine_set_layer_callback(self._h, self._cb, None))
-
-        # All-gathers of the updated parameters are left in flight by optimizer_step(); each part of
-        # the next forward pass first makes the compute stream wait for the buckets it reads (the
-        # embedding bucket is also the tied LM head, read again at the end).
-        L = self.cfg.num_hidden_layers
-        for bk in self.buckets:
-            touched = [tensor_layer(n, L) for n, o, k in zip(self.layout.names, self.layout.offsets, self.layout.numels)
-                       if o < bk["hi"] and o + k > bk["lo"]]
-            bk["first_use"] = min(touched) if touched else L
-            bk["gather"] = None
-
-        def on_forward(layer: int) -> None:
-            for bk in self.buckets:
-                if bk["gather"] is not None and bk["first_use"] <= layer:
-                    bk["gather"].wait()
-                    bk["gather"] = None
-
-        self._fcb = LAYER_CALLBACK(lambda layer, _u: on_forward(layer))
-        lib.check(_L.ctdk_engine_set_forward_callback(self._h, self._fcb, None))
-
     def wait_parameters(self) -> None:
         """Makes the current stream wait for every all-gather that optimizer_step() left in flight.
         Called before anything other than the engine's own forward pass reads self.params."""
-        for bk in getattr(self, "buckets", []):
-            if bk.get("gather") is not None:
-                bk["gather"].wait()
-                bk["gather"] = None
+        if self._t:
+            lib.check(_L.ctdk_trainer_wait_parameters(self._t, _stream_ptr()))
+
+    def gather_state(self, shard_state: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+        """m or v in arena order, assembled from every rank's slices (for checkpoints)."""
+        out = torch.empty(self.total, dtype=torch.float32, device=self.device) if out is None else out
+        lib.check(_L.ctdk_trainer_gather_state(self._t, shard_state.data_ptr(), out.data_ptr(), _stream_ptr()))
+        return out
+
+    def scatter_state(self, full: torch.Tensor, shard_state: torch.Tensor) -> None:
+        lib.check(_L.ctdk_trainer_scatter_state(self._t, full.data_ptr(), shard_state.data_ptr(), _stream_ptr()))
 
     # ---- step -------------------------------------------------------------------------
     def set_layer_callback(self, fn) -> None:
-        if self.world > 1 and self.grads is not None:
-            self._user_cb = fn          # chained in front of the gradient-bucket callback
-            return
+        """fn(layer) is called when everything that writes layer `layer`'s gradients has been
+        ordered before the current stream (see ctdk_engine_set_layer_callback)."""
         self._cb = LAYER_CALLBACK(lambda layer, _u: fn(layer)) if fn else LAYER_CALLBACK(0)
-        lib.check(_L.ctdk_engine_set_layer_callback(self._h, self._cb, None))
+        if self._t:
+            lib.check(_L.ctdk_trainer_set_layer_callback(self._t, self._cb, None))
+        else:
+            lib.check(_L.ctdk_engine_set_layer_callback(self._h, self._cb, None))
 
     def set_active_rows(self, rows: torch.Tensor | None) -> None:
         """Names the supervised positions (ascending int32 indices into the flattened batch) of the
@@ -416,84 +484,68 @@ class TrainEngine:
         """last=True (several ranks): this is the step's final backward pass, so each gradient
         bucket is reduce-scattered as soon as it is complete; optimizer_step() picks the results up."""
         B, T = ids.shape
-        self._reduce_in_backward = bool(last) and self.world > 1
-        try:
-            lib.check(_L.ctdk_engine_forward_backward(
-                self._h, ids.data_ptr(), targets.data_ptr(), loss_mask.data_ptr(), row_weight.data_ptr(),
-                B, T, int(accumulate), self.loss_sums.data_ptr(), _stream_ptr()))
-        finally:
-            self._reduce_in_backward = False
+        lib.check(_L.ctdk_trainer_forward_backward(
+            self._t, ids.data_ptr(), targets.data_ptr(), loss_mask.data_ptr(), row_weight.data_ptr(),
+            B, T, int(accumulate), int(last), _stream_ptr()))
 
     def forward_loss(self, ids, targets, loss_mask) -> None:
         B, T = ids.shape
-        lib.check(_L.ctdk_engine_forward_loss(self._h, ids.data_ptr(), targets.data_ptr(),
-                                              loss_mask.data_ptr(), B, T, self.loss_sums.data_ptr(),
-                                              _stream_ptr()))
+        if self._t:
+            lib.check(_L.ctdk_trainer_forward_loss(self._t, ids.data_ptr(), targets.data_ptr(), loss_mask.data_ptr(),
+                                                   B, T, _stream_ptr()))
+        else:
+            lib.check(_L.ctdk_engine_forward_loss(self._h, ids.data_ptr(), targets.data_ptr(), loss_mask.data_ptr(),
+                                                  B, T, self.loss_sums.data_ptr(), _stream_ptr()))
 
     def optimizer_step(self, lr=None) -> None:
         """reduce-scatter(grads) -> sum of squares (+ all-reduce) -> clip scale -> fused AdamW on
-        this rank's slices -> all-gather(params). No host synchronisation. With several ranks the
-        arena is handled bucket by bucket: reduce-scatters that forward_backward(last=True) already
-        started are only waited for (a stream dependency), the rest are issued here; the all-gather
-        of a bucket overlaps the AdamW of the next."""
-        hp = self.hp
-        lr = hp["lr"] if lr is None else lr
-        s = _stream_ptr()
-        sc = self._scalars
-        sc.zero_()
-        if self.world > 1:
-            import torch.distributed as dist
-            order = sorted(self.buckets, key=lambda bk: -bk["ready"])   # the order backward completes them
-            for bk in order:
-                if bk["work"] is None:
-                    bk["work"] = dist.reduce_scatter_tensor(self.grads[bk["a"]:bk["b"]], self.grads[bk["lo"]:bk["hi"]],
-                                                            op=dist.ReduceOp.SUM, group=self.group, async_op=True)
-            for bk in order:
-                bk["work"].wait()
-                bk["work"] = None
-                lib.call("ctdk_sumsq", self.grads[bk["a"]:bk["b"]].data_ptr(), bk["b"] - bk["a"], sc.data_ptr(), s)
-            dist.all_reduce(sc[0:1], group=self.group)
-            dist.all_reduce(self.loss_sums, group=self.group)
-        else:
-            lib.call("ctdk_sumsq", self.grads.data_ptr(), self.shard, sc.data_ptr(), s)
-        lib.call("ctdk_clip_scale", sc.data_ptr(), hp["clip"], 1e-6, sc[1:].data_ptr(), sc[2:].data_ptr(), s)
-        self.step_count += 1
-        t = np.float32(self.step_count)
-        bc1 = np.float32(1.0) - np.power(np.float32(hp["beta1"]), t, dtype=np.float32)
-        bc2 = np.float32(1.0) - np.power(np.float32(hp["beta2"]), t, dtype=np.float32)
-        ap = lib.AdamWParams(lr, hp["beta1"], hp["beta2"], hp["eps"], 0.0, float(bc1), float(bc2))
-        if self.world == 1:
-            lib.call("ctdk_adamw", self.params.data_ptr(), self.grads.data_ptr(), self.m.data_ptr(),
-                     self.v.data_ptr(), self.shard, C.byref(ap), sc[1:].data_ptr(), self.seg_end.data_ptr(),
-                     self.seg_wd.data_ptr(), self.seg_end.numel(), s)
-            return
-        import torch.distributed as dist
-        for bk in self.buckets:   # arena order = the order the next forward pass reads them
-            n, st = bk["b"] - bk["a"], bk["state"]
-            pslice = self.params[bk["a"]:bk["b"]]
-            lib.call("ctdk_adamw", pslice.data_ptr(), self.grads[bk["a"]:bk["b"]].data_ptr(),
-                     self.m[st:st + n].data_ptr(), self.v[st:st + n].data_ptr(), n, C.byref(ap), sc[1:].data_ptr(),
-                     bk["seg_end"].data_ptr(), bk["seg_wd"].data_ptr(), bk["seg_end"].numel(), s)
-            bk["gather"] = dist.all_gather_into_tensor(self.params[bk["lo"]:bk["hi"]], pslice, group=self.group,
-                                                       async_op=True)
+        this rank's slices -> all-gather(params), all inside ctdk_trainer_optimizer_step. No host
+        synchronisation; the all-gathers are left in flight for the next forward pass."""
+        lib.check(_L.ctdk_trainer_optimizer_step(self._t, self.hp["lr"] if lr is None else lr, _stream_ptr()))
         if os.environ.get("CTDK_DP_GATHER_OVERLAP", "1") != "1":
             self.wait_parameters()
 
     def train_step(self, ids, targets, loss_mask, row_weight, lr=None, active_rows=None) -> None:
         """One optimizer step on this rank's rows (already weighted per micro-batch). active_rows:
         optional int32 device tensor of the supervised positions (see set_active_rows)."""
-        self.loss_sums.zero_()
-        if active_rows is not None:
-            self.set_active_rows(active_rows)
-        self.forward_backward(ids, targets, loss_mask, row_weight, accumulate=False, last=True)
-        self.optimizer_step(lr)
+        B, T = ids.shape
+        self._active = active_rows
+        n = 0 if active_rows is None else active_rows.numel()
+        lib.check(_L.ctdk_trainer_step(self._t, ids.data_ptr(), targets.data_ptr(), loss_mask.data_ptr(),
+                                       row_weight.data_ptr(), B, T, active_rows.data_ptr() if n else None, n,
+                                       self.hp["lr"] if lr is None else lr, _stream_ptr()))
+        if os.environ.get("CTDK_DP_GATHER_OVERLAP", "1") != "1":
+            self.wait_parameters()
 
     def read_metrics(self) -> dict:
         """Synchronises and returns the logged loss (mask-weighted mean, main.cpp:365-380) and
-        the pre-clip gradient norm of the last step."""
-        ls = self.loss_sums.tolist()
-        sc = self._scalars.tolist()
-        return dict(loss=ls[0] / ls[1] if ls[1] > 0 else 0.0, mask_sum=ls[1], grad_norm=sc[2], clip_scale=sc[1])
+        the pre-clip gradient norm of the last step. Raises CtdkError if a bounded device-side wait
+        gave up since the last call (the results since then are not to be trusted)."""
+        out = (C.c_float * 5)()
+        lib.check(_L.ctdk_trainer_read_metrics(self._t, out, _stream_ptr()))
+        self.device_status = 0
+        return dict(loss=out[0] / out[1] if out[1] > 0 else 0.0, mask_sum=out[1], grad_norm=out[4], clip_scale=out[3])
+
+
+class _DeviceFloats:
+    """A few fp32 values in device memory that the library owns, exposed through the CUDA array
+    interface so that torch can view them without copying."""
+
+    def __init__(self, ptr: int, n: int):
+        self.__cuda_array_interface__ = {"shape": (n,), "typestr": "<f4", "data": (ptr, False), "version": 3,
+                                         "strides": None}
+
+
+def _view_device_floats(ptr: int, n: int, device) -> torch.Tensor:
+    return torch.as_tensor(_DeviceFloats(ptr, n), device=device)
+
+
+def check_device_status() -> int:
+    """Reads (and clears) the device status word that the kernels' bounded waits write when one of
+    them gives up; synchronises the current stream. Raises CtdkError (CTDK_ETIMEOUT) if a wait ran
+    out since the last check: the results computed since then are not to be trusted."""
+    lib.check(_L.ctdk_device_status(_stream_ptr(), None))
+    return 0
 
 
 def row_weights(loss_mask: torch.Tensor, micro_batch: int, accum_total: int) -> torch.Tensor:
@@ -574,6 +626,8 @@ class Decoder:
             lib.check(_L.ctdk_decode_prefill(self._h, ids.data_ptr(), ids.numel(), self.stream.cuda_stream))
             if n > 0:
                 lib.check(_L.ctdk_decode_greedy(self._h, n, out.data_ptr(), self.stream.cuda_stream))
+            # a bounded wait that gave up inside a kernel of the generation is an error, not a result
+            lib.check(_L.ctdk_device_status(self.stream.cuda_stream, None))
         torch.cuda.current_stream().wait_stream(self.stream)
         return out[:max(n, 0)]
 

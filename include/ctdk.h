@@ -347,6 +347,100 @@ int ctdk_engine_set_layer_callback(void* engine, ctdk_layer_callback cb, void* u
 int ctdk_engine_set_forward_callback(void* engine, ctdk_layer_callback cb, void* user);
 
 /* ------------------------------------------------------------------------------------
+ * Data feed: widens one pass's rows from the reference's bin format (int32 token rows and int8
+ * 0/1 loss masks of length S, tools/ctd_train/main.cpp:121-136) to what the engine takes, on the
+ * device, so that only 5 bytes per token cross PCIe instead of the 24 bytes of the int64 / fp32
+ * host vectors make_batch builds (main.cpp:145-174):
+ *   ids[r,t] = tok[r,t], targets[r,t] = tok[r,t+1], mask[r,t] = msk[r,t+1]   (t < S-1)
+ *   weight[r,t] = mask[r,t] / (accum_total * sum(mask of the row's micro-batch))
+ * where consecutive groups of micro_rows rows form a micro-batch and accum_total counts the
+ * micro-batches of the whole step over all ranks (mul_scalar(loss, 1/A) and the masked-CE backward,
+ * main.cpp:346-361, src/ops/loss.cu:388-411). A micro-batch with an empty mask gets weight 0
+ * (main.cpp:357). micro_sums is scratch of ceil(rows / micro_rows) floats.
+ * ------------------------------------------------------------------------------------ */
+int ctdk_batch_widen(const int32_t* tok, const int8_t* msk, int64_t rows, int S, int micro_rows,
+                     int accum_total, int64_t* ids, int64_t* targets, float* mask, float* weight,
+                     float* micro_sums, void* stream);
+
+/* ------------------------------------------------------------------------------------
+ * Data-parallel trainer: the part of the step loop after the backward pass (clip_grad_norm_,
+ * AdamW::step, zero_grad; tools/ctd_train/main.cpp:362-373) for one process per GPU, with ZeRO-1
+ * sharding of AdamW's m / v over buckets of the arena in place of the reference's host offload
+ * (src/core/optim.cu:94-130): ncclReduceScatter per gradient bucket started from the engine's
+ * layer callback underneath the backward pass, one scalar ncclAllReduce, fused AdamW on the rank's
+ * slices, ncclAllGather of the parameters left in flight under the next forward pass.
+ *
+ * Plan (host only, no GPU needed): the arena is padded to a multiple of 64*world floats
+ * (ctdk_dp_arena_floats) and cut into contiguous buckets — the embedding, then groups of
+ * layers_per_bucket decoder layers, cuts rounded down to 64*world floats; 0 = one bucket. For
+ * bucket i, [lo, hi) is its arena range, [own_lo, own_hi) the slice rank `rank` owns,
+ * state_offset where that slice starts in the rank's m / v arrays (the slices back to back) and
+ * ready the lowest completion index of the tensors it overlaps (-1 embedding, l decoder layer,
+ * L final norm): its gradients are final once the layer callback has fired for `ready`, and the
+ * forward pass first reads it at the forward callback of `ready`. ctdk_dp_segments returns the
+ * number of weight-decay segments of an arena range (decay group = embedding + linear weights,
+ * norm weights and padding 0; main.cpp:304-311) and fills up to `capacity` of them.
+ * ------------------------------------------------------------------------------------ */
+int64_t ctdk_dp_arena_floats(const ctdk_model_config* cfg, int world);
+int ctdk_dp_num_buckets(const ctdk_model_config* cfg, int world, int layers_per_bucket);
+int ctdk_dp_buckets(const ctdk_model_config* cfg, int world, int rank, int layers_per_bucket,
+                    int64_t* lo, int64_t* hi, int64_t* own_lo, int64_t* own_hi,
+                    int64_t* state_offset, int* ready);
+int ctdk_dp_segments(const ctdk_model_config* cfg, float weight_decay, int64_t lo, int64_t hi,
+                     int64_t* seg_end, float* seg_wd, int capacity);
+
+typedef struct {
+  float lr, beta1, beta2, eps, weight_decay, clip; /* AdamW + clip_grad_norm_ (main.cpp:304-313) */
+  int layers_per_bucket;                           /* < 0: default (4); 0: one bucket */
+} ctdk_trainer_hparams;
+
+/* Rank 0 makes the 128-byte NCCL unique id and hands it to the other ranks (file, socket, ...). */
+int ctdk_trainer_unique_id(void* id128);
+/* params / grads: arenas of ctdk_dp_arena_floats(cfg, world) floats; m / v: that / world floats
+ * (zeroed by the caller, or loaded); workspace as for ctdk_engine_create, which it calls. With
+ * world > 1 every rank must call it (communicator set-up is collective) with the same id. Allocates
+ * a few KB of device memory for scalars and segment tables; nothing is allocated afterwards. */
+int ctdk_trainer_create(const ctdk_model_config* cfg, float* params, float* grads, float* m, float* v,
+                        void* workspace, int64_t workspace_bytes, int64_t B, int64_t T, int rank,
+                        int world, const void* nccl_id, const ctdk_trainer_hparams* hp, void** trainer);
+int ctdk_trainer_destroy(void* trainer);
+void* ctdk_trainer_engine(void* trainer); /* the ctdk_engine_* handle inside (set_active_rows) */
+/* Called in front of the trainer's own layer callback (same contract as the engine's). */
+int ctdk_trainer_set_layer_callback(void* trainer, ctdk_layer_callback cb, void* user);
+/* One optimizer step on this rank's rows: zero the loss sums, forward + backward with the bucket
+ * reduce-scatters, then ctdk_trainer_optimizer_step. active_rows as ctdk_engine_set_active_rows. */
+int ctdk_trainer_step(void* trainer, const int64_t* ids, const int64_t* targets, const float* loss_mask,
+                      const float* row_weight, int64_t B, int64_t T, const int32_t* active_rows,
+                      int64_t n_active, float lr, void* stream);
+/* The pieces, for steps of several passes (gradient accumulation): `last` != 0 marks the final
+ * backward pass of the step, whose buckets are reduce-scattered as they complete. */
+int ctdk_trainer_zero_loss(void* trainer, void* stream);
+int ctdk_trainer_forward_backward(void* trainer, const int64_t* ids, const int64_t* targets,
+                                  const float* loss_mask, const float* row_weight, int64_t B, int64_t T,
+                                  int accumulate, int last, void* stream);
+int ctdk_trainer_forward_loss(void* trainer, const int64_t* ids, const int64_t* targets,
+                              const float* loss_mask, int64_t B, int64_t T, void* stream);
+int ctdk_trainer_optimizer_step(void* trainer, float lr, void* stream);
+/* Sums the two loss sums over the ranks (validation split over ranks; the optimizer step does this
+ * itself for training passes). Collective: every rank calls it the same number of times. */
+int ctdk_trainer_allreduce_loss(void* trainer, void* stream);
+/* Makes `stream` wait for the parameter all-gathers the last optimizer step left in flight; call it
+ * before anything but the trainer's own forward pass reads the parameter arena. */
+int ctdk_trainer_wait_parameters(void* trainer, void* stream);
+/* Synchronises `stream` and returns {sum mask*loss, sum mask, sum g^2, clip scale, gradient norm}
+ * of the last step (summed over ranks), then checks the device status word: CTDK_ETIMEOUT if a
+ * bounded device-side wait gave up since the last check. */
+int ctdk_trainer_read_metrics(void* trainer, float* out5, void* stream);
+const float* ctdk_trainer_loss_sums(void* trainer); /* device float[2] the passes add to */
+int64_t ctdk_trainer_step_count(void* trainer);
+int ctdk_trainer_set_step_count(void* trainer, int64_t n);
+/* Checkpoints (tools/ctd_train/main.cpp:208-271 keep m / v per parameter): gather assembles the
+ * ranks' slices of m or v into arena order in `full` (arena floats, device; every rank calls it);
+ * scatter copies this rank's slices out of an arena-order array at load. */
+int ctdk_trainer_gather_state(void* trainer, const float* shard_state, float* full, void* stream);
+int ctdk_trainer_scatter_state(void* trainer, const float* full, float* shard_state, void* stream);
+
+/* ------------------------------------------------------------------------------------
  * KV-cache greedy decoding, batch 1. Replaces the cached inference path: Model::forward with a
  * KVCache (include/ctd/nn/model.h:155-167), Attention::forward (include/ctd/nn/attention.h:43-97),
  * write_kv_inplace / read_kv_expanded (src/ops/kv_cache.cu:49-109) and the greedy sampler

@@ -1,11 +1,14 @@
 // Minimal JSON reader / line writer for the command-line tools: the run config, the
 // safetensors header and the loss.jsonl events (the reference uses nlohmann/json for these,
 // emberlm tools/ctd_train/main.cpp:72-103, 377-389; src/core/safetensors.cpp:40-70).
-// Numbers are kept as double, objects keep their keys sorted (as nlohmann's default object does,
+// Numbers are kept as double (non-negative integer literals also exactly, as uint64, so that a
+// 64-bit seed survives), objects keep their keys sorted (as nlohmann's default object does,
 // which is what makes the written header and events come out in alphabetical key order).
 #pragma once
 
 #include <cctype>
+#include <cerrno>
+#include <cstdint>
 #include <cstdio>
 #include <cstdlib>
 #include <map>
@@ -24,6 +27,8 @@ struct Value {
   enum Kind { kNull, kBool, kNumber, kString, kArray, kObject } kind = kNull;
   bool b = false;
   double num = 0.0;
+  uint64_t u64 = 0;        // exact value of a non-negative integer literal
+  bool is_u64 = false;
   std::string str;
   std::shared_ptr<Array> arr;
   std::shared_ptr<Object> obj;
@@ -39,6 +44,11 @@ struct Value {
   double number() const {
     if (kind != kNumber) throw std::runtime_error("json: number expected");
     return num;
+  }
+  // A non-negative integer literal exactly (nlohmann's get<uint64_t>()); other numbers are truncated.
+  uint64_t as_uint64() const {
+    if (kind != kNumber) throw std::runtime_error("json: number expected");
+    return is_u64 ? u64 : static_cast<uint64_t>(num);
   }
   const std::string& string() const {
     if (kind != kString) throw std::runtime_error("json: string expected");
@@ -118,6 +128,16 @@ class Parser {
     Value v;
     v.kind = Value::kNumber;
     v.num = d;
+    bool digits = end > begin;
+    for (const char* c = begin; c < end; ++c) digits = digits && *c >= '0' && *c <= '9';
+    if (digits && end - begin <= 20) {
+      errno = 0;
+      const unsigned long long u = std::strtoull(begin, nullptr, 10);
+      if (errno == 0) {
+        v.u64 = u;
+        v.is_u64 = true;
+      }
+    }
     return v;
   }
   std::string parse_string() {

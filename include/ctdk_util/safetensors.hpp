@@ -63,6 +63,7 @@ class File {
   }
 
   const std::map<std::string, Entry>& entries() const { return entries_; }
+  uint64_t data_origin() const { return origin_; }   // file offset of the data section
   bool has(const std::string& name) const { return entries_.count(name) != 0; }
   const Entry& entry(const std::string& name) const {
     auto it = entries_.find(name);
@@ -94,7 +95,8 @@ struct Item {
   const float* data;   // host pointer, numel floats
 };
 
-inline void save(const std::vector<Item>& items, const std::string& path) {
+// The 8-byte length and the JSON header text of a file holding `items` in this order.
+inline std::string header_bytes(const std::vector<Item>& items) {
   std::map<std::string, std::string> header;   // sorted by name
   uint64_t running = 0;
   for (const Item& it : items) {
@@ -119,13 +121,17 @@ inline void save(const std::vector<Item>& items, const std::string& path) {
   }
   text.push_back('}');
   while (text.size() % 8 != 0) text.push_back(' ');
+  std::string out(8, '\0');
+  const uint64_t hlen = text.size();
+  for (int i = 0; i < 8; ++i) out[i] = static_cast<char>((hlen >> (8 * i)) & 0xFF);
+  return out + text;
+}
+
+inline void save(const std::vector<Item>& items, const std::string& path) {
+  const std::string head = header_bytes(items);
   std::ofstream out(path, std::ios::binary | std::ios::trunc);
   if (!out) throw std::runtime_error("cannot open " + path + " for writing");
-  unsigned char len8[8];
-  uint64_t hlen = text.size();
-  for (int i = 0; i < 8; ++i) len8[i] = static_cast<unsigned char>((hlen >> (8 * i)) & 0xFF);
-  out.write(reinterpret_cast<const char*>(len8), 8);
-  out.write(text.data(), static_cast<std::streamsize>(text.size()));
+  out.write(head.data(), static_cast<std::streamsize>(head.size()));
   for (const Item& it : items) {
     int64_t n = 1;
     for (const int64_t d : it.shape) n *= d;

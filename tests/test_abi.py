@@ -16,7 +16,11 @@ def test_ctypes_signature_table_covers_header():
     special = {"ctdk_last_error", "ctdk_sm_count", "ctdk_rmsnorm_bwd_scratch_floats",
                "ctdk_qk_norm_rope_bwd_scratch_floats", "ctdk_launch_count", "ctdk_prof_enable",
                "ctdk_prof_collect", "ctdk_gemm_3xtf32_workspace_floats"}
-    engine = {n for n in lib.declared_symbols() if n.startswith(("ctdk_engine_", "ctdk_model_", "ctdk_decode_"))}
+    # engine / trainer / decoder entry points are bound in emberlm_b200/engine.py
+    engine = {n for n in lib.declared_symbols()
+              if n.startswith(("ctdk_engine_", "ctdk_model_", "ctdk_decode_", "ctdk_trainer_", "ctdk_dp_", "ctdk_batch_"))}
+    from emberlm_b200 import engine as E
+    assert all(getattr(E._L, n).argtypes is not None for n in engine if n.startswith(("ctdk_trainer_", "ctdk_dp_", "ctdk_batch_")))
     assert set(lib.declared_symbols()) - special - engine - set(lib._SIGS) == set()
 
 

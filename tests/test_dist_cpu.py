@@ -175,3 +175,29 @@ def test_dealing_and_row_weights():
     w = E.row_weights(m, 2, 4)                    # micro-batch 0: 3 ones; micro-batch 1: empty mask
     assert torch.allclose(w[:2][m[:2] > 0], torch.tensor(1.0 / (4 * 3)))
     assert float(w[2:].abs().sum()) == 0.0 and float(w[:2][m[:2] == 0].abs().sum()) == 0.0
+
+
+def test_library_plan_equals_the_python_statement():
+    """ctdk_dp_buckets / ctdk_dp_segments (the C++ trainer's plan, host only) against the Python
+    statement of the same rules above, for the five presets, 1-8 ranks and three bucket sizes."""
+    from emberlm_b200 import engine as E
+    for name in E.PRESETS:
+        cfg = E.make_config(**E.PRESETS[name])
+        lay = E.model_layout(cfg)
+        for world in (1, 2, 4, 8):
+            total = E.padded_total(lay.total, world)
+            assert total == E.lib.raw().ctdk_dp_arena_floats(cfg, world)
+            for per in (0, 1, 4):
+                py = E.make_buckets(lay, total, world, cfg.num_hidden_layers, per)
+                for rank in range(world):
+                    cc = E.dp_plan(cfg, world, rank, per)
+                    assert len(cc) == len(py)
+                    pos = 0
+                    for c, (lo, hi, ready) in zip(cc, py):
+                        a, b = E.bucket_slice(lo, hi, world, rank)
+                        assert (c["lo"], c["hi"], c["ready"], c["a"], c["b"], c["state"]) == (lo, hi, ready, a, b, pos)
+                        pos += b - a
+                        e1, w1 = E.build_segments(lay, 0.01, a, b)
+                        e2, w2 = E.dp_segments(cfg, 0.01, a, b)
+                        assert e1 == e2 and np.allclose(w1, w2, atol=1e-9)
+                    assert pos == total // world
