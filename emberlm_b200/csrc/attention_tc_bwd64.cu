@@ -20,6 +20,7 @@
 // Replaces, with attention_tc.cu, the backward of the bmm -> scale -> mask -> softmax -> bmm chain
 // of the reference's Attention::forward_train (emberlm include/ctd/nn/attention.h:123-141,
 // softmax backward src/ops/softmax.cu:56-93).
+#include <atomic>
 #include <cfloat>
 #include <climits>
 
@@ -870,7 +871,12 @@ int attn_bwd_dq_tc64(const float* qkv, const float* dout, const float* lse, cons
 }
 
 namespace {
-__device__ int g_kv_work_counter;
+// Work counters of the dK/dV kernel: every call takes the next one of a ring and zeroes it in its
+// own stream, so calls on different streams of a device do not draw from each other's sequence.
+// A counter is reused after kKvCounters further calls, long after its kernel has finished.
+constexpr int kKvCounters = 64;
+__device__ int g_kv_work_counter[kKvCounters];
+std::atomic<unsigned> g_kv_counter_next{0};
 }  // namespace
 
 // dK/dV part of the backward for D = 64. Returns CTDK_OK or a negative status.
@@ -896,8 +902,8 @@ int attn_bwd_dkv_tc64(const float* qkv, const float* dout, const float* lse, con
     void* cptr = nullptr;
     if (cudaGetSymbolAddress(&cptr, g_kv_work_counter) != cudaSuccess || cptr == nullptr)
       return fail(CTDK_ELAUNCH, "attn_bwd dkv(tcgen05): no work counter");
-    a.work_counter = static_cast<int*>(cptr);
-    if (cudaMemsetAsync(cptr, 0, sizeof(int), stream) != cudaSuccess)
+    a.work_counter = static_cast<int*>(cptr) + g_kv_counter_next.fetch_add(1, std::memory_order_relaxed) % kKvCounters;
+    if (cudaMemsetAsync(a.work_counter, 0, sizeof(int), stream) != cudaSuccess)
       return fail(CTDK_ELAUNCH, "attn_bwd dkv(tcgen05): counter reset failed");
   }
   CUtensorMap tqk, tdok, tqm, tdom, tkvt;

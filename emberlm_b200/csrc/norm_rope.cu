@@ -8,6 +8,8 @@
 // Differences are in the execution only: one CTA per row with 128-bit accesses and
 // warp-shuffle reductions, dw reduced through per-CTA partial rows instead of one atomic per
 // element, cos/sin from libm-accurate functions instead of the fast intrinsics.
+#include <mutex>
+
 #include "common.cuh"
 
 namespace ctdk {
@@ -640,12 +642,14 @@ static __device__ __align__(256) float g_rmsnorm_static_scratch[kStaticRows * kS
 // Device address of the array, resolved once per device. In host code the array's name is
 // only a handle for cudaGetSymbolAddress, never a pointer a kernel may be given.
 float* g_static_scratch_ptr[64] = {nullptr};
+std::mutex g_static_scratch_mu;   // callers on several host threads may make the first call together
 
 int static_scratch(float** out) {
   int dev = 0;
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess || dev < 0 || dev >= 64)
     return fail(CTDK_ELAUNCH, "ctdk_rmsnorm_bwd_static: no current device");
+  std::lock_guard<std::mutex> lk(g_static_scratch_mu);
   if (g_static_scratch_ptr[dev] == nullptr) {
     float* p = nullptr;
     e = cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_rmsnorm_static_scratch);
