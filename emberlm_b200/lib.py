@@ -85,6 +85,19 @@ _SIGS = {
     "ctdk_clip_scale": [_p, _f, _f, _p, _p, _p],
     "ctdk_adamw": [_p, _p, _p, _p, _l, C.POINTER(AdamWParams), _p, _p, _p, _i, _p],
     "ctdk_device_status": [_p, C.POINTER(C.c_int)],
+    "ctdk_softmax_fwd": [_p, _p, _l, _l, _p],
+    "ctdk_softmax_bwd": [_p, _p, _p, _l, _l, _p],
+    "ctdk_permute": [_p, _p, _i, C.POINTER(C.c_int64), C.POINTER(C.c_int), _p],
+    "ctdk_repeat_kv": [_p, _p, _l, _i, _i, _i, _p],
+    "ctdk_repeat_kv_sum": [_p, _p, _l, _i, _i, _i, _p],
+    "ctdk_causal_mask": [_p, _p, _l, _l, _l, _i, _f, _p],
+    "ctdk_mse_fwd": [_p, _p, _l, _p, _p],
+    "ctdk_mse_bwd": [_p, _p, _p, _p, _l, _p],
+    "ctdk_kv_write": [_p, _p, _l, _l, _i, _i, _l, _l, _p],
+    "ctdk_kv_read_expanded": [_p, _p, _l, _i, _i, _l, _i, _l, _p],
+    "ctdk_loss_ratio": [_p, _p, _p],
+    "ctdk_sample": [_p, _l, _l, _f, _i, _f, _p, _p, _p, _p],
+    "ctdk_ce_row_weight": [_p, _p, _p, _l, _p, _p],
 }
 for _name, _args in _SIGS.items():
     _fn = getattr(_lib, _name)
@@ -100,6 +113,8 @@ _lib.ctdk_prof_enable.argtypes = [C.c_int]
 _lib.ctdk_prof_collect.restype = C.c_int
 _lib.ctdk_prof_collect.argtypes = [C.c_int, C.POINTER(C.c_double), C.POINTER(C.c_double),
                                    C.POINTER(C.c_longlong)]
+_lib.ctdk_sample_workspace_bytes.restype = C.c_int64
+_lib.ctdk_sample_workspace_bytes.argtypes = [C.c_int64, C.c_int64]
 _lib.ctdk_rmsnorm_bwd_scratch_floats.restype = C.c_int64
 _lib.ctdk_rmsnorm_bwd_scratch_floats.argtypes = [C.c_int]
 _lib.ctdk_gemm_3xtf32_workspace_floats.restype = C.c_int64

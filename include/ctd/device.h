@@ -1,0 +1,3 @@
+// Device, DeviceType, kCPU, kCUDA0: see b200/core.hpp (one header per group of the ctd:: surface).
+#pragma once
+#include "b200/core.hpp"

@@ -1,0 +1,3 @@
+// add, sub, mul, scale, silu and their backward: see b200/ops.hpp (one header per group of the ctd:: surface).
+#pragma once
+#include "../b200/ops.hpp"

@@ -1,0 +1,3 @@
+// permute: see b200/ops.hpp (one header per group of the ctd:: surface).
+#pragma once
+#include "../b200/ops.hpp"

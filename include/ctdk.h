@@ -257,6 +257,43 @@ int ctdk_attn_bwd_p(const float* qkv, const float* out, const float* dout, const
                     int precision, void* stream);
 
 /* ------------------------------------------------------------------------------------
+ * Stand-alone ops of the reference's per-op API that the fused training path absorbs (kept for the
+ * public op surface; 64-bit indexing throughout):
+ *   softmax over the last axis and its backward dx = y * (g - sum(g*y))   (src/ops/softmax.cu:18-93)
+ *   permute of up to 6 axes into a new contiguous tensor: out axis i = in axis perm[i]
+ *                                                                         (src/ops/permute.cu:16-60)
+ *   repeat_kv: [rows, Hk, D] -> [rows, Hk*group, D], and the group sum that is its backward
+ *                                                                         (src/ops/repeat_kv.cu:14-43)
+ *   causal mask on [mats, Tq, Tk]: out = (j > q_pos_start + i) ? fill : in; fill = -FLT_MAX forward,
+ *   0 for the backward; in == out is allowed                               (src/ops/mask.cu:17-60)
+ *   mse: loss[0] = mean((pred - target)^2); dpred = 2 (pred - target) / n * dy[0] with dy on the device
+ *                                                                         (src/ops/loss.cu:17-75)
+ *   KV cache: write src [B, T, H, D] into cache [B, H, max_seq, D] at position pos; read the first
+ *   valid_len positions with every KV head repeated `group` times -> [B, H*group, valid_len, D]
+ *                                                                         (src/ops/kv_cache.cu:14-109)
+ *   loss_ratio: out[0] = sums[1] > 0 ? sums[0] / sums[1] : 0 (the masked mean from ctdk_ce_masked's sums)
+ *   ce_row_weight: row_weight[i] = mask[i] * dy[0] / mask_sum[0] (mask NULL: dy[0] / n), the factor of
+ *   CrossEntropy(Masked)Backward built without a host round trip           (src/ops/loss.cu:388-411)
+ * ------------------------------------------------------------------------------------ */
+int ctdk_softmax_fwd(const float* x, float* y, int64_t rows, int64_t width, void* stream);
+int ctdk_softmax_bwd(const float* y, const float* g, float* dx, int64_t rows, int64_t width, void* stream);
+int ctdk_permute(const float* x, float* y, int ndim, const int64_t* shape, const int* perm, void* stream);
+int ctdk_repeat_kv(const float* x, float* y, int64_t rows, int Hk, int D, int group, void* stream);
+int ctdk_repeat_kv_sum(const float* y, float* x, int64_t rows, int Hk, int D, int group, void* stream);
+int ctdk_causal_mask(const float* in, float* out, int64_t mats, int64_t Tq, int64_t Tk, int q_pos_start,
+                     float fill, void* stream);
+int ctdk_mse_fwd(const float* pred, const float* target, int64_t n, float* loss, void* stream);
+int ctdk_mse_bwd(const float* pred, const float* target, const float* dy, float* dpred, int64_t n,
+                 void* stream);
+int ctdk_kv_write(const float* src, float* cache, int64_t B, int64_t T, int H, int D, int64_t max_seq,
+                  int64_t pos, void* stream);
+int ctdk_kv_read_expanded(const float* cache, float* out, int64_t B, int Hk, int group, int64_t valid_len,
+                          int D, int64_t max_seq, void* stream);
+int ctdk_loss_ratio(const float* sums, float* out, void* stream);
+int ctdk_ce_row_weight(const float* loss_mask, const float* dy, const float* mask_sum, int64_t n,
+                       float* row_weight, void* stream);
+
+/* ------------------------------------------------------------------------------------
  * Optimizer. ctdk_sumsq adds sum(g^2) into out[0] (sum_sq_kernel_f32,
  * src/core/optim.cu:221-239). ctdk_adamw is one launch over a flat range of parameters:
  *   g' = g * grad_scale            (clip_grad_norm_'s scale, optim.cu:276-290; read from
@@ -439,6 +476,22 @@ int ctdk_trainer_set_step_count(void* trainer, int64_t n);
  * scatter copies this rank's slices out of an arena-order array at load. */
 int ctdk_trainer_gather_state(void* trainer, const float* shard_state, float* full, void* stream);
 int ctdk_trainer_scatter_state(void* trainer, const float* full, float* shard_state, void* stream);
+
+/* ------------------------------------------------------------------------------------
+ * Token sampling on the device with the semantics of the reference's host sampler
+ * (src/core/sampling.cpp:13-106; include/ctd/sampling.h:11-21): logits fp32 [B, V] on the device;
+ * temperature <= 0 is greedy (first index of the maximum); otherwise logits / temperature, optional
+ * top-k (0 < top_k < V: everything below the k-th largest is dropped, ties at the threshold stay),
+ * softmax, optional top-p (0 < top_p < 1: the largest probabilities in descending order until their
+ * sum reaches top_p, renormalised) and inverse-CDF selection in index order with the draw u[b]: one
+ * std::uniform_real_distribution<double>(0, 1) value per row from the caller's mt19937_64, in row
+ * order, which is the reference's draw order, so a seeded request picks the same tokens. u and
+ * out_tokens are device pointers (u may be NULL for greedy); workspace holds
+ * ctdk_sample_workspace_bytes(B, V) bytes (unused for greedy). Nothing is synchronised.
+ * ------------------------------------------------------------------------------------ */
+int64_t ctdk_sample_workspace_bytes(int64_t B, int64_t V);
+int ctdk_sample(const float* logits, int64_t B, int64_t V, float temperature, int top_k, float top_p,
+                const double* u, void* workspace, int64_t* out_tokens, void* stream);
 
 /* ------------------------------------------------------------------------------------
  * KV-cache greedy decoding, batch 1. Replaces the cached inference path: Model::forward with a

@@ -1,4 +1,4 @@
-// Checks of the C++ `ctd::` mirror (include/ctd_b200.hpp) against plain CPU loops, shaped after
+// Checks of the C++ `ctd::` surface (include/ctd/*.h) against plain CPU loops, shaped after
 // the reference's own gtest cases for these ops (tests/test_matmul.cpp, test_bmm.cpp, test_norm.cpp,
 // test_rope.cpp, test_elementwise.cpp, test_activations.cpp, test_embedding.cpp, test_tensor.cpp and
 // the AdamW / ClipGradNorm / CrossEntropyMasked cases of tests/test_autograd.cpp). There is no gtest
@@ -11,9 +11,24 @@
 #include <string>
 #include <vector>
 
-#include "ctd_b200.hpp"
+#include "ctd/autograd.h"
+#include "ctd/ops/elementwise.h"
+#include "ctd/ops/embedding.h"
+#include "ctd/ops/loss.h"
+#include "ctd/ops/matmul.h"
+#include "ctd/ops/norm.h"
+#include "ctd/ops/repeat_kv.h"
+#include "ctd/ops/rope.h"
+#include "ctd/optim.h"
+#include "ctd/tensor.h"
 
 using namespace ctd;
+
+// Attaches a gradient to a leaf the way the tape would (AccumulateGrad stores the first one).
+static void set_grad(Tensor& p, const Tensor& g) {
+  p.requires_grad_(true);
+  p.mutable_autograd_meta()->grad = g;
+}
 
 namespace {
 
@@ -320,7 +335,9 @@ CASE(CrossEntropyMasked_ForwardAndGradientMatchCpu) {
   std::vector<float> ones(N, 1.0f);
   CHECK_NEAR(host(ops::cross_entropy_masked(Z, T, dev(ones, {N})))[0], ce_cpu(z, t, ones, N, V), 1e-5);
   // gradient against central differences of the CPU loss
-  auto g = host(ops::cross_entropy_masked_backward_impl(Z, T, Mk, 1.0f));
+  Z.requires_grad_(true);
+  ops::cross_entropy_masked(Z, T, Mk).backward();
+  auto g = host(Z.grad());
   for (int probe : {0, 57, 2 * V + 3, 4 * V + static_cast<int>(t[4]), 8 * V + 130}) {
     auto zp = z, zm = z;
     zp[probe] += 1e-2f;
@@ -336,7 +353,8 @@ CASE(CrossEntropyMasked_ZeroSumThrows) {
   auto T = dev_i64(std::vector<int64_t>(N, 1), {N});
   auto Mk = Tensor::zeros({N}, DType::kFloat32, kCUDA0);
   CHECK(host(ops::cross_entropy_masked(Z, T, Mk))[0] == 0.0f);
-  CHECK_THROWS(ops::cross_entropy_masked_backward_impl(Z, T, Mk, 1.0f));
+  Z.requires_grad_(true);
+  CHECK_THROWS(ops::cross_entropy_masked(Z, T, Mk).backward());
 }
 
 // ---------------------------------------------------------------- optimizer
@@ -348,7 +366,7 @@ CASE(AdamW_SingleElementMatchesClosedForm) {
   double pr = p0, m = 0.0, v = 0.0;
   const float grads[3] = {0.5f, -0.25f, 2.0f};
   for (int s = 1; s <= 3; ++s) {
-    p.set_grad(Tensor::from_host(&grads[s - 1], {1}, DType::kFloat32, kCUDA0));
+    set_grad(p, Tensor::from_host(&grads[s - 1], {1}, DType::kFloat32, kCUDA0));
     m = b1 * m + (1 - b1) * grads[s - 1];
     v = b2 * v + (1 - b2) * grads[s - 1] * grads[s - 1];
     const double mh = m / (1 - std::pow(b1, s)), vh = v / (1 - std::pow(b2, s));
@@ -362,15 +380,15 @@ CASE(AdamW_DecoupledWeightDecayWithZeroGrad) {
   auto h = std::vector<float>(8, 2.0f);
   Tensor p = dev(h, {8});
   optim::AdamW opt({p}, 0.5f, 0.1f);
-  p.set_grad(Tensor::zeros({8}, DType::kFloat32, kCUDA0));   // seen by the optimizer's handle too
+  set_grad(p, Tensor::zeros({8}, DType::kFloat32, kCUDA0));   // seen by the optimizer's handle too
   opt.step();
   for (float v : host(p)) CHECK_NEAR(v, 2.0f - 0.5f * 0.1f * 2.0f, 1e-6);   // only the decay term moves it
 }
 CASE(ClipGradNorm_ScalesDownToMaxAndNoOpUnderMax) {
   std::vector<float> g1 = {3.0f, 0.0f, 0.0f}, g2 = {0.0f, 4.0f};
   Tensor p1 = Tensor::zeros({3}, DType::kFloat32, kCUDA0), p2 = Tensor::zeros({2}, DType::kFloat32, kCUDA0);
-  p1.set_grad(dev(g1, {3}));
-  p2.set_grad(dev(g2, {2}));
+  set_grad(p1, dev(g1, {3}));
+  set_grad(p2, dev(g2, {2}));
   const float norm = optim::clip_grad_norm_({p1, p2}, 1.0f);
   CHECK_NEAR(norm, 5.0f, 1e-6);
   auto a = host(p1.grad()), b = host(p2.grad());

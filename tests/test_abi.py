@@ -15,7 +15,7 @@ def test_library_exports_every_declared_symbol():
 def test_ctypes_signature_table_covers_header():
     special = {"ctdk_last_error", "ctdk_sm_count", "ctdk_rmsnorm_bwd_scratch_floats",
                "ctdk_qk_norm_rope_bwd_scratch_floats", "ctdk_launch_count", "ctdk_prof_enable",
-               "ctdk_prof_collect", "ctdk_gemm_3xtf32_workspace_floats"}
+               "ctdk_prof_collect", "ctdk_gemm_3xtf32_workspace_floats", "ctdk_sample_workspace_bytes"}
     # engine / trainer / decoder entry points are bound in emberlm_b200/engine.py
     engine = {n for n in lib.declared_symbols()
               if n.startswith(("ctdk_engine_", "ctdk_model_", "ctdk_decode_", "ctdk_trainer_", "ctdk_dp_", "ctdk_batch_"))}

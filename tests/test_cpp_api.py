@@ -1,4 +1,4 @@
-"""The C++ `ctd::` mirror (include/ctd_b200.hpp, ctd_b200_nn.hpp): it compiles and links against the
+"""The C++ `ctd::` surface (include/ctd/*.h over include/ctd/b200/*.hpp): it compiles and links against the
 C-ABI library on any host; on a B200 the case lists in tests/cpp/ (the reference's op tests, and its
 training-loop idiom against the step engine) run and must pass."""
 import os
@@ -11,7 +11,7 @@ PKG = os.path.join(ROOT, "emberlm_b200")
 CUDA = os.environ.get("CUDA_HOME", "/usr/local/cuda")
 
 
-PROGRAMS = ["test_ctd_api", "test_ctd_train_loop"]
+PROGRAMS = ["test_ctd_api", "test_ctd_train_loop", "test_ctd_autograd"]
 
 
 def _build(tmp_path, name):
