@@ -48,6 +48,18 @@ METRIC = "train tokens/s (fwd+bwd+AdamW)"
 NCU_GEMM_DRAM_BYTES_PER_FLOP = (74.0e6 + 115.7e6) / (2.0 * 16384 * 2560 * 960)
 
 
+def workload_config(name: str) -> dict:
+    """The `config` object both arms print: what the workload is, nothing about how an arm runs it."""
+    preset, rows, S, mb, A, ckpt = WORKLOADS[name]
+    return {"workload": name, "global_batch": rows, "seq_len": S, "positions_per_step": rows * (S - 1), "micro_batch": mb,
+            "grad_accum": A, "gradient_checkpointing": ckpt}
+
+
+def step_rows(vocab: int, rows: int, S: int, step: int):
+    """The documents of step `step` (both arms train on the same rows; four distinct steps, then they repeat)."""
+    return synth_rows(vocab, rows, S, seed=4321 + step % 4)
+
+
 def algorithmic_flops_per_step(cfg: dict, rows: int, T: int) -> float:
     """3 * [2*tok*(P_mat + V*hid) + L*B*H*2*T^2*D]: forward + 2x backward, causal half of the
     attention square, recomputation and masked-row skipping not counted."""
@@ -173,7 +185,8 @@ def run_ours(args) -> dict:
     my_mbs = list(range(rank, A, world))          # micro-batches dealt round-robin
     my_rows = len(my_mbs) * mb
     cfgd = dict(E.PRESETS[preset])
-    cfg = E.make_config(**cfgd, gradient_checkpointing=ckpt)
+    precision = lib.GEMM_3XTF32 if args.precision == "3xtf32" else lib.GEMM_TF32
+    cfg = E.make_config(**cfgd, gradient_checkpointing=ckpt, precision=precision)
     eng = E.TrainEngine(cfg, my_rows, T, device=f"cuda:{local}", group=group, **HP)
     eng.init_parameters(seed=1234)
 
@@ -185,7 +198,7 @@ def run_ours(args) -> dict:
     L_.ctdk_prof_collect.argtypes = [C.c_int, C.POINTER(C.c_double), C.POINTER(C.c_double), C.POINTER(C.c_longlong)]
 
     def host_batch(step):
-        tok, msk = synth_rows(cfgd["vocab_size"], rows, S, seed=4321 + step)
+        tok, msk = step_rows(cfgd["vocab_size"], rows, S, step)
         sel = np.concatenate([np.arange(j * mb, (j + 1) * mb) for j in my_mbs])
         return tok[sel], msk[sel]
 
@@ -194,9 +207,16 @@ def run_ours(args) -> dict:
     pinned_act = [torch.empty(my_rows * T, dtype=torch.int32).pin_memory() for _ in range(2)]
     host = [host_batch(s) for s in range(min(n_steps, 4))]
 
-    def to_device(step, slot):
-        """H2D of one step's rows (int32 tokens + int8 masks) and on-device widening to what the
-        engine takes (int64 ids/targets, fp32 mask, per-row weights)."""
+    dev = torch.device(f"cuda:{local}")
+    d_bufs = [dict(ids=torch.empty((my_rows, T), dtype=torch.int64, device=dev), tgt=torch.empty((my_rows, T), dtype=torch.int64, device=dev),
+                   mask=torch.empty((my_rows, T), dtype=torch.float32, device=dev), w=torch.empty((my_rows, T), dtype=torch.float32, device=dev),
+                   sums=torch.empty(len(my_mbs) + 1, dtype=torch.float32, device=dev)) for _ in range(max(2, len(host)))]
+
+    def to_device(step, slot, keep=None):
+        """One step's rows as they lie in the bins (int32 tokens, int8 masks: 5 bytes per token) and the
+        supervised positions from pinned host memory to the device, then widened there by the library
+        (ctdk_batch_widen: int64 ids / targets, fp32 mask, per-row weights). keep: index of a private
+        set of output buffers (the device-resident arm keeps one per step); None = slot's."""
         t, m = host[step % len(host)]
         pinned_tok[slot].copy_(torch.from_numpy(t))
         pinned_msk[slot].copy_(torch.from_numpy(m))
@@ -205,11 +225,11 @@ def run_ours(args) -> dict:
         d_tok = pinned_tok[slot].cuda(non_blocking=True)
         d_msk = pinned_msk[slot].cuda(non_blocking=True)
         d_act = pinned_act[slot][:act.size].cuda(non_blocking=True)
-        ids = d_tok[:, :-1].to(torch.int64).contiguous()
-        tgt = d_tok[:, 1:].to(torch.int64).contiguous()
-        mask = d_msk[:, 1:].to(torch.float32).contiguous()
-        w = E.row_weights(mask, mb, A)
-        return ids, tgt, mask, w, d_act
+        b = d_bufs[slot if keep is None else keep]
+        lib.check(L_.ctdk_batch_widen(d_tok.data_ptr(), d_msk.data_ptr(), my_rows, S, mb, A, b["ids"].data_ptr(), b["tgt"].data_ptr(),
+                                      b["mask"].data_ptr(), b["w"].data_ptr(), b["sums"].data_ptr(),
+                                      torch.cuda.current_stream().cuda_stream))
+        return b["ids"], b["tgt"], b["mask"], b["w"], d_act
 
     def barrier():
         if world > 1:
@@ -230,7 +250,7 @@ def run_ours(args) -> dict:
         return float(ms)
 
     # ---- device-resident arm ------------------------------------------------------------
-    resident = [to_device(s, s % 2) for s in range(len(host))]
+    resident = [to_device(s, s % 2, keep=s) for s in range(len(host))]
     torch.cuda.synchronize()
 
     def step_resident(s):
@@ -254,7 +274,7 @@ def run_ours(args) -> dict:
     L_.ctdk_prof_enable(0)
     clocks = sampler.stop() if sampler else None
     prof = {}
-    for name, cls in (("gemm", 0), ("attn", 1), ("adamw", 2), ("norm", 3)):
+    for name, cls in (("gemm", 0), ("attn", 1), ("adamw", 2), ("norm", 3), ("norm_bwd", 4), ("qk_norm_rope", 5), ("ce", 6), ("embedding", 7)):
         a, b, n = C.c_double(), C.c_double(), C.c_longlong()
         L_.ctdk_prof_collect(cls, C.byref(a), C.byref(b), C.byref(n))
         prof[name] = (a.value, b.value, n.value)
@@ -283,13 +303,15 @@ def run_ours(args) -> dict:
     out = {
         "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms_total / args.steps, "higher_is_better": True,
-        "scaling": "strong", "vs_baseline": None, "dtype": "tf32 (fp32 storage, fp32 accumulate)",
+        "scaling": "strong", "vs_baseline": None, "dtype": ("3xtf32" if args.precision == "3xtf32" else "tf32") + " (fp32 storage, fp32 accumulate)",
         "data": "synthetic", "impl": "ours",
-        "config": {"workload": args.workload, "global_batch": rows, "seq_len": S, "positions_per_step": positions,
-                   "micro_batch": mb, "grad_accum": A, "parallelism": f"dp{world}+zero1",
-                   "gradient_checkpointing": ckpt, "supervised_positions_per_rank": act_mean,
-                   "lm_head": "supervised rows only (masked rows have zero loss and gradient)", "l2": "inputs larger than L2 (activations of several GB per step)",
-                   "algorithmic_tflop_per_step": flops_step / 1e12},
+        "config": workload_config(args.workload),
+        "notes": {"parallelism": f"dp{world}+zero1 (C++ trainer in libctdk.so, NCCL reduce-scatter / all-gather per bucket)",
+                  "precision": args.precision, "supervised_positions_per_rank": act_mean,
+                  "lm_head": "supervised rows only (masked rows have zero loss and gradient)",
+                  "l2": "inputs larger than L2 (activations of several GB per step)",
+                  "algorithmic_tflop_per_step": flops_step / 1e12,
+                  "workspace_gib_per_rank": eng.workspace.numel() / 2**30},
         "step_tflops_per_gpu": flops_step / (ms_total / args.steps / 1e3) / 1e12 / world,
         "step_frac_of_tf32_peak": flops_step / (ms_total / args.steps / 1e3) / 1e12 / world / tf32_peak,
         "loss": metrics["loss"], "grad_norm": metrics["grad_norm"],
@@ -310,13 +332,62 @@ def run_ours(args) -> dict:
                                        "scaled to the average launch by FLOPs"},
         "kernel_classes": {k: {"ms_per_step": v[0] / args.steps, "launches_per_step": v[2] / args.steps,
                                "achieved": (v[1] / (v[0] / 1e3) / (1e12 if k in ("gemm", "attn") else 1e9)) if v[0] > 0 else None,
-                               "unit": "TFLOP/s" if k in ("gemm", "attn") else "GB/s"} for k, v in prof.items()},
+                               "unit": "TFLOP/s" if k in ("gemm", "attn") else "GB/s",
+                               "frac_of_measured_peak": (v[1] / (v[0] / 1e3) / 1e12 / tf32_peak if k in ("gemm", "attn")
+                                                         else v[1] / (v[0] / 1e3) / 1e9 / peaks["hbm_gbs"]) if v[0] > 0 else None}
+                           for k, v in prof.items()},
     }
+    if args.rank_invariance and world > 1:
+        out["rank_invariance"] = rank_invariance(E, eng, cfg, cfgd, rows, S, mb, A, my_mbs, rank, world, dev)
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         out["cpu_baseline"] = cpu_baseline(preset)
     if world > 1:
         dist.destroy_process_group()
     return out if rank == 0 else None
+
+
+def rank_invariance(E, eng, cfg, cfgd, rows, S, mb, A, my_mbs, rank, world, dev) -> dict | None:
+    """One optimizer step from identical weights on all ranks (data-parallel) and on rank 0 alone (every
+    micro-batch in one pass): the updated weights must agree per tensor up to summation order.
+    Reported as max|a-b| / max|b| per tensor; the worst one is named."""
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+    T = S - 1
+    tok, msk = step_rows(cfgd["vocab_size"], rows, S, 0)
+
+    def device_batch(sel, engine):
+        t = torch.from_numpy(tok[sel]).to(dev)
+        m = torch.from_numpy(msk[sel]).to(dev)
+        ids, tgt = t[:, :-1].to(torch.int64).contiguous(), t[:, 1:].to(torch.int64).contiguous()
+        mask = m[:, 1:].to(torch.float32).contiguous()
+        return ids, tgt, mask, E.row_weights(mask, mb, A)
+
+    eng.init_parameters(seed=99)
+    eng.m.zero_(); eng.v.zero_(); eng.step_count = 0
+    sel = np.concatenate([np.arange(j * mb, (j + 1) * mb) for j in my_mbs])
+    eng.train_step(*device_batch(sel, eng))
+    eng.read_metrics()
+    got = eng.params.clone()
+    dist.barrier()
+    if rank != 0:
+        return None
+    solo = E.TrainEngine(cfg, rows, T, device=str(dev), **HP)
+    solo.init_parameters(seed=99)
+    solo.train_step(*device_batch(np.arange(rows), solo))
+    solo.read_metrics()
+    worst, worst_name, over = 0.0, "", 0
+    lay = solo.layout
+    for n, o, k in zip(lay.names, lay.offsets, lay.numels):
+        a, b = got[o:o + k], solo.params[o:o + k]
+        e = float((a - b).abs().max() / b.abs().max().clamp_min(1e-30))
+        over += e > 1e-5
+        if e > worst:
+            worst, worst_name = e, n
+    return {"ranks": world, "tensors": len(lay.names), "worst_tensor": worst_name, "worst_max_rel_err": worst,
+            "tensors_above_1e-5": int(over),
+            "note": "one AdamW step from identical weights, all ranks vs rank 0 alone; differences come from the order of the "
+                    "gradient sums (reduce-scatter, split-K) and AdamW's sign-like first step on near-zero gradients (<= 2*lr)"}
 
 
 def cpu_baseline(preset: str) -> dict:
@@ -353,7 +424,8 @@ def run_reference(args) -> dict | None:
     cfg = om.PRESETS[preset]
     params = om.init_params(cfg, seed=1234)
     n_steps = args.warmup + args.steps
-    tok, msk = om.synth_batch(cfg.vocab_size, rows * min(n_steps, 4), S, seed=4321)
+    parts = [step_rows(cfg.vocab_size, rows, S, st) for st in range(min(n_steps, 4))]    # the rows of the other arm
+    tok, msk = np.concatenate([p_[0] for p_ in parts]), np.concatenate([p_[1] for p_ in parts])
     t0 = time.perf_counter()
     try:
         r = ref_run.run_reference(cfg, params, tok, msk, mb, A, steps=args.steps, warmup=args.warmup,
@@ -366,9 +438,8 @@ def run_reference(args) -> dict | None:
     return {**base, "value": value, "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": ms / args.steps, "scaling": "strong", "vs_baseline": None,
             "dtype": "fp32 (cuBLAS SGEMM, default math mode)", "data": "synthetic",
-            "config": {"workload": args.workload, "global_batch": rows, "seq_len": S, "positions_per_step": positions,
-                       "micro_batch": mb, "grad_accum": A, "parallelism": "single GPU (the reference has no DP)",
-                       "gradient_checkpointing": ckpt},
+            "config": workload_config(args.workload),
+            "notes": {"parallelism": "single GPU (the reference has no data parallelism)"},
             "loss": r["loss"][-1], "grad_norm": r["grad_norm"][-1],
             "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": 0, "kind": "reference",
                              "sample": "the reference's own CUDA build on one B200 (it has no CPU path); "
@@ -435,6 +506,11 @@ def main():
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--workload", choices=sorted(WORKLOADS) + ["qwen3_0_6b_decode"], default=DEFAULT_WORKLOAD)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--precision", choices=["tf32", "3xtf32"], default="tf32",
+                    help="3xtf32: every contraction splits its operands into TF32 high and low parts (near-fp32 results)")
+    ap.add_argument("--rank-invariance", action="store_true",
+                    help="after the timing, one step from identical weights on all ranks and on rank 0 alone: per-tensor "
+                         "difference of the updated weights (needs room for the whole batch on rank 0)")
     args = ap.parse_args()
     if args.warmup < 3 and args.impl == "ours":
         print(f"note: --warmup {args.warmup} < 3; timing rules ask for at least 3", file=sys.stderr)

@@ -12,7 +12,7 @@
 // index of the maximum, otherwise temperature, top-k threshold, softmax, top-p nucleus and one
 // uniform draw from mt19937_64(seed). Greedy requests without a thinking budget run on the device
 // in chunks (ctdk_decode_greedy: one CUDA graph launch per token); everything else feeds one chosen
-// token at a time (ctdk_decode_step) and samples on the host from the copied-back logits.
+// token at a time (ctdk_decode_step) and samples on the device (ctdk_sample), one draw per token.
 #include <algorithm>
 #include <chrono>
 #include <cmath>
@@ -50,58 +50,6 @@ struct Sampler {
   int top_k = 0;
   float top_p = 0.0f;
 };
-
-int64_t sample_row(const std::vector<float>& row, const Sampler& cfg, std::mt19937_64& rng) {
-  const int64_t V = static_cast<int64_t>(row.size());
-  if (cfg.temperature <= 0.0f) return std::max_element(row.begin(), row.end()) - row.begin();   // first maximum
-  std::vector<float> p(row);
-  const float inv_t = 1.0f / cfg.temperature;
-  for (auto& x : p) x *= inv_t;
-  if (cfg.top_k > 0 && cfg.top_k < V) {
-    std::vector<float> sorted(p);
-    std::nth_element(sorted.begin(), sorted.begin() + (cfg.top_k - 1), sorted.end(), std::greater<float>());
-    const float thresh = sorted[cfg.top_k - 1];
-    for (auto& x : p)
-      if (x < thresh) x = -std::numeric_limits<float>::infinity();
-  }
-  const float m = *std::max_element(p.begin(), p.end());
-  double s = 0.0;
-  for (auto& x : p) {
-    x = std::exp(x - m);
-    s += x;
-  }
-  const float inv = static_cast<float>(1.0 / s);
-  for (auto& x : p) x *= inv;
-  if (cfg.top_p > 0.0f && cfg.top_p < 1.0f) {
-    std::vector<int64_t> idx(V);
-    std::iota(idx.begin(), idx.end(), 0);
-    std::sort(idx.begin(), idx.end(), [&](int64_t a, int64_t b) { return p[a] > p[b]; });
-    std::vector<char> keep(V, 0);
-    double cum = 0.0;
-    for (int64_t i = 0; i < V; ++i) {
-      cum += p[idx[i]];
-      keep[idx[i]] = 1;
-      if (cum >= cfg.top_p) break;
-    }
-    double kept = 0.0;
-    for (int64_t i = 0; i < V; ++i) {
-      if (!keep[i]) p[i] = 0.0f;
-      kept += p[i];
-    }
-    if (kept > 0.0) {
-      const float k = static_cast<float>(1.0 / kept);
-      for (auto& x : p) x *= k;
-    }
-  }
-  std::uniform_real_distribution<double> U(0.0, 1.0);
-  const double r = U(rng);
-  double c = 0.0;
-  for (int64_t i = 0; i < V; ++i) {
-    c += p[i];
-    if (r < c) return i;
-  }
-  return V - 1;
-}
 
 std::vector<int64_t> id_list(const minijson::Value& req, const char* key) {
   std::vector<int64_t> out;
@@ -229,9 +177,17 @@ int main(int argc, char** argv) try {
       }
     }
   } else {
-    std::vector<float> logits(static_cast<size_t>(V));
+    // Sampling on the device (ctdk_sample: the reference sampler's semantics and draw order): the
+    // uniform draw goes there, the token id comes back; the V logits never leave the GPU.
     const float* d_logits = nullptr;
     CTDK_OK_OR_THROW(ctdk_decode_logits(dec, &d_logits));
+    void* d_sample_ws = nullptr;
+    double* d_u = nullptr;
+    int64_t* d_tok = nullptr;
+    CUDA_OK(cudaMalloc(&d_sample_ws, static_cast<size_t>(ctdk_sample_workspace_bytes(1, V))));
+    CUDA_OK(cudaMalloc(reinterpret_cast<void**>(&d_u), sizeof(double)));
+    CUDA_OK(cudaMalloc(reinterpret_cast<void**>(&d_tok), sizeof(int64_t)));
+    std::uniform_real_distribution<double> uniform(0.0, 1.0);
     std::vector<int64_t> window, force_queue;
     bool in_think = false;
     int think_tokens = 0;
@@ -246,9 +202,11 @@ int main(int argc, char** argv) try {
         tok = force_queue.front();
         force_queue.erase(force_queue.begin());
       } else {
-        CUDA_OK(cudaMemcpyAsync(logits.data(), d_logits, static_cast<size_t>(V) * sizeof(float), cudaMemcpyDeviceToHost, stream));
+        const double u = sampler.temperature > 0.0f ? uniform(rng) : 0.0;   // greedy takes no draw (sampling.cpp:33)
+        CUDA_OK(cudaMemcpyAsync(d_u, &u, sizeof u, cudaMemcpyHostToDevice, stream));
+        CTDK_OK_OR_THROW(ctdk_sample(d_logits, 1, V, sampler.temperature, sampler.top_k, sampler.top_p, d_u, d_sample_ws, d_tok, stream));
+        CUDA_OK(cudaMemcpyAsync(&tok, d_tok, sizeof tok, cudaMemcpyDeviceToHost, stream));
         CUDA_OK(cudaStreamSynchronize(stream));
-        tok = sample_row(logits, sampler, rng);
       }
       emit(minijson::Line().add("token", static_cast<long long>(tok)).dump());
       ++generated;
@@ -277,6 +235,9 @@ int main(int argc, char** argv) try {
       ++fed;
     }
     CUDA_OK(cudaStreamSynchronize(stream));
+    cudaFree(d_sample_ws);
+    cudaFree(d_u);
+    cudaFree(d_tok);
   }
   const double decode_s = std::chrono::duration<double>(std::chrono::steady_clock::now() - t2).count();
   std::cerr << "[ctd_generate] generated " << generated << " tok in " << decode_s << " s  ("

@@ -239,8 +239,10 @@ int ctdk_embedding_fwd(const int64_t* ids, const float* W, float* out, int64_t r
   const int vec = (H % 4 == 0) && aligned16(W) && aligned16(out);
   const int64_t cap = static_cast<int64_t>(sm_count()) * 8;
   const int64_t need = (rows + 7) / 8;
+  void* prof = prof_begin(CTDK_PROF_EMBED, 8.0 * static_cast<double>(rows) * H, static_cast<cudaStream_t>(stream));
   embedding_fwd_kernel<<<static_cast<int>(need < cap ? need : cap), 256, 0,
                          static_cast<cudaStream_t>(stream)>>>(ids, W, out, rows, H, V, vec, st);
+  prof_end(prof, static_cast<cudaStream_t>(stream));
   return check_launch("ctdk_embedding_fwd");
 }
 
@@ -253,8 +255,10 @@ int ctdk_embedding_bwd(const int64_t* ids, const float* dy, float* dW, int64_t r
   CTDK_REQUIRE(st != nullptr, "ctdk_embedding_bwd: no status word");
   const int64_t cap = static_cast<int64_t>(sm_count()) * 8;
   const int64_t need = (rows + 7) / 8;
+  void* prof = prof_begin(CTDK_PROF_EMBED, 12.0 * static_cast<double>(rows) * H, static_cast<cudaStream_t>(stream));
   embedding_bwd_kernel<<<static_cast<int>(need < cap ? need : cap), 256, 0,
                          static_cast<cudaStream_t>(stream)>>>(ids, dy, dW, rows, H, V, st);
+  prof_end(prof, static_cast<cudaStream_t>(stream));
   return check_launch("ctdk_embedding_bwd");
 }
 
@@ -297,9 +301,13 @@ int ctdk_ce_masked(float* logits, const int64_t* targets, const float* loss_mask
   CTDK_REQUIRE(!dlogits_inplace || row_weight, "ctdk_ce_masked: row_weight required");
   const int vec = (V % 4 == 0) && aligned16(logits);
   const int64_t cap = static_cast<int64_t>(sm_count()) * 4;
+  // one read of every logit, one rewrite when the block becomes dlogits (all rows counted: the
+  // engine compacts the supervised rows before the head, so every row of a block is live)
+  void* prof = prof_begin(CTDK_PROF_CE, (dlogits_inplace ? 8.0 : 4.0) * static_cast<double>(n) * V, static_cast<cudaStream_t>(stream));
   ce_masked_kernel<<<static_cast<int>(n < cap ? n : cap), 512, 0,
                      static_cast<cudaStream_t>(stream)>>>(
       logits, targets, loss_mask, row_weight, loss_sum, lse_out, n, V, dlogits_inplace, vec);
+  prof_end(prof, static_cast<cudaStream_t>(stream));
   return check_launch("ctdk_ce_masked");
 }
 

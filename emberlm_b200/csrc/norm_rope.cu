@@ -587,6 +587,7 @@ int ctdk_rmsnorm_bwd(const float* dy, const float* x, const float* w, float* dx,
     return CTDK_OK;
   }
   CTDK_REQUIRE(dy && x && w && dx, "ctdk_rmsnorm_bwd: null pointer");
+  void* prof = prof_begin(CTDK_PROF_NORM_BWD, (add_to_dx ? 16.0 : 12.0) * static_cast<double>(rows) * H, s);
   int64_t cap = static_cast<int64_t>(sm_count()) * 8;
   if (cap > kNormPartialRows) cap = kNormPartialRows;
   const int grid = static_cast<int>(rows < cap ? rows : cap);
@@ -618,6 +619,7 @@ int ctdk_rmsnorm_bwd(const float* dy, const float* x, const float* w, float* dx,
   int rc = check_launch("ctdk_rmsnorm_bwd");
   if (rc != CTDK_OK) return rc;
   launch_pdl(dw_finalize_wide_kernel, dim3(ceil_div(H, 32)), dim3(1024), 0, s, dw_scratch, dw, grid, H, accumulate_dw);
+  prof_end(prof, s);
   return check_launch("ctdk_rmsnorm_bwd(finalize)");
 }
 
@@ -761,12 +763,15 @@ int ctdk_qk_norm_rope_fwd(const float* qkv, float* qkv_out, const float* wq, con
   const int grid = static_cast<int>(need < cap ? need : cap);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const float2* tb = reinterpret_cast<const float2*>(rope_table);
+  // q and k are read and written; v is copied only when the result goes to a second buffer
+  void* prof = prof_begin(CTDK_PROF_QKROPE, 8.0 * static_cast<double>(rows) * D * (H + Hk + (qkv_out != qkv ? Hk : 0)), s);
   if (D == 64)
     launch_pdl(qk_norm_rope_fwd_kernel<1>, dim3(grid), dim3(256), 0, s, qkv, qkv_out, wq, wk, rstd_q, rstd_k, tb, rows, T, H,
                Hk, eps);
   else
     launch_pdl(qk_norm_rope_fwd_kernel<2>, dim3(grid), dim3(256), 0, s, qkv, qkv_out, wq, wk, rstd_q, rstd_k, tb, rows, T, H,
                Hk, eps);
+  prof_end(prof, s);
   return check_launch("ctdk_qk_norm_rope_fwd");
 }
 
@@ -804,6 +809,8 @@ int ctdk_qk_norm_rope_bwd(float* dqkv, const float* qkv_pre, const float* wq, co
   const int64_t need = (items + per_cta - 1) / per_cta;
   const int grid = static_cast<int>(need < cap ? need : cap);
   const float2* tb = reinterpret_cast<const float2*>(rope_table);
+  // d(q), d(k) read and written in place; with QK-Norm the saved pre-norm q / k are read as well
+  void* prof = prof_begin(CTDK_PROF_QKROPE, (has_norm ? 12.0 : 8.0) * static_cast<double>(rows) * D * (H + Hk), s);
   if (D == 64)
     launch_pdl(qk_norm_rope_bwd_kernel<1>, dim3(grid), dim3(256), 0, s, dqkv, qkv_pre, wq, wk, rstd_q, rstd_k, scratch, tb,
                rows, T, H, Hk);
@@ -811,9 +818,13 @@ int ctdk_qk_norm_rope_bwd(float* dqkv, const float* qkv_pre, const float* wq, co
     launch_pdl(qk_norm_rope_bwd_kernel<2>, dim3(grid), dim3(256), 0, s, dqkv, qkv_pre, wq, wk, rstd_q, rstd_k, scratch, tb,
                rows, T, H, Hk);
   int rc = check_launch("ctdk_qk_norm_rope_bwd");
-  if (rc != CTDK_OK || !has_norm) return rc;
+  if (rc != CTDK_OK || !has_norm) {
+    prof_end(prof, s);
+    return rc;
+  }
   qk_dw_finalize_kernel<<<ceil_div(2 * D, 128), 128, 0, s>>>(scratch, dwq, dwk, grid, D,
                                                              accumulate_dw);
+  prof_end(prof, s);
   return check_launch("ctdk_qk_norm_rope_bwd(finalize)");
 }
 

@@ -45,7 +45,11 @@ long long ctdk_launch_count(void);
 #define CTDK_PROF_GEMM 0
 #define CTDK_PROF_ATTN 1
 #define CTDK_PROF_ADAMW 2
-#define CTDK_PROF_NORM 3
+#define CTDK_PROF_NORM 3      /* RMSNorm forward: 8 B per element */
+#define CTDK_PROF_NORM_BWD 4  /* RMSNorm backward incl. the dw column sums: 12 B per element (+ 4 when it adds into dx) */
+#define CTDK_PROF_QKROPE 5    /* fused QK-Norm + RoPE, forward and backward: 8 B per q / k element (+ v copy when out of place) */
+#define CTDK_PROF_CE 6        /* masked cross-entropy on a logits block: 8 B per logit of a supervised row */
+#define CTDK_PROF_EMBED 7     /* embedding gather / scatter-add: 8 B / 12 B per element */
 int ctdk_prof_enable(int on);
 int ctdk_prof_collect(int cls, double* total_ms, double* total_work, long long* launches);
 

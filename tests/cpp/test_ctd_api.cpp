@@ -362,6 +362,7 @@ CASE(AdamW_SingleElementMatchesClosedForm) {
   const float lr = 0.1f, b1 = 0.9f, b2 = 0.95f, eps = 1e-8f, wd = 0.01f;
   float p0 = 1.5f;
   Tensor p = Tensor::from_host(&p0, {1}, DType::kFloat32, kCUDA0);
+  p.requires_grad_(true);   // before the optimizer copies the handle: copies share the gradient slot from here on
   optim::AdamW opt({p}, lr, wd, b1, b2, eps);
   double pr = p0, m = 0.0, v = 0.0;
   const float grads[3] = {0.5f, -0.25f, 2.0f};
@@ -379,6 +380,7 @@ CASE(AdamW_SingleElementMatchesClosedForm) {
 CASE(AdamW_DecoupledWeightDecayWithZeroGrad) {
   auto h = std::vector<float>(8, 2.0f);
   Tensor p = dev(h, {8});
+  p.requires_grad_(true);
   optim::AdamW opt({p}, 0.5f, 0.1f);
   set_grad(p, Tensor::zeros({8}, DType::kFloat32, kCUDA0));   // seen by the optimizer's handle too
   opt.step();

@@ -1,8 +1,11 @@
 """Stream ordering inside the step engine and the attention backward:
   - the weight-gradient GEMMs run on a side stream by default; with CTDK_ENGINE_SIDE_STREAM=0
-    everything stays on the caller's stream. Both schedules must give bit-identical gradients
-    (a missed wait would show up as a difference on some run), with and without accumulation and
-    checkpointing; checked at a size whose kernels take long enough to overlap;
+    everything stays on the caller's stream. Both schedules must give the same gradients, with
+    and without accumulation and checkpointing, at a size whose kernels take long enough to
+    overlap. "The same" is measured against what one schedule does from run to run: GEMMs split
+    into more than two k-ranges add their parts at L2 in arrival order, so two runs of ONE
+    schedule already differ in the last bits of the head's d(hidden), which TF32 rounding then
+    amplifies down the layers; a missed wait would show up far above that;
   - the layer callback contract: when cb(l) fires, everything that writes layer l's gradients is
     ordered before the caller's stream, so a copy issued on a second stream behind an event
     recorded there must see the final values;
@@ -55,16 +58,22 @@ np.savez(out, **{k: v.cpu().numpy() for k, v in g.items() if k != "model.embed_t
 @pytest.mark.parametrize("ckpt,accumulate", [(0, 0), (1, 0), (0, 1), (1, 1)])
 def test_side_stream_schedule_is_bit_identical_to_one_stream(tmp_path, ckpt, accumulate):
     outs = []
-    for side in ("1", "0"):
-        out = tmp_path / f"g{side}.npz"
+    for i, side in enumerate(("0", "0", "1")):      # one stream twice (the run-to-run floor), then the side stream
+        out = tmp_path / f"g{i}.npz"
         env = dict(os.environ, CTDK_ENGINE_SIDE_STREAM=side)
         r = subprocess.run([sys.executable, "-c", _CHILD, str(ROOT), str(ckpt), str(accumulate), str(out)], env=env,
                            capture_output=True, text=True, timeout=600)
         assert r.returncode == 0, r.stderr[-2000:]
         outs.append(np.load(out))
+
+    def err(a, b):
+        return float(np.abs(a - b).max() / max(np.abs(b).max(), 1e-30))
+
     # (the tied embedding's gradient takes float atomics from the scatter-add: left out above)
-    for k in outs[0].files:
-        assert np.array_equal(outs[0][k], outs[1][k]), k
+    floor = max(err(outs[1][k], outs[0][k]) for k in outs[0].files)
+    worst = max((err(outs[2][k], outs[0][k]), k) for k in outs[0].files)
+    print(f"run-to-run {floor:.2e}, side stream vs one stream {worst[0]:.2e} ({worst[1]})")
+    assert worst[0] <= max(4 * floor, 1e-6), (worst, floor)
 
 
 def test_layer_callback_sees_final_gradients():
