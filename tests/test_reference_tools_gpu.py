@@ -151,7 +151,10 @@ def test_three_generators_emit_the_same_seeded_stream(workspace):
             assert got[w][1] == got["ref"][1], (w, req)
             a, b = got[w][0], got["ref"][0]
             first = next((i for i in range(len(b)) if a[i] != b[i]), None)
-            assert first is None or abs(a[first] - b[first]) <= 2, (w, req, first, a, b)
+            # (with top_k = 50 only fifty boundaries exist, a thousand times fewer chances to sit on one,
+            # and the neighbouring survivor can be any id: those streams must simply be equal)
+            near = 0 if "top_k" in req else 3
+            assert first is None or abs(a[first] - b[first]) <= near, (w, req, first, a, b)
     # protocol corners on every build: empty prompt, the cache limit
     for w in GENERATORS:
         r = subprocess.run([str(GENERATORS[w]), "--model", str(w0)], input=json.dumps(dict(input_ids=[])), capture_output=True, text=True,
