@@ -15,6 +15,9 @@
 #include <new>
 #include <vector>
 
+#include <algorithm>
+#include <cstdlib>
+
 #include "common.cuh"
 
 namespace ctdk {
@@ -329,6 +332,451 @@ __global__ void set_counters_kernel(int* pos, int* count, int p, int c) {
   *reinterpret_cast<unsigned long long*>(pos + 4) = 0ull;   // the argmax word lives behind the counters
 }
 
+
+// ----------------------------------------------------------------------------------------
+// Persistent token loop. The kernel-per-phase path above spends most of a token in the ~200
+// launch-to-launch dependencies (each kernel streams 8-25 MB of weights in 2-4 us but waits ~8 us
+// for its predecessor to drain). Here ONE cooperative kernel generates all the requested tokens:
+// its CTAs stay resident, every phase of a layer is a grid-stride loop over weight rows, and the
+// phases are separated by a grid barrier (an atomic counter in global memory, ~2 us) instead of a
+// kernel boundary. While a CTA waits at a barrier, the weight rows of its next phase are already on
+// their way into L2 (prefetch.global.L2), so the HBM stream of phase p+1 overlaps the barrier of
+// phase p. Every wait is bounded: a barrier that does not complete within the budget sets the
+// device status word, and every CTA leaves at its next barrier.
+//   per layer: [RMSNorm + QKV rows] | [QK-Norm + RoPE + cache write + split attention + merge]
+//              | [O rows + residual] | [RMSNorm + gate|up rows] | [SwiGLU + down rows + residual]
+//   per token: ... | [RMSNorm + LM-head rows + arg-max]
+// ----------------------------------------------------------------------------------------
+constexpr int kSyncWords = 256;   // uint32: [0] barrier count, [2] abort flag, [8..8+H) head arrivals, [128..131] two 64-bit argmax words
+constexpr int kMaxPersistLayers = 40;
+constexpr int kPersistSplits = 16;  // key ranges per head in the persistent kernel (the partial buffer is sized for these)
+
+struct PLayer {
+  int64_t w_in, wq, wo, wqn, wkn, w_post, wg, wd;
+};
+struct PersistArgs {
+  const float* P;
+  PLayer lw[kMaxPersistLayers];
+  int64_t embed, norm;
+  int L, hid, I, D, H, Hk, V, QKVN, max_seq;
+  int qk_norm;
+  float eps, scale;
+  const float2* table;
+  float *kcache, *vcache, *x, *qkv, *attn, *hm, *gu, *logits, *attn_part;
+  int64_t* cur_token;
+  int* counters;
+  unsigned int* sync;
+  int64_t* out_tokens;
+  int out_offset, n_tokens;
+  int* status;
+};
+
+__device__ __forceinline__ unsigned int ld_acquire_u32(const unsigned int* p) {
+  unsigned int v;
+  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void prefetch_l2(const void* p) { asm volatile("prefetch.global.L2 [%0];" ::"l"(p)); }
+
+// All CTAs of the grid meet here: one release reduction on a counter per CTA (no value comes back,
+// so the arriving thread does not wait for it; the CTA's earlier writes are ordered before it by
+// the bar.sync and the release), then one thread per CTA polls the counter. A flag per CTA watched
+// by every other CTA measured twice as slow (all pollers hit the same few L2 lines). `epoch` counts
+// the barriers this CTA has passed. Returns false once any CTA has given up (the abort flag is
+// set): the caller unwinds.
+__device__ __forceinline__ bool grid_barrier(const PersistArgs& a, unsigned int& epoch) {
+  __shared__ int s_ok;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    ++epoch;
+    const unsigned int target = epoch * gridDim.x;
+    asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(&a.sync[0]) : "memory");
+    int ok = 1;
+    if (ld_acquire_u32(&a.sync[0]) < target) {
+      const uint64_t t0 = globaltimer_ns();
+      unsigned int spins = 0;
+      while (ld_acquire_u32(&a.sync[0]) < target) {
+        if ((++spins & 0xffu) == 0u) {
+          if (ld_acquire_u32(&a.sync[2]) != 0u) {   // someone else gave up
+            ok = 0;
+            break;
+          }
+          if (globaltimer_ns() - t0 > kWaitBudgetNs) {
+            if (atomicCAS(a.status, 0, CTDK_ETIMEOUT) == 0) {
+              a.status[1] = 90;
+              a.status[2] = static_cast<int>(blockIdx.x);
+              a.status[3] = static_cast<int>(epoch);
+            }
+            atomicExch(&a.sync[2], 1u);
+            ok = 0;
+            break;
+          }
+        }
+      }
+    }
+    if (ok && ld_acquire_u32(&a.sync[2]) != 0u) ok = 0;
+    s_ok = ok;
+  }
+  __syncthreads();
+  return s_ok != 0;
+}
+// Rows n = first, first + step, ... of W[N, K] for this warp when WPR warps of a CTA share a row.
+template <int WPR>
+__device__ __forceinline__ void row_walk(int& first, int& step) {
+  const int wid = threadIdx.x >> 5;
+  first = blockIdx.x * (8 / WPR) + wid / WPR;
+  step = gridDim.x * (8 / WPR);
+}
+// Requests this warp's share of W[N, K] into L2 (one 128-byte line per lane and iteration).
+template <int WPR>
+__device__ __forceinline__ void prefetch_rows(const float* __restrict__ W, int N, int K) {
+  int first, step;
+  row_walk<WPR>(first, step);
+  const int lane = threadIdx.x & 31, part = (threadIdx.x >> 5) % WPR;
+  const int Kp = K / WPR;
+  for (int n = first; n < N; n += step) {
+    const char* row = reinterpret_cast<const char*>(W + static_cast<int64_t>(n) * K + part * Kp);
+    for (int off = lane * 128; off < Kp * 4; off += 32 * 128) prefetch_l2(row + off);
+  }
+}
+// y[n] = dot(W[n, :], xs) (+ residual[n]); xs is the staged input in shared memory. With WPR > 1
+// the warps of a group each take a K range and meet on a named barrier.
+template <int WPR>
+__device__ __forceinline__ void gemv_rows(const float* __restrict__ W, const float* xs, float* __restrict__ y,
+                                          const float* __restrict__ residual, int N, int K, float* pair_red) {
+  int first, step;
+  row_walk<WPR>(first, step);
+  const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, part = wid % WPR;
+  const int Kp4 = K / WPR / 4;
+  const float4* x4 = reinterpret_cast<const float4*>(xs) + part * Kp4;
+  for (int n = first; n < N; n += step) {
+    const float4* w4 = reinterpret_cast<const float4*>(W + static_cast<int64_t>(n) * K) + part * Kp4;
+    float acc = 0.0f;
+#pragma unroll 8
+    for (int i = lane; i < Kp4; i += 32) {
+      const float4 w = __ldcs(w4 + i), v = x4[i];
+      acc += w.x * v.x + w.y * v.y + w.z * v.z + w.w * v.w;
+    }
+    acc = warp_sum(acc);
+    if (WPR == 1) {
+      if (lane == 0) y[n] = residual != nullptr ? acc + __ldcg(residual + n) : acc;
+    } else {
+      if (lane == 0) pair_red[wid] = acc;
+      asm volatile("bar.sync %0, %1;" ::"r"(1 + wid / WPR), "r"(32 * WPR) : "memory");
+      if (part == 0 && lane == 0) {
+        float t = 0.0f;
+#pragma unroll
+        for (int k = 0; k < WPR; ++k) t += pair_red[wid + k];
+        y[n] = residual != nullptr ? t + __ldcg(residual + n) : t;
+      }
+      asm volatile("bar.sync %0, %1;" ::"r"(1 + wid / WPR), "r"(32 * WPR) : "memory");
+    }
+  }
+}
+// xs = x * rsqrt(mean(x^2) + eps) * nw (every CTA stages its own copy).
+__device__ __forceinline__ void stage_rmsnorm(const float* __restrict__ x, const float* __restrict__ nw, float eps, int K,
+                                              float* xs, float* red) {
+  const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+  float ss = 0.0f;
+  for (int i = threadIdx.x; i < K; i += blockDim.x) {
+    const float v = __ldcg(x + i);   // written by other CTAs one barrier ago: not through L1
+    xs[i] = v;
+    ss += v * v;
+  }
+  ss = warp_sum(ss);
+  if (lane == 0) red[wid] = ss;
+  __syncthreads();
+  float tot = 0.0f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) tot += red[i];
+  const float sc = rsqrtf(tot / static_cast<float>(K) + eps);
+  for (int i = threadIdx.x; i < K; i += blockDim.x) xs[i] = xs[i] * sc * nw[i];
+  __syncthreads();
+}
+
+// Post-processes head `slot` of the new row (per-head RMSNorm when w != nullptr, then RoPE at pos)
+// into dst[D]; one warp.
+__device__ __forceinline__ void head_post(const float* __restrict__ xr, const float* __restrict__ w, const float2* __restrict__ table,
+                                          int pos, int D, float eps, float* dst) {
+  const int lane = threadIdx.x & 31, Dh = D / 2;
+  float s = 1.0f;
+  if (w != nullptr) {
+    float ss = 0.0f;
+    for (int i = lane; i < D; i += 32) {
+      const float v = __ldcg(xr + i);
+      ss += v * v;
+    }
+    ss = warp_sum(ss);
+    s = rsqrtf(ss / static_cast<float>(D) + eps);
+  }
+  for (int i = lane; i < Dh; i += 32) {
+    float p = __ldcg(xr + i), q = __ldcg(xr + i + Dh);
+    if (w != nullptr) {
+      p = p * s * w[i];
+      q = q * s * w[i + Dh];
+    }
+    const float2 cs = table[static_cast<int64_t>(pos) * Dh + i];
+    dst[i] = p * cs.x - q * cs.y;
+    dst[i + Dh] = p * cs.y + q * cs.x;
+  }
+}
+
+__global__ void __launch_bounds__(256, 2) decode_persistent_kernel(const __grid_constant__ PersistArgs a) {
+  extern __shared__ float sm[];   // staged input vector (up to max(hid, H*D, I) floats), then attention scratch
+  __shared__ float red[8];
+  __shared__ float pair_red[8];
+  __shared__ unsigned long long best_s[8];
+  __shared__ int s_last;
+  const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+  const int hid = a.hid, I = a.I, D = a.D, H = a.H, Hk = a.Hk, G = H / Hk;
+  const int64_t cache_layer = static_cast<int64_t>(Hk) * a.max_seq * D;
+  unsigned int epoch = 0;
+  int pos = a.counters[0];
+  int64_t tok = *a.cur_token;
+  unsigned long long* words = reinterpret_cast<unsigned long long*>(a.sync + 128);
+  bool alive = true;
+
+  for (int t = 0; t < a.n_tokens && alive; ++t) {
+    const float* xin = a.P + a.embed + tok * hid;   // layer 0 reads the embedding row in place
+    for (int l = 0; l < a.L && alive; ++l) {
+      const PLayer& w = a.lw[l];
+      // ---- phase 1: qkv = Wqkv rmsnorm(x) ----
+      stage_rmsnorm(xin, a.P + w.w_in, a.eps, hid, sm, red);
+      gemv_rows<1>(a.P + w.wq, sm, a.qkv, nullptr, a.QKVN, hid, pair_red);
+      prefetch_rows<2>(a.P + w.wo, hid, H * D);
+      if (!(alive = grid_barrier(a, epoch))) break;
+
+      // ---- phase 2: attention of the new row, split over key ranges; the last split of a head merges ----
+      {
+        float* kc = a.kcache + l * cache_layer;
+        float* vc = a.vcache + l * cache_layer;
+        const int Lk = pos + 1;
+        const int per = (Lk + kPersistSplits - 1) / kPersistSplits;
+        float* qs = sm;                 // [D] post-processed q of the head
+        float* kn = sm + D;             // [D] post-processed new k of the kv head
+        float* sc = sm + 2 * D;         // [per] scores
+        float* scr = sc + (((a.max_seq + kPersistSplits - 1) / kPersistSplits + 4) & ~3);   // [8][D] per-warp partial sums
+        for (int item = blockIdx.x; item < H * kPersistSplits; item += gridDim.x) {
+          const int h = item / kPersistSplits, sp = item % kPersistSplits, hk = h / G;
+          const int j0 = sp * per, j1 = min(Lk, j0 + per);
+          float* dst = a.attn_part + (static_cast<int64_t>(h) * kPersistSplits + sp) * (D + 2);
+          const bool has_new = pos >= j0 && pos < j1;   // this range ends with the new position
+          if (wid == 0) head_post(a.qkv + static_cast<int64_t>(h) * D, a.qk_norm ? a.P + w.wqn : nullptr, a.table, pos, D, a.eps, qs);
+          if (wid == 1 && has_new) {
+            head_post(a.qkv + static_cast<int64_t>(H + hk) * D, a.qk_norm ? a.P + w.wkn : nullptr, a.table, pos, D, a.eps, kn);
+            if (h % G == 0) {   // one head of the group puts the new K / V rows into the cache for later tokens
+              __syncwarp();
+              for (int i = lane; i < D; i += 32) {
+                kc[(static_cast<int64_t>(hk) * a.max_seq + pos) * D + i] = kn[i];
+                vc[(static_cast<int64_t>(hk) * a.max_seq + pos) * D + i] = __ldcg(a.qkv + static_cast<int64_t>(H + Hk + hk) * D + i);
+              }
+            }
+          }
+          __syncthreads();
+          const float* kb = kc + static_cast<int64_t>(hk) * a.max_seq * D;
+          const float* vb = vc + static_cast<int64_t>(hk) * a.max_seq * D;
+          const float* vnew = a.qkv + static_cast<int64_t>(H + Hk + hk) * D;
+          // scores: one warp per key (a key row is one coalesced read of the warp), four keys in flight
+          float mx = -FLT_MAX;
+          {
+            const float4* q4 = reinterpret_cast<const float4*>(qs);
+            const int D4 = D / 4;
+            for (int jb = j0 + wid; jb < j1; jb += 32) {
+              float part[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+              for (int u = 0; u < 4; ++u) {
+                const int j = jb + 8 * u;
+                if (j < j1) {
+                  const float4* kr = reinterpret_cast<const float4*>(j == pos ? kn : kb + static_cast<int64_t>(j) * D);
+                  for (int i = lane; i < D4; i += 32) {
+                    const float4 k4 = kr[i], b4 = q4[i];
+                    part[u] += k4.x * b4.x + k4.y * b4.y + k4.z * b4.z + k4.w * b4.w;
+                  }
+                }
+              }
+#pragma unroll
+              for (int u = 0; u < 4; ++u) {
+                const int j = jb + 8 * u;
+                const float v = warp_sum(part[u]) * a.scale;
+                if (j < j1) {
+                  if (lane == 0) sc[j - j0] = v;
+                  mx = fmaxf(mx, v);
+                }
+              }
+            }
+          }
+          mx = warp_max(mx);
+          if (lane == 0) red[wid] = mx;
+          __syncthreads();
+          mx = -FLT_MAX;
+#pragma unroll
+          for (int i = 0; i < 8; ++i) mx = fmaxf(mx, red[i]);
+          __syncthreads();
+          float sum = 0.0f;
+          for (int j = j0 + threadIdx.x; j < j1; j += blockDim.x) {
+            const float e = __expf(sc[j - j0] - mx);
+            sc[j - j0] = e;
+            sum += e;
+          }
+          sum = warp_sum(sum);
+          if (lane == 0) red[wid] = sum;
+          __syncthreads();
+          sum = 0.0f;
+#pragma unroll
+          for (int i = 0; i < 8; ++i) sum += red[i];
+          // weighted sum of the value rows: one warp per key (a row is one coalesced read), four rows in
+          // flight per warp; the eight warps' sums meet in shared memory
+          {
+            const int D4 = D / 4;
+            float4 acc4[2] = {make_float4(0.f, 0.f, 0.f, 0.f), make_float4(0.f, 0.f, 0.f, 0.f)};   // D <= 256: two float4 per lane
+            for (int jb = j0 + wid; jb < j1; jb += 32) {
+#pragma unroll
+              for (int u = 0; u < 4; ++u) {
+                const int j = jb + 8 * u;
+                if (j < j1) {
+                  const float pj = sc[j - j0];
+                  const float4* vr = reinterpret_cast<const float4*>(j == pos ? vnew : vb + static_cast<int64_t>(j) * D);
+#pragma unroll
+                  for (int c = 0; c < 2; ++c) {
+                    const int i = lane + 32 * c;
+                    if (i < D4) {
+                      const float4 v4 = j == pos ? __ldcg(vr + i) : vr[i];
+                      acc4[c].x += pj * v4.x;
+                      acc4[c].y += pj * v4.y;
+                      acc4[c].z += pj * v4.z;
+                      acc4[c].w += pj * v4.w;
+                    }
+                  }
+                }
+              }
+            }
+#pragma unroll
+            for (int c = 0; c < 2; ++c) {
+              const int i = lane + 32 * c;
+              if (i < D4) reinterpret_cast<float4*>(scr + wid * D)[i] = acc4[c];
+            }
+          }
+          __syncthreads();
+          if (threadIdx.x < D) {
+            float tsum = 0.0f;
+#pragma unroll
+            for (int p2 = 0; p2 < 8; ++p2) tsum += scr[p2 * D + threadIdx.x];
+            dst[2 + threadIdx.x] = j0 < j1 ? tsum : 0.0f;
+          }
+          if (threadIdx.x == 0) {
+            dst[0] = j0 < j1 ? mx : -FLT_MAX;
+            dst[1] = j0 < j1 ? sum : 0.0f;
+          }
+          // the split that arrives last at its head merges all of them
+          __threadfence();
+          __syncthreads();
+          if (threadIdx.x == 0) {
+            const unsigned int prev = atomicAdd(&a.sync[8 + h], 1u);
+            s_last = prev == static_cast<unsigned int>(kPersistSplits - 1);
+            if (s_last) a.sync[8 + h] = 0u;   // next use is a grid barrier away
+          }
+          __syncthreads();
+          if (s_last) {
+            __threadfence();
+            const float* pp = a.attn_part + static_cast<int64_t>(h) * kPersistSplits * (D + 2);
+            float M = -FLT_MAX;
+#pragma unroll
+            for (int s2 = 0; s2 < kPersistSplits; ++s2) M = fmaxf(M, __ldcg(pp + s2 * (D + 2)));
+            float lsum = 0.0f, wv[kPersistSplits];
+#pragma unroll
+            for (int s2 = 0; s2 < kPersistSplits; ++s2) {
+              wv[s2] = __expf(__ldcg(pp + s2 * (D + 2)) - M);
+              lsum += __ldcg(pp + s2 * (D + 2) + 1) * wv[s2];
+            }
+            const float inv = 1.0f / lsum;
+            for (int dd = threadIdx.x; dd < D; dd += blockDim.x) {
+              float o = 0.0f;
+#pragma unroll
+              for (int s2 = 0; s2 < kPersistSplits; ++s2) o += __ldcg(pp + s2 * (D + 2) + 2 + dd) * wv[s2];
+              a.attn[static_cast<int64_t>(h) * D + dd] = o * inv;
+            }
+          }
+          __syncthreads();
+        }
+      }
+      prefetch_rows<1>(a.P + w.wg, 2 * I, hid);
+      if (!(alive = grid_barrier(a, epoch))) break;
+
+      // ---- phase 3: hm = x + Wo attn ----
+      for (int i = threadIdx.x; i < H * D; i += blockDim.x) sm[i] = __ldcg(a.attn + i);
+      __syncthreads();
+      gemv_rows<2>(a.P + w.wo, sm, a.hm, xin, hid, H * D, pair_red);
+      prefetch_rows<2>(a.P + w.wd, hid, I);
+      if (!(alive = grid_barrier(a, epoch))) break;
+
+      // ---- phase 4: gu = Wgu rmsnorm(hm) ----
+      stage_rmsnorm(a.hm, a.P + w.w_post, a.eps, hid, sm, red);
+      gemv_rows<1>(a.P + w.wg, sm, a.gu, nullptr, 2 * I, hid, pair_red);
+      if (l + 1 < a.L) prefetch_rows<1>(a.P + a.lw[l + 1].wq, a.QKVN, hid);
+      if (!(alive = grid_barrier(a, epoch))) break;
+
+      // ---- phase 5: x = hm + Wd (silu(gate) * up) ----
+      for (int i = threadIdx.x; i < I; i += blockDim.x) {
+        const float g = __ldcg(a.gu + i);
+        sm[i] = g / (1.0f + __expf(-g)) * __ldcg(a.gu + I + i);
+      }
+      __syncthreads();
+      gemv_rows<2>(a.P + w.wd, sm, a.x, a.hm, hid, I, pair_red);
+      if (!(alive = grid_barrier(a, epoch))) break;
+      xin = a.x;
+    }
+    if (!alive) break;
+
+    // ---- LM head (tied embedding) + arg-max: first index of the maximum ----
+    stage_rmsnorm(xin, a.P + a.norm, a.eps, hid, sm, red);
+    {
+      unsigned long long best = 0ull;
+      int first, step;
+      row_walk<1>(first, step);
+      const int K4 = hid / 4;
+      const float4* x4 = reinterpret_cast<const float4*>(sm);
+      const float* E = a.P + a.embed;
+      for (int n = first; n < a.V; n += step) {
+        const float4* w4 = reinterpret_cast<const float4*>(E + static_cast<int64_t>(n) * hid);
+        float acc = 0.0f;
+#pragma unroll 8
+        for (int i = lane; i < K4; i += 32) {
+          const float4 wv4 = __ldcs(w4 + i), v = x4[i];
+          acc += wv4.x * v.x + wv4.y * v.y + wv4.z * v.z + wv4.w * v.w;
+        }
+        acc = warp_sum(acc);
+        if (lane == 0) {
+          a.logits[n] = acc;
+          const unsigned long long k = argmax_key(acc, n);
+          best = k > best ? k : best;
+        }
+      }
+      if (lane == 0) best_s[wid] = best;
+      __syncthreads();
+      if (threadIdx.x == 0) {
+#pragma unroll
+        for (int i = 1; i < 8; ++i) best = best_s[i] > best ? best_s[i] : best;
+        atomicMax(&words[t & 1], best);
+      }
+    }
+    if (!(alive = grid_barrier(a, epoch))) break;
+    {
+      const unsigned long long wv = *reinterpret_cast<volatile unsigned long long*>(&words[t & 1]);
+      tok = static_cast<int64_t>(0xFFFFFFFFu - static_cast<unsigned>(wv & 0xFFFFFFFFull));
+      if (blockIdx.x == 0 && threadIdx.x == 0) {
+        a.out_tokens[a.out_offset + t] = tok;
+        words[(t + 1) & 1] = 0ull;   // last read one barrier ago
+      }
+      pos += 1;
+    }
+  }
+  if (blockIdx.x == 0 && threadIdx.x == 0) {
+    a.counters[0] = pos;
+    a.counters[1] += a.n_tokens;
+    *a.cur_token = tok;
+  }
+}
+
 }  // namespace
 }  // namespace ctdk
 
@@ -355,6 +803,8 @@ struct Decoder {
   float *pa, *pb, *pqkv, *pattn, *plse, *pgu, *pact;  // prefill buffers ([max_seq, ...])
   int64_t* cur_token;
   int* counters;  // [0] = position of the next token, [1] = tokens generated
+  unsigned int* sync = nullptr;
+  int persistent_grid = -1;   // CTAs of the persistent token kernel; 0 = not usable here; -1 = not decided yet
   cudaGraphExec_t graph = nullptr;
   int64_t* graph_out = nullptr;
   cudaStream_t graph_stream = nullptr;
@@ -397,9 +847,10 @@ void carve_decoder(Decoder& d, Bump2& b) {
   d.plse = b.floats(H * S);
   d.pgu = b.floats(S * 2 * I);
   d.pact = b.floats(S * I);
-  d.attn_part = b.floats(static_cast<int64_t>(H) * kAttnSplits * (D + 2));
+  d.attn_part = b.floats(static_cast<int64_t>(H) * (kPersistSplits > kAttnSplits ? kPersistSplits : kAttnSplits) * (D + 2));
   d.cur_token = reinterpret_cast<int64_t*>(b.floats(2));
   d.counters = reinterpret_cast<int*>(b.floats(8));  // position, count, scratch, -, then the 64-bit argmax word
+  d.sync = reinterpret_cast<unsigned int*>(b.floats(kSyncWords));   // persistent kernel: grid barrier, per-head arrivals, argmax words
 }
 
 int init_decoder(Decoder& d, const ctdk_model_config* cfg, int64_t max_seq) {
@@ -509,6 +960,76 @@ int enqueue_token_step(Decoder& d, int64_t* out_tokens, cudaStream_t s) {
   if (launch_pdl(argmax_finish_kernel, 1, 1, 0, s, word, d.cur_token, out_tokens, d.counters, d.counters + 1) != cudaSuccess)
     return fail(CTDK_ELAUNCH, "decode argmax finish: launch failed");
   return check_launch("decode argmax finish");
+}
+
+// Returns CTDK_OK when the persistent kernel was launched for `n` tokens, 1 when it does not apply
+// (the caller takes the kernel-per-phase path), or a negative status.
+int launch_persistent(Decoder& d, int64_t n, int64_t* out_tokens, cudaStream_t s) {
+  const ctdk_model_config& c = d.cfg;
+  const int hid = c.hidden_size, I = c.intermediate_size, D = c.head_dim, H = c.num_attention_heads;
+  const size_t stage = static_cast<size_t>(std::max(std::max(hid, H * D), I));
+  const size_t attn = static_cast<size_t>(2 * D + (d.max_seq + kPersistSplits - 1) / kPersistSplits + 8 + 8 * D);
+  const size_t smem = std::max(stage, attn) * sizeof(float);
+  if (d.persistent_grid < 0) {
+    d.persistent_grid = 0;
+    const char* env = std::getenv("CTDK_DECODE_PERSISTENT");
+    const bool off = env != nullptr && env[0] == '0';
+    int dev = 0, coop = 0, per_sm = 0;
+    const bool shape_ok = c.num_hidden_layers <= kMaxPersistLayers && hid % 8 == 0 && (H * D) % 8 == 0 && I % 8 == 0 && D % 4 == 0 &&
+                          256 % D == 0 && H <= 96 && smem <= 96 * 1024 && n < (1 << 20);
+    if (!off && shape_ok && cudaGetDevice(&dev) == cudaSuccess &&
+        cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, dev) == cudaSuccess && coop != 0 &&
+        cudaFuncSetAttribute(decode_persistent_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) == cudaSuccess &&
+        cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, decode_persistent_kernel, 256, smem) == cudaSuccess && per_sm >= 1)
+      d.persistent_grid = sm_count() * (per_sm > 2 ? 2 : per_sm);
+    cudaGetLastError();
+  }
+  if (d.persistent_grid <= 0) return 1;
+  PersistArgs a{};
+  a.P = d.params;
+  for (int l = 0; l < c.num_hidden_layers; ++l) {
+    const LayerW& w = d.lw[l];
+    a.lw[l] = PLayer{w.w_in, w.wq, w.wo, w.wqn, w.wkn, w.w_post, w.wg, w.wd};
+  }
+  a.embed = d.embed;
+  a.norm = d.norm;
+  a.L = c.num_hidden_layers;
+  a.hid = hid;
+  a.I = I;
+  a.D = D;
+  a.H = H;
+  a.Hk = c.num_key_value_heads;
+  a.V = c.vocab_size;
+  a.QKVN = d.QKVN;
+  a.max_seq = d.max_seq;
+  a.qk_norm = c.qk_norm;
+  a.eps = c.rms_norm_eps;
+  a.scale = 1.0f / sqrtf(static_cast<float>(D));
+  a.table = reinterpret_cast<const float2*>(d.rope_table);
+  a.kcache = d.kcache;
+  a.vcache = d.vcache;
+  a.x = d.x;
+  a.qkv = d.qkv;
+  a.attn = d.attn;
+  a.hm = d.hm;
+  a.gu = d.gu;
+  a.logits = d.logits;
+  a.attn_part = d.attn_part;
+  a.cur_token = d.cur_token;
+  a.counters = d.counters;
+  a.sync = d.sync;
+  a.out_tokens = out_tokens;
+  a.out_offset = static_cast<int>(d.generated);
+  a.n_tokens = static_cast<int>(n);
+  a.status = device_status_word();
+  if (a.status == nullptr) return fail(CTDK_ELAUNCH, "decode: no status word");
+  if (cudaMemsetAsync(d.sync, 0, kSyncWords * sizeof(unsigned int), s) != cudaSuccess)
+    return fail(CTDK_ELAUNCH, "decode: clearing the barrier words failed");
+  void* params[] = {&a};
+  const cudaError_t e = cudaLaunchCooperativeKernel(reinterpret_cast<const void*>(decode_persistent_kernel), dim3(d.persistent_grid),
+                                                    dim3(256), params, smem, s);
+  if (e != cudaSuccess) return fail(CTDK_ELAUNCH, "decode: cooperative launch failed: %s", cudaGetErrorString(e));
+  return check_launch("decode persistent");
 }
 
 __global__ void set_token_kernel(int64_t* cur, int64_t value) { *cur = value; }
@@ -662,6 +1183,14 @@ int ctdk_decode_greedy(void* decoder, int64_t n_new, int64_t* out_tokens, void* 
     --todo;
   }
   if (todo == 0) return CTDK_OK;
+  // All remaining tokens in one cooperative launch of the persistent kernel where it applies.
+  {
+    const int rc = launch_persistent(d, todo, out_tokens, s);
+    if (rc <= 0) {
+      if (rc == CTDK_OK) d.generated += todo;
+      return rc;
+    }
+  }
   // One token step = ~9 kernels per layer; captured once and replayed, so a step costs one launch.
   const bool can_capture = s != nullptr;
   if (can_capture && (d.graph == nullptr || d.graph_out != out_tokens || d.graph_stream != s)) {

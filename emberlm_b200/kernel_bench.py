@@ -6,6 +6,7 @@
   python -m emberlm_b200.kernel_bench adamw --n 361821120
   python -m emberlm_b200.kernel_bench rmsnorm --rows 32736 --hid 960
   python -m emberlm_b200.kernel_bench ce --rows 5376 --v 49152
+  python -m emberlm_b200.kernel_bench qkrope --b 32 --t 1023 --h 15 --hk 5 --d 64 [--qknorm 1]
 
 Inputs are larger than L2 or an L2-flushing write runs between timed iterations (--flush).
 This is also the small case used for ncu captures of one kernel."""
@@ -67,7 +68,7 @@ def step_gemm_shapes(cfg, tok):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("kernel", choices=["gemm", "gemm-step", "attn", "adamw", "rmsnorm", "ce", "mlp"])
+    ap.add_argument("kernel", choices=["gemm", "gemm-step", "attn", "adamw", "rmsnorm", "ce", "mlp", "qkrope"])
     ap.add_argument("--m", type=int, default=32736)
     ap.add_argument("--n", type=int, default=2560)
     ap.add_argument("--k", type=int, default=960)
@@ -87,6 +88,7 @@ def main():
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--flush", action="store_true")
+    ap.add_argument("--qknorm", type=int, default=0)
     a = ap.parse_args()
 
     if a.kernel == "gemm":
@@ -139,6 +141,21 @@ def main():
         dx, dw = torch.empty_like(x), torch.empty_like(w)
         ms = _time(lambda: ops.rms_norm_backward(dy, x, w, 1e-5, dx=dx, dw=dw), a.iters, a.warmup, a.flush)
         print(json.dumps(dict(kernel="rmsnorm_bwd", rows=a.rows, H=a.hid, ms=ms, gbs=12.0 * x.numel() / ms / 1e6)))
+    elif a.kernel == "qkrope":
+        B, T, H, Hk, D = a.b, a.t, a.h, a.hk, a.d
+        qkv = torch.randn(B * T, (H + 2 * Hk) * D, device="cuda")
+        dqkv = torch.randn_like(qkv)
+        table = ops.rope_table(T, D, 0, 100000.0)
+        wq = torch.ones(D, device="cuda") if a.qknorm else None
+        wk = torch.ones(D, device="cuda") if a.qknorm else None
+        out, rq, rk = ops.qk_norm_rope(qkv, B, T, H, Hk, D, table, wq, wk)
+        qk_elems = B * T * (H + Hk) * D
+        fwd_bytes = 8.0 * (qk_elems + B * T * Hk * D)            # q, k read + written, v copied (out of place)
+        ms = _time(lambda: ops.qk_norm_rope(qkv, B, T, H, Hk, D, table, wq, wk), a.iters, a.warmup, a.flush)
+        print(json.dumps(dict(kernel="qk_norm_rope_fwd", B=B, T=T, H=H, Hk=Hk, D=D, qknorm=a.qknorm, ms=ms, gbs=fwd_bytes / ms / 1e6)))
+        bwd_bytes = (12.0 if a.qknorm else 8.0) * qk_elems
+        ms = _time(lambda: ops.qk_norm_rope_backward(dqkv, qkv, B, T, H, Hk, D, table, wq, wk, rq, rk), a.iters, a.warmup, a.flush)
+        print(json.dumps(dict(kernel="qk_norm_rope_bwd", B=B, T=T, H=H, Hk=Hk, D=D, qknorm=a.qknorm, ms=ms, gbs=bwd_bytes / ms / 1e6)))
     elif a.kernel == "ce":
         z = torch.randn(a.rows, a.v, device="cuda")
         t = torch.randint(0, a.v, (a.rows,), device="cuda")

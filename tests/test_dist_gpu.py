@@ -67,3 +67,66 @@ def test_two_gpu_step_equals_one_gpu_step(tmp_path):
     # single elements by up to 2*lr; bound the error relative to the largest weight
     assert np.abs(b["params"] - a["params"]).max() <= 3 * HP["lr"]
     assert np.mean(np.abs(b["params"] - a["params"]) > 1e-6) < 1e-3
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_ctd_train_two_ranks_equals_one_rank(tmp_path):
+    """The C++ trainer started as two processes (RANK / WORLD_SIZE / LOCAL_RANK, NCCL id through a
+    file): same loss.jsonl as one process on the same config, and a final checkpoint (parameters,
+    optimizer.m / .v gathered from the two ranks' slices, optimizer.step) that matches it."""
+    import json
+    import subprocess
+    from pathlib import Path
+    from emberlm_b200 import build, engine as E, safetensors_io
+    exe = Path(build.HERE) / "ctd_train"
+    cfg = E.make_config(**E.PRESETS["smollm2_135m"])
+    eng = E.TrainEngine(cfg, 1, 8, train=False)
+    eng.init_parameters(seed=5)
+    w0 = tmp_path / "init.safetensors"
+    safetensors_io.save_safetensors([(n, v.cpu().numpy()) for n, v in eng.named_parameters().items()], w0)
+    del eng
+    torch.cuda.empty_cache()
+    S_, docs = 65, 8
+    rng = np.random.default_rng(9)
+    tok = rng.integers(0, cfg.vocab_size, size=(docs, S_), dtype=np.int32)
+    msk = np.zeros((docs, S_), np.int8)
+    for d in range(docs):
+        msk[d, 8 + d:40 + d] = 1
+    data = tmp_path / "data"
+    data.mkdir()
+    for name, arr in (("train.bin", tok), ("train_mask.bin", msk), ("val.bin", tok[:5]), ("val_mask.bin", msk[:5])):
+        arr.tofile(data / name)
+    conf = dict(init_weights=str(w0), data_dir=str(data), seq_len=S_, batch_size=2, grad_accum_steps=4, total_steps=3, warmup_steps=0,
+                min_lr_ratio=1.0, clip_grad_norm=1.0, val_every=3, save_every=0, log_every=1, seed=42, **HP)
+    conf.pop("clip", None)
+    runs = {}
+    for world in (1, 2):
+        run = tmp_path / f"run{world}"
+        run.mkdir()
+        (run / "config.json").write_text(json.dumps(conf))
+        procs = []
+        for r in range(world):
+            env = dict(os.environ, RANK=str(r), WORLD_SIZE=str(world), LOCAL_RANK=str(r), CTDK_NCCL_ID_FILE=str(run / "nccl_id"),
+                       NCCL_NVLS_ENABLE="0")
+            procs.append(subprocess.Popen([str(exe), "--config", str(run / "config.json")], env=env, stdout=subprocess.PIPE,
+                                          stderr=subprocess.PIPE, text=True))
+        for p in procs:
+            out, err = p.communicate(timeout=900)
+            assert p.returncode == 0, err[-2000:]
+        runs[world] = ([json.loads(l) for l in (run / "loss.jsonl").read_text().splitlines()],
+                       safetensors_io.load_safetensors(run / "final.safetensors"),
+                       safetensors_io.load_safetensors(str(run / "final.safetensors") + ".opt.safetensors"))
+    (e1, p1, o1), (e2, p2, o2) = runs[1], runs[2]
+    assert [(e["step"], e["phase"]) for e in e1] == [(e["step"], e["phase"]) for e in e2]
+    for a, b in zip(e1, e2):
+        assert abs(a["loss"] - b["loss"]) <= 1e-5 * abs(a["loss"]), (a, b)
+        if a["phase"] == "train":
+            assert abs(a["grad_norm"] - b["grad_norm"]) <= 1e-3 * a["grad_norm"]   # summation order, amplified by TF32 rounding down the layers
+    assert set(p1) == set(p2) and set(o1) == set(o2)
+    assert float(o2["optimizer.step"][0]) == 3.0
+    for n in p1:
+        d = np.abs(p1[n] - p2[n])
+        assert d.max() <= 7 * HP["lr"] and np.mean(d > 1e-6) < 2e-2, n      # sign-like early AdamW steps (see above)
+    for n in ("optimizer.m.model.layers.7.mlp.up_proj.weight", "optimizer.v.model.embed_tokens.weight", "optimizer.m.model.norm.weight"):
+        d = np.abs(o1[n] - o2[n]).max() / max(np.abs(o1[n]).max(), 1e-30)
+        assert d <= 1e-3, (n, d)
