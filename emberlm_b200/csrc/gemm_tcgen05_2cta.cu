@@ -4,7 +4,7 @@
 // this moves one third fewer operand bytes through L2 and shared memory than the one-CTA
 // 128 x 256 tile of gemm_tcgen05.cu, which is what bounds that kernel with 4-byte operands.
 //
-// Roles per CTA (6 warps): TMA producer, MMA warp, 4 epilogue warps. Only the even CTA of the
+// Roles per CTA (10 warps): TMA producer, MMA warp, 8 epilogue warps. Only the even CTA of the
 // pair (the leader) issues MMAs; both CTAs' TMA loads report their bytes to the leader's
 // "full" barrier; the leader releases stages and publishes finished accumulators to both CTAs
 // with a multicast tcgen05.commit; both CTAs' epilogue warps report to the leader's
@@ -25,24 +25,13 @@ constexpr int kStage2 = kATile + kBHalf;
 constexpr int kStages2 = 6;
 constexpr int kChunk2 = 32 * BK2 * 4;    // one {32 x 32} box of an MN-major operand
 constexpr int kEpiBuf = 32 * 128;         // one {32 x 32} fp32 output box in transit
-constexpr int kEpiStage = 4 * 2 * kEpiBuf;  // 4 epilogue warps x 2 buffers
+constexpr int kEpiWarps = 8;              // two per tensor-memory lane quarter, each takes half of the tile's columns
+constexpr int kThreads2 = 32 * (2 + kEpiWarps);
+constexpr int kEpiStage = kEpiWarps * kEpiBuf;  // one staging box per epilogue warp (two for the SwiGLU backward, which runs 5 stages)
 constexpr int kTiles2 = kStages2 * kStage2 + kEpiStage;   // operand ring + output staging: 224 KB, split per mode
 constexpr int kSmem2 = kTiles2 + 1024 + 256;
 constexpr uint32_t kPeerMask = 0xFEFFFFFFu;  // clears the CTA-rank bit of a shared::cluster address
 constexpr int kGroupM2 = 8;
-
-#ifdef CTDK_GEMM_PROBE
-__device__ long long g_gemm_probe[16];
-#define GP_DECL() long long _acc[8] = {0, 0, 0, 0, 0, 0, 0, 0}
-#define GP_T0() const long long _pt0 = clock64()
-#define GP_ADD(i) _acc[i] += clock64() - _pt0
-#define GP_FLUSH(lo, hi) for (int _i = lo; _i < hi; ++_i) atomicAdd(reinterpret_cast<unsigned long long*>(&g_gemm_probe[_i]), static_cast<unsigned long long>(_acc[_i]))
-#else
-#define GP_DECL()
-#define GP_T0()
-#define GP_ADD(i)
-#define GP_FLUSH(lo, hi)
-#endif
 
 struct Gemm2Args {
   float* C;
@@ -156,7 +145,7 @@ __device__ __forceinline__ void tile_coords2(int tile, int m_blocks, int n_block
 }
 
 template <bool A_MN, bool B_MN>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads2, 1)
     gemm_tf32_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                           const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmD,
                           const Gemm2Args args) {
@@ -170,8 +159,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
   uint64_t* full = bars;                   // [kStages2]  used in the leader only
   uint64_t* empty = bars + kStages2;       // [kStages2]  one per CTA, signalled by multicast commit
   uint64_t* tfull = bars + 2 * kStages2;   // [2]         one per CTA, multicast commit
-  uint64_t* tempty = tfull + 2;            // [2]         leader only, 8 arrivals (4 warps x 2 CTAs)
-  uint64_t* ld_bar = tempty + 2;           // [4 warps][2 slots]  gate / up boxes of the SwiGLU-backward epilogue
+  uint64_t* tempty = tfull + 2;            // [2]         leader only, 16 arrivals (8 warps x 2 CTAs)
+  uint64_t* ld_bar = tempty + 2;           // [8 warps]   gate / up boxes of the SwiGLU-backward epilogue
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(ld_bar + 8);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -191,7 +180,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(&tfull[a], 1);
-      mbar_init(&tempty[a], 8);
+      mbar_init(&tempty[a], 2 * kEpiWarps);
     }
     for (int a = 0; a < 8; ++a) mbar_init(&ld_bar[a], 1);
     mbar_fence_init();
@@ -217,8 +206,6 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
       int s = 0;
       uint32_t ph = 0;
       bool ok = true;
-      GP_DECL();
-      const long long _k0 = clock64();
       for (int unit = pair; unit < num_units && ok; unit += n_pairs) {
         int mb, nb;
         tile_coords2(unit % num_tiles, m_blocks, n_blocks, mb, nb);
@@ -232,14 +219,11 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
         const int kb1 = static_cast<int>(static_cast<int64_t>(split + 1) * k_blocks / args.splits);
         for (int kb = kb0; kb < kb1; ++kb) {
           {
-            GP_T0();
             if (!mbar_wait_bounded(&empty[s], ph ^ 1u, args.status, 61)) {
               ok = false;
               break;
             }
-            GP_ADD(0);
           }
-          GP_T0();
           unsigned char* a_dst = smem + s * kStage2;
           unsigned char* b_dst = a_dst + kATile;
           if (leader) mbar_expect_tx(&full[s], 2 * kStage2);  // bytes of both CTAs
@@ -266,17 +250,12 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
           } else {
             tma_load_2d_pair(b_dst, &tmB, &full[s], k0, n0);
           }
-          GP_ADD(1);
           if (++s == n_stages) {
             s = 0;
             ph ^= 1u;
           }
         }
       }
-#ifdef CTDK_GEMM_PROBE
-      _acc[2] = clock64() - _k0;
-      if (leader) { GP_FLUSH(0, 3); }
-#endif
     }
     __syncwarp();
   } else if (warp == 1) {
@@ -290,7 +269,6 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
       uint32_t ph = 0;
       bool ok = true;
       int it = 0;
-      GP_DECL();
       for (int unit = pair; unit < num_units && ok; unit += n_pairs, ++it) {
         const int split = unit / num_tiles;
         const int kb0 = static_cast<int>(static_cast<int64_t>(split) * k_blocks / args.splits);
@@ -298,25 +276,20 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
         const int acc = it & 1;
         const uint32_t acc_ph = (static_cast<uint32_t>(it) >> 1) & 1u;
         {
-          GP_T0();
           if (!mbar_wait_bounded(&tempty[acc], acc_ph ^ 1u, args.status, 62)) {
             ok = false;
             break;
           }
-          GP_ADD(3);
         }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BN2);
         for (int kb = kb0; kb < kb1; ++kb) {
           {
-            GP_T0();
             if (!mbar_wait_bounded(&full[s], ph, args.status, 63)) {
               ok = false;
               break;
             }
-            GP_ADD(4);
           }
-          GP_T0();
           tc_fence_after();
           const uint32_t a_addr = smem_u32(smem + s * kStage2);
           const uint32_t b_addr = a_addr + kATile;
@@ -329,7 +302,6 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
             umma_tf32_pair(d_tmem, adesc, bdesc, idesc, (kb != kb0 || ks != 0) ? 1u : 0u);
           }
           umma_commit_pair(&empty[s]);
-          GP_ADD(5);
           if (++s == n_stages) {
             s = 0;
             ph ^= 1u;
@@ -337,17 +309,18 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
         }
         if (ok) umma_commit_pair(&tfull[acc]);
       }
-      GP_FLUSH(3, 6);
     }
     __syncwarp();
   } else {
     // ---------------- epilogue (both CTAs, own 128 rows, all 256 columns) ----------------
+    // A warp may read the tensor-memory lanes of quarter (warp id % 4); the two warps of a quarter
+    // take the first and the second half of the tile's 32-column chunks.
     const int q = warp & 3;
+    const int ew = warp - 2, half = ew >> 2;
     const int row_in_tile = static_cast<int>(rank) * BM2 + q * 32 + lane;
     int it = 0;
     bool ok = true;
-    uint32_t chunk_cnt = 0;   // chunks this warp has fetched gate / up boxes for (SwiGLU backward)
-    GP_DECL();
+    uint32_t chunk_cnt = 0;   // chunks this warp has fetched gate / up boxes for (SwiGLU backward): the parity of its barrier
     for (int unit = pair; unit < num_units && ok; unit += n_pairs, ++it) {
       int mb, nb;
       tile_coords2(unit % num_tiles, m_blocks, n_blocks, mb, nb);
@@ -356,14 +329,11 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
       const int acc = it & 1;
       const uint32_t acc_ph = (static_cast<uint32_t>(it) >> 1) & 1u;
       {
-        GP_T0();
         if (!mbar_wait_bounded(&tfull[acc], acc_ph, args.status, 64)) {
           ok = false;
           break;
         }
-        GP_ADD(6);
       }
-      GP_T0();
       tc_fence_after();
       const int64_t grow = static_cast<int64_t>(mb) * 2 * BM2 + row_in_tile;
       const bool row_ok = grow < args.M;
@@ -371,36 +341,31 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
       const float* xrow = args.aux != nullptr ? args.aux + grow * args.ldc : nullptr;
       const uint32_t t_row = tmem_base + static_cast<uint32_t>(acc * BN2) + (static_cast<uint32_t>(q * 32) << 16);
       if (args.swiglu == 2) {
-        // SwiGLU backward on the accumulator: d(act) stays in registers; gate and up boxes are
-        // fetched by TMA one chunk ahead into one of two box pairs, turned into d(gate) and
-        // d(up) in place and stored from there.
+        // SwiGLU backward on the accumulator: d(act) stays in registers; the gate and up boxes of a
+        // chunk are fetched by TMA into the warp's box pair, turned into d(gate) and d(up) in place
+        // and stored from there (the eight warps of the CTA hide one another's fetch latency).
         const int r0 = mb * 2 * BM2 + static_cast<int>(rank) * BM2 + q * 32;
         int n_ch = (args.N - nb * BN2 + 31) / 32;
         if (n_ch > BN2 / 32) n_ch = BN2 / 32;
-        unsigned char* boxes = epi_stage + q * (4 * kEpiBuf);   // [slot][gate, up]
-        auto fetch = [&](int ch) {   // lane 0 only
-          const uint32_t k = chunk_cnt + static_cast<uint32_t>(ch), slot = k & 1u;
-          const int col = nb * BN2 + ch * 32;
-          uint64_t* bar = &ld_bar[q * 2 + slot];
-          mbar_expect_tx(bar, 2 * kEpiBuf);
-          tma_load_2d(boxes + slot * 2 * kEpiBuf, &tmC, bar, col, r0);
-          tma_load_2d(boxes + slot * 2 * kEpiBuf + kEpiBuf, &tmC, bar, args.N + col, r0);
-        };
-        if (lane == 0) fetch(0);
+        unsigned char* boxes = epi_stage + ew * (2 * kEpiBuf);   // [gate, up]
+        const int ch_end = n_ch < half * 4 + 4 ? n_ch : half * 4 + 4;
 #pragma unroll 1
-        for (int ch = 0; ch < n_ch && ok; ++ch) {
-          const uint32_t k = chunk_cnt + static_cast<uint32_t>(ch), slot = k & 1u;
-          if (ch + 1 < n_ch && lane == 0) {
-            bulk_wait_read<0>();   // the other box pair was last read by the stores of chunk ch-1
-            fetch(ch + 1);
+        for (int ch = half * 4; ch < ch_end && ok; ++ch) {
+          if (lane == 0) {
+            bulk_wait_read<0>();   // the boxes were last read by the stores of the chunk before
+            const int col = nb * BN2 + ch * 32;
+            mbar_expect_tx(&ld_bar[ew], 2 * kEpiBuf);
+            tma_load_2d(boxes, &tmC, &ld_bar[ew], col, r0);
+            tma_load_2d(boxes + kEpiBuf, &tmC, &ld_bar[ew], args.N + col, r0);
           }
           float v[32];
           tmem_ld_32x32(t_row + static_cast<uint32_t>(ch * 32), v);
-          if (!mbar_wait_bounded(&ld_bar[q * 2 + slot], (k >> 1) & 1u, args.status, 65)) {
+          if (!mbar_wait_bounded(&ld_bar[ew], chunk_cnt & 1u, args.status, 65)) {
             ok = false;
             break;
           }
-          unsigned char* bg = boxes + slot * 2 * kEpiBuf + lane * 128;
+          ++chunk_cnt;
+          unsigned char* bg = boxes + lane * 128;
           unsigned char* bu = bg + kEpiBuf;
 #pragma unroll
           for (int c = 0; c < 8; ++c) {
@@ -420,23 +385,21 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
           if (lane == 0) {
             const int col = nb * BN2 + ch * 32;
             if (r0 < args.M) {
-              tma_store_2d(&tmD, boxes + slot * 2 * kEpiBuf, col, r0);
-              tma_store_2d(&tmD, boxes + slot * 2 * kEpiBuf + kEpiBuf, args.N + col, r0);
+              tma_store_2d(&tmD, boxes, col, r0);
+              tma_store_2d(&tmD, boxes + kEpiBuf, args.N + col, r0);
             }
             bulk_commit();
           }
           __syncwarp();
         }
-        chunk_cnt += static_cast<uint32_t>(n_ch);
       } else if (args.swiglu) {
         // columns 0..127 of the accumulator are gate, 128..255 the matching up columns: three boxes
         // per 32-column chunk (gate and up into the packed buffer, silu(gate)*up into the second
-        // output) through the two staging boxes in turn
+        // output) through the warp's staging box
         const int r0 = mb * 2 * BM2 + static_cast<int>(rank) * BM2 + q * 32;
-        int n_sent = 0;
         auto send = [&](const float (&v)[32], const CUtensorMap* map, int col) {
-          unsigned char* buf = epi_stage + (q * 2 + (n_sent & 1)) * kEpiBuf;
-          if (n_sent >= 2 && lane == 0) bulk_wait_read<1>();
+          unsigned char* buf = epi_stage + ew * kEpiBuf;
+          if (lane == 0) bulk_wait_read<0>();   // the box sent before has left
           __syncwarp();
 #pragma unroll
           for (int c = 0; c < 8; ++c)
@@ -448,10 +411,9 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
             if (r0 < args.M) tma_store_2d(map, buf, col, r0);
             bulk_commit();
           }
-          ++n_sent;
         };
 #pragma unroll 1
-        for (int ch = 0; ch < BN2 / 64; ++ch) {
+        for (int ch = half * 2; ch < half * 2 + 2; ++ch) {
           const int col = nb * (BN2 / 2) + ch * 32;
           float g[32], u[32];
           tmem_ld_32x32(t_row + static_cast<uint32_t>(ch * 32), g);
@@ -470,7 +432,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
         // chunk ahead) and coalesced stores of C.
         const int r0 = mb * 2 * BM2 + static_cast<int>(rank) * BM2 + q * 32;
         const int lr = lane >> 3, lc = lane & 7;   // after the transpose: rows j*4+lr, columns lc*4..+3
-        float* stage = reinterpret_cast<float*>(epi_stage + q * 2 * kEpiBuf);
+        float* buf = reinterpret_cast<float*>(epi_stage + ew * kEpiBuf);
         float4 X[8], Xn[8];
         auto fetch = [&](int ch, float4 (&x)[8]) {
           const int col = nb * BN2 + ch * 32 + lc * 4;
@@ -481,15 +443,15 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
                                                   : make_float4(0.f, 0.f, 0.f, 0.f);
           }
         };
-        fetch(0, X);
+        fetch(half * 4, X);
 #pragma unroll 1
-        for (int ch = 0; ch < BN2 / 32; ++ch) {
+        for (int ch = half * 4; ch < half * 4 + 4; ++ch) {
           const int col0 = nb * BN2 + ch * 32;
           if (col0 >= args.N) break;
-          if (ch + 1 < BN2 / 32) fetch(ch + 1, Xn);
+          if (ch + 1 < half * 4 + 4) fetch(ch + 1, Xn);
           float v[32];
           tmem_ld_32x32(t_row + static_cast<uint32_t>(ch * 32), v);
-          float* buf = stage + (ch & 1) * (kEpiBuf / 4);
+          __syncwarp();   // the reads of the chunk before are done
 #pragma unroll
           for (int c = 0; c < 8; ++c)
             *reinterpret_cast<float4*>(buf + lane * 32 + ((c ^ (lane & 7)) << 2)) =
@@ -512,7 +474,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
         }
       } else
 #pragma unroll 1
-      for (int ch = 0; ch < BN2 / 32; ++ch) {
+      for (int ch = half * 4; ch < half * 4 + 4; ++ch) {
         const int col0 = nb * BN2 + ch * 32;
         if (col0 >= args.N) break;
         float v[32];
@@ -520,8 +482,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
         if (args.tma_out) {
           // 32 rows x 32 columns through a 4 KB staging box (128-byte rows, 16-byte chunks XORed
           // with the row number as the map's swizzle expects), then one TMA store / reduce-add.
-          unsigned char* buf = epi_stage + (q * 2 + (ch & 1)) * kEpiBuf;
-          if (ch >= 2 && lane == 0) bulk_wait_read<1>();   // the box sent two chunks ago has left
+          unsigned char* buf = epi_stage + ew * kEpiBuf;
+          if (lane == 0) bulk_wait_read<0>();   // the box sent before has left
           __syncwarp();
 #pragma unroll
           for (int c = 0; c < 8; ++c)
@@ -594,13 +556,9 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
       __syncwarp();
       if (lane == 0) {
         mbar_arrive_leader(&tempty[acc]);
-        if (args.tma_out) bulk_wait_read<0>();   // both staging boxes are free for the next tile
+        if (args.tma_out) bulk_wait_read<0>();   // the staging box is free for the next tile (and before the CTA ends)
       }
-      GP_ADD(7);
     }
-#ifdef CTDK_GEMM_PROBE
-    if (threadIdx.x == 64 && leader) { GP_FLUSH(6, 8); }
-#endif
   }
 
   tc_fence_before();
@@ -621,7 +579,7 @@ int launch2(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc,
   const int tiles = ((args.M + 255) / 256) * (args.swiglu == 1 ? args.N / (BN2 / 2) : (args.N + BN2 - 1) / BN2) * args.splits;
   int pairs = sm_budget() / 2;
   if (tiles < pairs) pairs = tiles;
-  e = launch_pdl(kern, dim3(2 * pairs), dim3(192), kSmem2, stream, ta, tb, tc, td, args);
+  e = launch_pdl(kern, dim3(2 * pairs), dim3(kThreads2), kSmem2, stream, ta, tb, tc, td, args);
   if (e != cudaSuccess) return fail(CTDK_ELAUNCH, "gemm(2cta): launch failed: %s", cudaGetErrorString(e));
   return check_launch("ctdk_gemm(tcgen05, cta pair)");
 }

@@ -244,51 +244,41 @@ __global__ void __launch_bounds__(128) dw_finalize_kernel(const float* __restric
   dw[c] = accumulate ? dw[c] + acc : acc;
 }
 
-// Same column sum for many partial rows: 1024 threads = 32 row groups x 32 columns per CTA, four
-// independent running sums per thread so that four loads are in flight (the pass is latency-bound:
-// a few MB read by H / 32 CTAs).
+// Same column sum for many partial rows: 1024 threads = 32 row groups x 32 columns per CTA. The pass
+// is latency-bound (a few MB read by H / 32 CTAs), so each thread issues sixteen independent loads
+// before it adds them; the order of the additions is fixed. Columns below `split` go to dw0, the
+// rest to dw1 (the QK-Norm pair keeps its two weight gradients in separate tensors).
 __global__ void __launch_bounds__(1024) dw_finalize_wide_kernel(const float* __restrict__ partial,
-                                                                float* __restrict__ dw, int nparts,
-                                                                int H, int accumulate) {
+                                                                float* __restrict__ dw0, float* __restrict__ dw1,
+                                                                int split, int nparts, int H, int accumulate) {
   pdl_launch();
   pdl_wait();
   __shared__ float red[32][33];
   const int cl = threadIdx.x & 31, rg = threadIdx.x >> 5;
   const int c = blockIdx.x * 32 + cl;
-  float a0 = 0.0f, a1 = 0.0f, a2 = 0.0f, a3 = 0.0f;
+  float acc = 0.0f;
   if (c < H) {
     const float* src = partial + c;
-    int p = rg;
-    for (; p + 96 < nparts; p += 128) {
-      a0 += src[static_cast<int64_t>(p) * H];
-      a1 += src[static_cast<int64_t>(p + 32) * H];
-      a2 += src[static_cast<int64_t>(p + 64) * H];
-      a3 += src[static_cast<int64_t>(p + 96) * H];
+    for (int base = rg; base < nparts; base += 32 * 16) {
+      float v[16];
+#pragma unroll
+      for (int u = 0; u < 16; ++u) {
+        const int p = base + 32 * u;
+        v[u] = p < nparts ? src[static_cast<int64_t>(p) * H] : 0.0f;
+      }
+#pragma unroll
+      for (int u = 0; u < 16; u += 4) acc += (v[u] + v[u + 1]) + (v[u + 2] + v[u + 3]);
     }
-    for (; p < nparts; p += 32) a0 += src[static_cast<int64_t>(p) * H];
   }
-  red[rg][cl] = (a0 + a1) + (a2 + a3);
+  red[rg][cl] = acc;
   __syncthreads();
   if (rg == 0 && c < H) {
     float t = 0.0f;
 #pragma unroll
     for (int r = 0; r < 32; ++r) t += red[r][cl];
-    dw[c] = accumulate ? dw[c] + t : t;
+    float* dst = c < split ? dw0 + c : dw1 + (c - split);
+    *dst = accumulate ? *dst + t : t;
   }
-}
-
-// partial rows are [2][D] (q-norm then k-norm); dwq/dwk (+)= column sums.
-__global__ void __launch_bounds__(128) qk_dw_finalize_kernel(const float* __restrict__ partial,
-                                                             float* __restrict__ dwq,
-                                                             float* __restrict__ dwk,
-                                                             int nparts, int D,
-                                                             int accumulate) {
-  const int c = blockIdx.x * blockDim.x + threadIdx.x;
-  if (c >= 2 * D) return;
-  float acc = 0.0f;
-  for (int p = 0; p < nparts; ++p) acc += partial[static_cast<int64_t>(p) * 2 * D + c];
-  float* dst = (c < D) ? dwq + c : dwk + (c - D);
-  *dst = accumulate ? *dst + acc : acc;
 }
 
 // ---------------------------------------------------------------------------------------
@@ -618,7 +608,7 @@ int ctdk_rmsnorm_bwd(const float* dy, const float* x, const float* w, float* dx,
   }
   int rc = check_launch("ctdk_rmsnorm_bwd");
   if (rc != CTDK_OK) return rc;
-  launch_pdl(dw_finalize_wide_kernel, dim3(ceil_div(H, 32)), dim3(1024), 0, s, dw_scratch, dw, grid, H, accumulate_dw);
+  launch_pdl(dw_finalize_wide_kernel, dim3(ceil_div(H, 32)), dim3(1024), 0, s, static_cast<const float*>(dw_scratch), dw, dw, H, grid, H, accumulate_dw);
   prof_end(prof, s);
   return check_launch("ctdk_rmsnorm_bwd(finalize)");
 }
@@ -822,8 +812,8 @@ int ctdk_qk_norm_rope_bwd(float* dqkv, const float* qkv_pre, const float* wq, co
     prof_end(prof, s);
     return rc;
   }
-  qk_dw_finalize_kernel<<<ceil_div(2 * D, 128), 128, 0, s>>>(scratch, dwq, dwk, grid, D,
-                                                             accumulate_dw);
+  launch_pdl(dw_finalize_wide_kernel, dim3(ceil_div(2 * D, 32)), dim3(1024), 0, s, static_cast<const float*>(scratch), dwq, dwk, D, grid,
+             2 * D, accumulate_dw);
   prof_end(prof, s);
   return check_launch("ctdk_qk_norm_rope_bwd(finalize)");
 }
