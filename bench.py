@@ -22,6 +22,7 @@ import argparse
 import ctypes as C
 import json
 import os
+import re
 import subprocess
 import sys
 import threading
@@ -498,6 +499,73 @@ def run_decode(args) -> dict:
             "last_tokens": toks[-4:].tolist()}
 
 
+def run_decode_reference(args) -> dict:
+    """The reference's own generator (tools/ctd_generate/main.cpp:104-184, built unmodified as
+    oracle/_ref/ref_ctd_generate) on the same workload: same random weights written as a safetensors
+    file, the same prompts as requests on its stdin (one process per request, as the tool reads its
+    whole stdin), greedy, 512 new tokens. A step is the prefill plus the decode time the tool logs
+    itself; its weight load is not counted."""
+    import tempfile
+    import torch
+    from emberlm_b200 import engine as E, safetensors_io
+    base = {"impl": "reference", "metric": "decode tokens/s (greedy, KV cache, batch 1)", "unit": "tokens/s", "higher_is_better": True}
+    exe = ROOT / "oracle" / "_ref" / "ref_ctd_generate"
+    if not exe.exists():
+        return {**base, "unavailable": "oracle/_ref/ref_ctd_generate not built (reference sources absent at build time)"}
+    torch.cuda.set_device(0)
+    cfgd = dict(E.PRESETS["qwen3_0_6b"])
+    dec = E.Decoder(E.make_config(**cfgd), max_seq_len=1024)
+    gen = torch.Generator(device="cuda").manual_seed(1234)
+    for (_, v), dcy in zip(dec.named_parameters().items(), dec.layout.decay):
+        v.normal_(0.0, 0.02, generator=gen) if dcy else v.fill_(1.0)
+    prompt_len, new_tokens = 256, 512
+    prompts = [torch.randint(0, cfgd["vocab_size"], (prompt_len,), generator=gen, device="cuda").tolist()
+               for _ in range(args.warmup + args.steps)]
+    t_all = time.perf_counter()
+    with tempfile.TemporaryDirectory() as tmp:
+        path = os.path.join(tmp, "model.safetensors")
+        safetensors_io.save_safetensors([(n, v.cpu().numpy()) for n, v in dec.named_parameters().items()], path)
+        del dec
+        torch.cuda.empty_cache()
+        # One request per process (the tool reads its whole stdin as one request); its own log gives the
+        # prefill and decode times, so the weight load of every process is not counted.
+        secs, last = [], []
+        deadline = time.perf_counter() + 280.0   # the whole arm is bounded: a bench run must end within minutes
+        try:
+            for i, ids in enumerate(prompts):
+                left = deadline - time.perf_counter()
+                if left <= 5:
+                    raise RuntimeError(f"time limit reached after {i} requests")
+                r = subprocess.run([str(exe), "--model", path], capture_output=True, text=True, timeout=left,
+                                   input=json.dumps(dict(input_ids=ids, max_new_tokens=new_tokens, max_seq_len=1024, temperature=0.0)))
+                if r.returncode != 0:
+                    raise RuntimeError("generator exited: " + r.stderr[-300:])
+                out = [json.loads(ln) for ln in r.stdout.strip().splitlines()]
+                got = [m["token"] for m in out if "token" in m]
+                if len(got) != new_tokens:
+                    raise RuntimeError(f"generator returned {len(got)} tokens: {out[-1]}")
+                pre = re.search(r"prefill \(\d+ tok\) in ([0-9.eE+-]+) s", r.stderr)
+                dcd = re.search(r"generated \d+ tok in ([0-9.eE+-]+) s", r.stderr)
+                if not pre or not dcd:
+                    raise RuntimeError("generator log without timings: " + r.stderr[-300:])
+                if i >= args.warmup:
+                    secs.append(float(pre.group(1)) + float(dcd.group(1)))
+                last = got[-4:]
+        except Exception as e:  # noqa: BLE001
+            return {**base, "unavailable": f"reference generator failed: {str(e)[:200]}"}
+    total = sum(secs)
+    value = new_tokens * args.steps / total
+    return {**base, "value": value, "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": total / args.steps * 1e3,
+            "scaling": "replicas only", "vs_baseline": None, "dtype": "fp32 (cuBLAS SGEMM, default math mode)", "data": "synthetic",
+            "config": {"workload": "qwen3_0_6b_decode", "prompt_len": prompt_len, "new_tokens": new_tokens,
+                       "l2": "weights (2.4 GB) larger than L2"},
+            "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": 0, "kind": "reference",
+                             "sample": "the reference's own generator (CUDA build, one B200; it has no CPU path), prefill + decode seconds from its log; "
+                                       f"whole run {time.perf_counter() - t_all:.0f} s incl. writing and loading the weights"},
+            "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "last_tokens": last}
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -515,7 +583,7 @@ def main():
     if args.warmup < 3 and args.impl == "ours":
         print(f"note: --warmup {args.warmup} < 3; timing rules ask for at least 3", file=sys.stderr)
     if args.workload == "qwen3_0_6b_decode":
-        out = run_decode(args) if args.impl == "ours" else {"impl": "reference", "unavailable": "decode arm not wired to the reference harness"}
+        out = run_decode(args) if args.impl == "ours" else run_decode_reference(args)
     else:
         out = run_reference(args) if args.impl == "reference" else run_ours(args)
     if out is not None:

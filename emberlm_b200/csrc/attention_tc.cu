@@ -60,22 +60,6 @@ __device__ __forceinline__ float fast_exp2(float x) {
 // conversion pipe.
 __device__ __forceinline__ uint32_t tf32_rna_bits(float x) { return __float_as_uint(x) + 0x1000u; }
 
-#ifdef CTDK_ATTN_PROBE
-__device__ long long g_attn_probe[16];
-#define PROBE_DECL() long long _acc[10] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0}
-#define PROBE_T0() const long long _pt0 = clock64()
-#define PROBE_ADD(i) _acc[i] += clock64() - _pt0
-#define PROBE_CNT(i) _acc[i] += 1
-#define PROBE_IF(c) if (c)
-#define PROBE_FLUSH(lo, hi) for (int _i = lo; _i < hi; ++_i) atomicAdd(reinterpret_cast<unsigned long long*>(&g_attn_probe[_i]), static_cast<unsigned long long>(_acc[_i]))
-#else
-#define PROBE_DECL()
-#define PROBE_T0()
-#define PROBE_ADD(i)
-#define PROBE_CNT(i)
-#define PROBE_IF(c) if (false)
-#define PROBE_FLUSH(lo, hi)
-#endif
 
 struct FwdArgs {
   float* out;
@@ -226,15 +210,12 @@ __global__ void __launch_bounds__(192, FwdCfg<D>::kCtasPerSm)
       const uint64_t qd_ = make_smem_desc(smem_u32(q_s), 16, 1024, kLayoutSw128);
       uint32_t g0 = 0, n_it = 0;
       bool ok = true;
-      PROBE_DECL();
       for (int it = blockIdx.x; it < args.n_items && ok; it += gridDim.x, ++n_it) {
         const FwdItem w = fwd_item(args, it);
         auto issue_s = [&](int j) {
           const uint32_t g = g0 + static_cast<uint32_t>(j), s = g & 1u;
           {
-            PROBE_T0();
             if (!mbar_wait_bounded_w(&k_full[s], (g >> 1) & 1u, args.status, 22)) return false;
-            PROBE_ADD(1);
           }
           tc_fence_after();
           const uint64_t kd = make_smem_desc(k_base + s * C::kKBytes, 16, 1024, kLayoutSw128);
@@ -249,9 +230,7 @@ __global__ void __launch_bounds__(192, FwdCfg<D>::kCtasPerSm)
           return true;
         };
         {
-          PROBE_T0();
           if (!mbar_wait_bounded_w(q_full, n_it & 1u, args.status, 21)) break;
-          PROBE_ADD(0);
         }
         tc_fence_after();
         // Tensor-pipe order: S(0) S(1) | PV(0) S(2) | PV(1) S(3) | ... S(j+2) reuses the columns
@@ -261,14 +240,10 @@ __global__ void __launch_bounds__(192, FwdCfg<D>::kCtasPerSm)
         for (int j = 0; j < w.n_steps && ok; ++j) {
           const uint32_t g = g0 + static_cast<uint32_t>(j), s = g & 1u, ph = (g >> 1) & 1u;
           {
-            PROBE_T0();
             if (!mbar_wait_bounded_w(&p_ready[s], ph, args.status, 23)) { ok = false; break; }
-            PROBE_ADD(2);
           }
           {
-            PROBE_T0();
             if (!mbar_wait_bounded_w(&v_full[s], ph, args.status, 24)) { ok = false; break; }
-            PROBE_ADD(3);
           }
           tc_fence_after();
           // A: 8 probability columns of tensor memory; B: 8 key rows (two 4-row swizzle
@@ -286,7 +261,6 @@ __global__ void __launch_bounds__(192, FwdCfg<D>::kCtasPerSm)
         }
         g0 += static_cast<uint32_t>(w.n_steps);
       }
-      if (lane == 0) { PROBE_FLUSH(0, 4); }
     }
     __syncwarp();
   } else {
@@ -300,7 +274,6 @@ __global__ void __launch_bounds__(192, FwdCfg<D>::kCtasPerSm)
     const uint32_t to = tm_o + lane_off;
     uint32_t g0 = 0, n_done = 0;
     bool ok = true;
-    PROBE_DECL();
     for (int it = blockIdx.x; it < args.n_items && ok; it += gridDim.x, ++n_done) {
       const FwdItem w = fwd_item(args, it);
       const int row = w.q0 + qd * 32 + lane;   // query position inside the sequence
@@ -308,11 +281,8 @@ __global__ void __launch_bounds__(192, FwdCfg<D>::kCtasPerSm)
       for (int j = 0; j < w.n_steps && ok; ++j) {
         const uint32_t g = g0 + static_cast<uint32_t>(j), s = g & 1u;
         {
-          PROBE_T0();
           if (!mbar_wait_bounded(&s_full[s], (g >> 1) & 1u, args.status, 31)) { ok = false; break; }
-          PROBE_IF(threadIdx.x == 64) PROBE_ADD(4);
         }
-        PROBE_T0();
         tc_fence_after();
         const uint32_t ts = tm_s(g) + lane_off;
         float a[64];
@@ -374,7 +344,6 @@ __global__ void __launch_bounds__(192, FwdCfg<D>::kCtasPerSm)
         tc_fence_before();
         mbar_arrive(&p_ready[s]);
         l_run += s0 + s1;
-        PROBE_IF(threadIdx.x == 64) { PROBE_ADD(5); PROBE_CNT(8); }
       }
       g0 += static_cast<uint32_t>(w.n_steps);
       // The item's last P V, on a barrier of its own with one phase per item: pv_full cannot be
@@ -382,11 +351,8 @@ __global__ void __launch_bounds__(192, FwdCfg<D>::kCtasPerSm)
       // parity wait cannot tell them apart. The next item's first P V cannot start before these
       // threads have read O and arrived at its p_ready.
       {
-        PROBE_T0();
         if (!ok || !mbar_wait_bounded(o_full, n_done & 1u, args.status, 33)) { ok = false; break; }
-        PROBE_IF(threadIdx.x == 64) PROBE_ADD(6);
       }
-      PROBE_T0();
       tc_fence_after();
       // Normalised output rows go through a small per-warp staging area (16 rows x 32 floats,
       // 128-byte rows with the 16-byte chunks XORed by the row number) so that each store
@@ -427,9 +393,7 @@ __global__ void __launch_bounds__(192, FwdCfg<D>::kCtasPerSm)
       tc_fence_before();
       if (row < args.T)
         args.lse[(static_cast<int64_t>(w.b) * args.H + w.h) * args.T + row] = (m_ref + log2f(l_run)) * kLn2f;
-      PROBE_IF(threadIdx.x == 64) { PROBE_ADD(7); PROBE_CNT(9); }
     }
-    PROBE_IF(threadIdx.x == 64) PROBE_FLUSH(4, 10);
   }
 
   tc_fence_before();

@@ -50,20 +50,6 @@ __device__ __forceinline__ float ex2f(float x) {
 // Round-to-nearest to TF32 as an integer add (the tensor core ignores the 13 low mantissa bits).
 __device__ __forceinline__ uint32_t rna_bits(float x) { return __float_as_uint(x) + 0x1000u; }
 
-#ifdef CTDK_ATTN_PROBE
-__device__ long long g_bwd_probe[32];
-#define BP_DECL() long long _acc[12] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0}
-#define BP_T0() const long long _pt0 = clock64()
-#define BP_ADD(i) _acc[i] += clock64() - _pt0
-#define BP_CNT(i) _acc[i] += 1
-#define BP_FLUSH(base, lo, hi) for (int _i = lo; _i < hi; ++_i) atomicAdd(reinterpret_cast<unsigned long long*>(&g_bwd_probe[base + _i]), static_cast<unsigned long long>(_acc[_i]))
-#else
-#define BP_DECL()
-#define BP_T0()
-#define BP_ADD(i)
-#define BP_CNT(i)
-#define BP_FLUSH(base, lo, hi)
-#endif
 
 struct Bwd64Args {
   const float* lse;
@@ -244,15 +230,12 @@ __global__ void __launch_bounds__(320, 1)
       const uint32_t stages_addr = smem_u32(stages);
       uint32_t g0 = 0, n_it = 0;
       bool ok = true;
-      BP_DECL();
       for (int it = blockIdx.x; it < args.n_items && ok; it += gridDim.x, ++n_it) {
         const DqItem w = dq_item(args, it);
         auto issue_sdp = [&](int j) {
           const uint32_t g = g0 + static_cast<uint32_t>(j), st = g % kDqStages;
           {
-            BP_T0();
             if (!mbar_wait_bounded_w(&kv_full[st], (g / kDqStages) & 1u, args.status, 44)) return false;
-            BP_ADD(1);
           }
           tc_fence_after();
           const uint64_t kd = make_smem_desc(stages_addr + st * kDqStageBytes, 16, 1024, kLayoutSw128);
@@ -271,9 +254,7 @@ __global__ void __launch_bounds__(320, 1)
           return true;
         };
         {
-          BP_T0();
           if (!mbar_wait_bounded_w(qdo_ready, n_it & 1u, args.status, 43)) break;
-          BP_ADD(0);
         }
         tc_fence_after();
         // Tensor-pipe order: SdP(0) SdP(1) | dQ(0) SdP(2) | dQ(1) SdP(3) | ...
@@ -282,14 +263,10 @@ __global__ void __launch_bounds__(320, 1)
         for (int j = 0; j < w.n_steps && ok; ++j) {
           const uint32_t g = g0 + static_cast<uint32_t>(j), st = g % kDqStages;
           {
-            BP_T0();
             if (!mbar_wait_bounded_w(&ds_ready[g & 1u], (g >> 1) & 1u, args.status, 45)) { ok = false; break; }
-            BP_ADD(2);
           }
           {
-            BP_T0();
             if (!mbar_wait_bounded_w(&km_full[st], (g / kDqStages) & 1u, args.status, 46)) { ok = false; break; }
-            BP_ADD(3);
           }
           tc_fence_after();
           const uint64_t kmd =
@@ -305,7 +282,6 @@ __global__ void __launch_bounds__(320, 1)
         }
         g0 += static_cast<uint32_t>(w.n_steps);
       }
-      if (lane == 0) { BP_FLUSH(0, 0, 4); }
     }
     __syncwarp();
   } else {
@@ -319,25 +295,19 @@ __global__ void __launch_bounds__(320, 1)
     float* stg = reinterpret_cast<float*>(o_stage + cw * 2048);
     uint32_t g0 = 0, n_it = 0;
     bool ok = true;
-    BP_DECL();
     const int64_t RS = static_cast<int64_t>(args.H + 2 * args.Hk) * D;
     // Reads item n's finished dQ out of its accumulator and stores it. Runs after the NEXT item's
     // Q / dO have been handed to the MMA warp, i.e. while that item's first S / dP MMAs execute.
     auto epilogue = [&](const DqItem& w, uint32_t n) {
       {
-        BP_T0();
         if (!mbar_wait_bounded(dq_done, n & 1u, args.status, 49)) return false;
-        BP_ADD(8);
       }
-      BP_T0();
       tc_fence_after();
       float v[32];
       tmem_ld_32x32(tm_dq(n) + lane_off + static_cast<uint32_t>(half * 32), v);
       float* dst = args.dqkv + (static_cast<int64_t>(w.b) * args.T + w.q0 + qd * 32) * RS + w.h * D + half * 32;
       store_block_32x32(stg, v, dst, RS, args.T - (w.q0 + qd * 32), lane);
       tc_fence_before();
-      BP_ADD(9);
-      BP_CNT(11);
       return true;
     };
     DqItem prev{};
@@ -351,17 +321,13 @@ __global__ void __launch_bounds__(320, 1)
       const float neg_dls = row_ok ? -args.delta[lbase + row] * args.scale : 0.0f;
       // Q (first warp of the pair) or dO (second) row of this thread: shared -> tensor memory
       {
-        BP_T0();
         if (!mbar_wait_bounded(land_full, n_it & 1u, args.status, 47)) { ok = false; break; }
-        BP_ADD(4);
       }
       {
-        BP_T0();
         float v[64];
         load_row_sw128(half == 0 ? q_land : do_land, qd * 32 + lane, v);
         tmem_st_32x64((half == 0 ? tm_qa : tm_doa) + lane_off, *reinterpret_cast<uint32_t(*)[64]>(v));
         tmem_wait_st();
-        BP_ADD(5);
       }
       tc_fence_before();
       mbar_arrive(qdo_ready);
@@ -369,11 +335,8 @@ __global__ void __launch_bounds__(320, 1)
       for (int j = 0; j < w.n_steps && ok; ++j) {
         const uint32_t g = g0 + static_cast<uint32_t>(j);
         {
-          BP_T0();
           if (!mbar_wait_bounded(&sdp_full[g & 1u], (g >> 1) & 1u, args.status, 48)) { ok = false; break; }
-          BP_ADD(6);
         }
-        BP_T0();
         tc_fence_after();
         const uint32_t ts = tm_s(g) + lane_off + static_cast<uint32_t>(half * 32);
         const uint32_t tp = tm_dp(g) + lane_off + static_cast<uint32_t>(half * 32);
@@ -402,17 +365,12 @@ __global__ void __launch_bounds__(320, 1)
         tmem_wait_st();
         tc_fence_before();
         mbar_arrive(&ds_ready[g & 1u]);
-        BP_ADD(7);
-        BP_CNT(10);
       }
       g0 += static_cast<uint32_t>(w.n_steps);
       prev = w;
       have_prev = true;
     }
     if (ok && have_prev) epilogue(prev, n_it - 1u);
-#ifdef CTDK_ATTN_PROBE
-    if (threadIdx.x == 64) { BP_FLUSH(0, 4, 12); }
-#endif
   }
 
   tc_fence_before();
@@ -579,7 +537,6 @@ __global__ void __launch_bounds__(320, 1)
       const uint32_t stages_addr = smem_u32(stages);
       uint32_t g0 = 0, r0 = 0, n_it = 0;
       bool ok = true;
-      BP_DECL();
       for (;; ++n_it) {
         if (!mbar_wait_bounded_w(&iq_full[n_it & 1u], (n_it >> 1) & 1u, args.status, 60)) break;
         const int it = item_q[n_it & 1u];
@@ -590,9 +547,7 @@ __global__ void __launch_bounds__(320, 1)
         auto issue_sdp = [&](int u) {
           const uint32_t g = g0 + static_cast<uint32_t>(u), r = r0 + 1u + static_cast<uint32_t>(u), st = r % kKvStages;
           {
-            BP_T0();
             if (!mbar_wait_bounded_w(&qk_full[st], (r / kKvStages) & 1u, args.status, 54)) return false;
-            BP_ADD(1);
           }
           tc_fence_after();
           const uint64_t qd_ = make_smem_desc(stages_addr + st * kKvStageBytes, 16, 1024, kLayoutSw128);
@@ -611,9 +566,7 @@ __global__ void __launch_bounds__(320, 1)
           return true;
         };
         {
-          BP_T0();
           if (!mbar_wait_bounded_w(kvt_ready, n_it & 1u, args.status, 53)) break;
-          BP_ADD(0);
         }
         tc_fence_after();
         if (lane == 0) {   // K and V sit in tensor memory: their ring entry is free again
@@ -626,14 +579,10 @@ __global__ void __launch_bounds__(320, 1)
         for (int u = 0; u < w.n_units && ok; ++u) {
           const uint32_t g = g0 + static_cast<uint32_t>(u), r = r0 + 1u + static_cast<uint32_t>(u), st = r % kKvStages;
           {
-            BP_T0();
             if (!mbar_wait_bounded_w(&pds_ready[g & 1u], (g >> 1) & 1u, args.status, 55)) { ok = false; break; }
-            BP_ADD(2);
           }
           {
-            BP_T0();
             if (!mbar_wait_bounded_w(&qm_full[st], (r / kKvStages) & 1u, args.status, 56)) { ok = false; break; }
-            BP_ADD(3);
           }
           tc_fence_after();
           const uint64_t qmd =
@@ -655,7 +604,6 @@ __global__ void __launch_bounds__(320, 1)
         g0 += static_cast<uint32_t>(w.n_units);
         r0 += static_cast<uint32_t>(w.n_units) + 1u;
       }
-      if (lane == 0) { BP_FLUSH(16, 0, 4); }
     }
     __syncwarp();
   } else {
@@ -670,7 +618,6 @@ __global__ void __launch_bounds__(320, 1)
     float* stg = reinterpret_cast<float*>(o_stage + cw * 2048);
     uint32_t g0 = 0, r0 = 0, n_it = 0;
     bool ok = true;
-    BP_DECL();
     for (;; ++n_it) {
       if (!mbar_wait_bounded(&iq_full[n_it & 1u], (n_it >> 1) & 1u, args.status, 61)) break;
       const int it = item_q[n_it & 1u];
@@ -695,14 +642,12 @@ __global__ void __launch_bounds__(320, 1)
       // K (first warp of the pair) or V (second) row of this thread: shared -> tensor memory.
       // The tensor-memory copies of the previous item are free: its last MMA was awaited below.
       {
-        BP_T0();
         const uint32_t st = r0 % kKvStages, ph = (r0 / kKvStages) & 1u;
         if (!mbar_wait_bounded(half == 0 ? &qk_full[st] : &qm_full[st], ph, args.status, 62)) { ok = false; break; }
         float v[64];
         load_row_sw128(stages + st * kKvStageBytes + half * kRowTileBytes, qd * 32 + lane, v);
         tmem_st_32x64((half == 0 ? tm_ka : tm_va) + lane_off, *reinterpret_cast<uint32_t(*)[64]>(v));
         tmem_wait_st();
-        BP_ADD(5);
       }
       tc_fence_before();
       mbar_arrive(kvt_ready);
@@ -723,16 +668,11 @@ __global__ void __launch_bounds__(320, 1)
         }
         next_const = fetch_const(u + 1);
         {
-          BP_T0();
           if (!mbar_wait_bounded(&const_full[cb], (g / 3u) & 1u, args.status, 59)) { ok = false; break; }
-          BP_ADD(4);
         }
         {
-          BP_T0();
           if (!mbar_wait_bounded(&sdp_full[g & 1u], (g >> 1) & 1u, args.status, 57)) { ok = false; break; }
-          BP_ADD(6);
         }
-        BP_T0();
         tc_fence_after();
         const uint32_t ts = tm_s(g) + lane_off + static_cast<uint32_t>(half * 32);
         const uint32_t tp = tm_dp(g) + lane_off + static_cast<uint32_t>(half * 32);
@@ -780,17 +720,12 @@ __global__ void __launch_bounds__(320, 1)
         tmem_wait_st();
         tc_fence_before();
         mbar_arrive(&pds_ready[g & 1u]);
-        BP_ADD(7);
-        BP_CNT(10);
       }
       g0 += static_cast<uint32_t>(w.n_units);
       r0 += static_cast<uint32_t>(w.n_units) + 1u;
       {
-        BP_T0();
         if (!ok || !mbar_wait_bounded(done_bar, n_it & 1u, args.status, 58)) { ok = false; break; }
-        BP_ADD(8);
       }
-      BP_T0();
       tc_fence_after();
       {
         float* rowp = args.dqkv + (static_cast<int64_t>(w.b) * args.T + w.k0 + qd * 32) * RS;
@@ -802,12 +737,7 @@ __global__ void __launch_bounds__(320, 1)
         store_block_32x32(stg, v, rowp + col_k + half * 32, RS, rows_left, lane);
       }
       tc_fence_before();
-      BP_ADD(9);
-      BP_CNT(11);
     }
-#ifdef CTDK_ATTN_PROBE
-    if (threadIdx.x == 64) { BP_FLUSH(16, 4, 12); }
-#endif
   }
 
   tc_fence_before();

@@ -47,6 +47,9 @@ struct Gemm2Args {
                   //    output act = silu(gate) * up [M, N]: each tile holds 128 gate and the matching 128 up columns
                   // 2: the product is d(act) [M, N]; the epilogue reads gate|up [M, 2N] through map C and
                   //    writes d(gate)|d(up) [M, 2N] through map D (SwiGLU backward), d(act) is never stored
+  int narrow;     // 1: the plain epilogue (store / add of the bare accumulator) is run by the first warp of each lane
+                  //    quarter through both staging boxes of its pair, which measured ~1 % faster than eight warps with
+                  //    one box each; the epilogues that compute (SwiGLU, +residual) use all eight warps
   int stages;     // operand ring depth: 6, or 5 when the epilogue needs 64 KB of staging (swiglu == 2)
   int* status;
 };
@@ -474,7 +477,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads2, 1)
         }
       } else
 #pragma unroll 1
-      for (int ch = half * 4; ch < half * 4 + 4; ++ch) {
+      for (int ch = args.narrow ? half * 8 : half * 4; ch < (args.narrow ? 8 : half * 4 + 4); ++ch) {
         const int col0 = nb * BN2 + ch * 32;
         if (col0 >= args.N) break;
         float v[32];
@@ -482,8 +485,11 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads2, 1)
         if (args.tma_out) {
           // 32 rows x 32 columns through a 4 KB staging box (128-byte rows, 16-byte chunks XORed
           // with the row number as the map's swizzle expects), then one TMA store / reduce-add.
-          unsigned char* buf = epi_stage + ew * kEpiBuf;
-          if (lane == 0) bulk_wait_read<0>();   // the box sent before has left
+          unsigned char* buf = epi_stage + (args.narrow ? ew + 4 * (ch & 1) : ew) * kEpiBuf;
+          if (lane == 0) {
+            if (!args.narrow) bulk_wait_read<0>();   // the box sent before has left
+            else if (ch >= 2) bulk_wait_read<1>();
+          }
           __syncwarp();
 #pragma unroll
           for (int c = 0; c < 8; ++c)
@@ -592,7 +598,7 @@ int launch2(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc,
 int gemm_tcgen05_2cta(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, bool a_mn, bool b_mn,
                       bool a3d, bool b3d, int tma_out, float* C, const float* aux, int64_t ldc, int M, int N, int K,
                       int epilogue, int vec_ok, int splits, int* status, cudaStream_t stream) {
-  Gemm2Args args{C, aux, ldc, M, N, K, epilogue, vec_ok, splits, a3d ? 1 : 0, b3d ? 1 : 0, tma_out, 0, kStages2, status};
+  Gemm2Args args{C, aux, ldc, M, N, K, epilogue, vec_ok, splits, a3d ? 1 : 0, b3d ? 1 : 0, tma_out, 0, 1, kStages2, status};
   if (!a_mn && !b_mn) return launch2<false, false>(ta, tb, tc, tc, args, stream);
   if (!a_mn && b_mn) return launch2<false, true>(ta, tb, tc, tc, args, stream);
   if (a_mn && !b_mn) return launch2<true, false>(ta, tb, tc, tc, args, stream);
@@ -604,7 +610,7 @@ int gemm_tcgen05_2cta(const CUtensorMap& ta, const CUtensorMap& tb, const CUtens
 // outputs, {32, 32} boxes. N must be a multiple of 128.
 int gemm_tcgen05_2cta_swiglu(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tgu, const CUtensorMap& tact,
                              int M, int N, int K, int* status, cudaStream_t stream) {
-  Gemm2Args args{nullptr, nullptr, 0, M, N, K, CTDK_EPI_STORE, 1, 1, 0, 0, 1, 1, kStages2, status};
+  Gemm2Args args{nullptr, nullptr, 0, M, N, K, CTDK_EPI_STORE, 1, 1, 0, 0, 1, 1, 0, kStages2, status};
   return launch2<false, false>(ta, tb, tgu, tact, args, stream);
 }
 
@@ -612,7 +618,7 @@ int gemm_tcgen05_2cta_swiglu(const CUtensorMap& ta, const CUtensorMap& tb, const
 // accumulator; tgu: gate|up [M, 2N] for loading, tdgu: d(gate)|d(up) [M, 2N] for storing, {32, 32} boxes.
 int gemm_tcgen05_2cta_swiglu_bwd(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tgu, const CUtensorMap& tdgu,
                                  bool b3d, int M, int N, int K, int* status, cudaStream_t stream) {
-  Gemm2Args args{nullptr, nullptr, 0, M, N, K, CTDK_EPI_STORE, 1, 1, 0, b3d ? 1 : 0, 1, 2, kStages2 - 1, status};
+  Gemm2Args args{nullptr, nullptr, 0, M, N, K, CTDK_EPI_STORE, 1, 1, 0, b3d ? 1 : 0, 1, 2, 0, kStages2 - 1, status};
   return launch2<false, true>(ta, tb, tgu, tdgu, args, stream);
 }
 
