@@ -154,57 +154,54 @@ __global__ void __launch_bounds__(320, 1)
     }
     __syncwarp();
   } else if (warp == 1) {
-    if (lane == 0) {
-      const uint32_t idesc_s = idesc_b(false, TKB);
-      const uint32_t idesc_dq = idesc_b(true, D);
-      bool ok = mbar_wait_bounded(q_full, 0, args.status, 43);
+    // The whole warp runs this role converged; one elected lane issues each MMA / commit (issued
+    // from inside a one-lane branch an MMA costs the thread ~80 cycles, more than its pipe time).
+    const uint32_t idesc_s = idesc_b(false, TKB);
+    const uint32_t idesc_dq = idesc_b(true, D);
+    bool ok = mbar_wait_bounded_w(q_full, 0, args.status, 43);
+    tc_fence_after();
+    const uint64_t qd = make_smem_desc(smem_u32(q_s), 16, 1024, kLayoutSw128);
+    const uint64_t dod = make_smem_desc(smem_u32(do_s), 16, 1024, kLayoutSw128);
+    auto issue_sdp = [&](int j) {
+      const int s = j % NB;
+      if (!mbar_wait_bounded_w(&kv_full[s], static_cast<uint32_t>(j / NB) & 1u, args.status, 44)) return false;
       tc_fence_after();
-      const uint32_t q_addr = smem_u32(q_s), do_addr = smem_u32(do_s);
-      auto issue_sdp = [&](int j) {
-        const int s = j % NB;
-        if (!mbar_wait_bounded(&kv_full[s], static_cast<uint32_t>(j / NB) & 1u, args.status, 44)) return false;
-        tc_fence_after();
-        const uint32_t k_addr = smem_u32(kk_s + s * C::kKeyTile), v_addr = smem_u32(v_s + s * C::kKeyTile);
+      const uint64_t kd = make_smem_desc(smem_u32(kk_s + s * C::kKeyTile), 16, 1024, kLayoutSw128);
+      const uint64_t vd = make_smem_desc(smem_u32(v_s + s * C::kKeyTile), 16, 1024, kLayoutSw128);
+      const uint32_t ts = tm_s(s), tp = tm_dp(s);
 #pragma unroll
-        for (int ks = 0; ks < D / 8; ++ks) {
-          const uint32_t ao = static_cast<uint32_t>((ks >> 2) * kRowChunk + (ks & 3) * 32);
-          const uint32_t bo = static_cast<uint32_t>((ks >> 2) * kKeyChunk + (ks & 3) * 32);
-          umma_tf32(tm_s(s), make_smem_desc(q_addr + ao, 16, 1024, kLayoutSw128),
-                    make_smem_desc(k_addr + bo, 16, 1024, kLayoutSw128), idesc_s, ks != 0 ? 1u : 0u);
-        }
+      for (int ks = 0; ks < D / 8; ++ks)
+        umma_tf32_w(ts, qd + static_cast<uint64_t>(((ks >> 2) * kRowChunk + (ks & 3) * 32) >> 4),
+                    kd + static_cast<uint64_t>(((ks >> 2) * kKeyChunk + (ks & 3) * 32) >> 4), idesc_s, ks != 0 ? 1u : 0u);
 #pragma unroll
-        for (int ks = 0; ks < D / 8; ++ks) {
-          const uint32_t ao = static_cast<uint32_t>((ks >> 2) * kRowChunk + (ks & 3) * 32);
-          const uint32_t bo = static_cast<uint32_t>((ks >> 2) * kKeyChunk + (ks & 3) * 32);
-          umma_tf32(tm_dp(s), make_smem_desc(do_addr + ao, 16, 1024, kLayoutSw128),
-                    make_smem_desc(v_addr + bo, 16, 1024, kLayoutSw128), idesc_s, ks != 0 ? 1u : 0u);
-        }
-        umma_commit(&kv_empty[s]);
-        umma_commit(&sdp_full[s]);
-        return true;
-      };
-      auto issue_dq = [&](int jj) {
-        const int s = jj % NB;
-        const uint32_t ph = static_cast<uint32_t>(jj / NB) & 1u;
-        if (!mbar_wait_bounded(&ds_ready[s], ph, args.status, 45)) return false;
-        if (!mbar_wait_bounded(&km_full[s], ph, args.status, 46)) return false;
-        tc_fence_after();
-        const uint32_t k_addr = smem_u32(km_s + s * C::kKeyTile);
+      for (int ks = 0; ks < D / 8; ++ks)
+        umma_tf32_w(tp, dod + static_cast<uint64_t>(((ks >> 2) * kRowChunk + (ks & 3) * 32) >> 4),
+                    vd + static_cast<uint64_t>(((ks >> 2) * kKeyChunk + (ks & 3) * 32) >> 4), idesc_s, ks != 0 ? 1u : 0u);
+      umma_commit_w(&kv_empty[s]);
+      umma_commit_w(&sdp_full[s]);
+      return true;
+    };
+    auto issue_dq = [&](int jj) {
+      const int s = jj % NB;
+      const uint32_t ph = static_cast<uint32_t>(jj / NB) & 1u;
+      if (!mbar_wait_bounded_w(&ds_ready[s], ph, args.status, 45)) return false;
+      if (!mbar_wait_bounded_w(&km_full[s], ph, args.status, 46)) return false;
+      tc_fence_after();
+      const uint64_t kmd = make_smem_desc(smem_u32(km_s + s * C::kKeyTile), kKeyChunk, 512, kLayoutSw128Base32);
+      const uint32_t ts = tm_s(s);
 #pragma unroll
-        for (int ks = 0; ks < TKB / 8; ++ks)
-          umma_tf32_ta(tm_dq, tm_s(s) + static_cast<uint32_t>(ks * 8),
-                       make_smem_desc(k_addr + ks * 1024, kKeyChunk, 512, kLayoutSw128Base32), idesc_dq,
+      for (int ks = 0; ks < TKB / 8; ++ks)
+        umma_tf32_ta_w(tm_dq, ts + static_cast<uint32_t>(ks * 8), kmd + static_cast<uint64_t>((ks * 1024) >> 4), idesc_dq,
                        (jj != 0 || ks != 0) ? 1u : 0u);
-        umma_commit(&km_empty[s]);
-        return true;
-      };
-      for (int j = 0; j <= n_tiles && ok; ++j) {
-        if (NB == 2 && j < n_tiles) ok = issue_sdp(j);
-        if (ok && j >= 1) ok = issue_dq(j - 1);
-        if (NB == 1 && ok && j < n_tiles) ok = issue_sdp(j);
-      }
-      umma_commit(dq_full);
+      umma_commit_w(&km_empty[s]);
+      return true;
+    };
+    for (int j = 0; j <= n_tiles && ok; ++j) {
+      if (NB == 2 && j < n_tiles) ok = issue_sdp(j);
+      if (ok && j >= 1) ok = issue_dq(j - 1);
+      if (NB == 1 && ok && j < n_tiles) ok = issue_sdp(j);
     }
+    umma_commit_w(dq_full);
     __syncwarp();
   } else {
     // 8 compute warps: warp pair (w, w+4) shares a lane quarter, each takes half of the keys.
@@ -452,62 +449,58 @@ __global__ void __launch_bounds__(DkvCfg<D, TQB, NB>::kThreads, 1)
     }
     __syncwarp();
   } else if (warp == 1) {
-    if (lane == 0) {
-      const uint32_t idesc_s = idesc_b(false, TQB);
-      const uint32_t idesc_d = idesc_b(true, D);
-      bool ok = mbar_wait_bounded(kv_full, 0, args.status, 53);
+    // converged-warp issue, as in the dQ kernel
+    const uint32_t idesc_s = idesc_b(false, TQB);
+    const uint32_t idesc_d = idesc_b(true, D);
+    bool ok = mbar_wait_bounded_w(kv_full, 0, args.status, 53);
+    tc_fence_after();
+    const uint64_t kd = make_smem_desc(smem_u32(k_s), 16, 1024, kLayoutSw128);
+    const uint64_t vd = make_smem_desc(smem_u32(v_s), 16, 1024, kLayoutSw128);
+    auto issue_sdp = [&](int u) {
+      const int s = u % NB;
+      if (!mbar_wait_bounded_w(&qk_full[s], static_cast<uint32_t>(u / NB) & 1u, args.status, 54)) return false;
       tc_fence_after();
-      const uint32_t k_addr = smem_u32(k_s), v_addr = smem_u32(v_s);
-      auto issue_sdp = [&](int u) {
-        const int s = u % NB;
-        if (!mbar_wait_bounded(&qk_full[s], static_cast<uint32_t>(u / NB) & 1u, args.status, 54)) return false;
-        tc_fence_after();
-        const uint32_t q_addr = smem_u32(qk_s + s * C::kQTile), do_addr = smem_u32(dok_s + s * C::kQTile);
+      const uint64_t qd_ = make_smem_desc(smem_u32(qk_s + s * C::kQTile), 16, 1024, kLayoutSw128);
+      const uint64_t dod = make_smem_desc(smem_u32(dok_s + s * C::kQTile), 16, 1024, kLayoutSw128);
+      const uint32_t ts = tm_s(s), tp = tm_dp(s);
 #pragma unroll
-        for (int ks = 0; ks < D / 8; ++ks) {
-          const uint32_t ao = static_cast<uint32_t>((ks >> 2) * kKeyChunk + (ks & 3) * 32);
-          const uint32_t bo = static_cast<uint32_t>((ks >> 2) * kQChunk + (ks & 3) * 32);
-          umma_tf32(tm_s(s), make_smem_desc(k_addr + ao, 16, 1024, kLayoutSw128),
-                    make_smem_desc(q_addr + bo, 16, 1024, kLayoutSw128), idesc_s, ks != 0 ? 1u : 0u);
-        }
+      for (int ks = 0; ks < D / 8; ++ks)
+        umma_tf32_w(ts, kd + static_cast<uint64_t>(((ks >> 2) * kKeyChunk + (ks & 3) * 32) >> 4),
+                    qd_ + static_cast<uint64_t>(((ks >> 2) * kQChunk + (ks & 3) * 32) >> 4), idesc_s, ks != 0 ? 1u : 0u);
 #pragma unroll
-        for (int ks = 0; ks < D / 8; ++ks) {
-          const uint32_t ao = static_cast<uint32_t>((ks >> 2) * kKeyChunk + (ks & 3) * 32);
-          const uint32_t bo = static_cast<uint32_t>((ks >> 2) * kQChunk + (ks & 3) * 32);
-          umma_tf32(tm_dp(s), make_smem_desc(v_addr + ao, 16, 1024, kLayoutSw128),
-                    make_smem_desc(do_addr + bo, 16, 1024, kLayoutSw128), idesc_s, ks != 0 ? 1u : 0u);
-        }
-        umma_commit(&qk_empty[s]);
-        umma_commit(&sdp_full[s]);
-        return true;
-      };
-      auto issue_dvdk = [&](int u) {
-        const int s = u % NB;
-        const uint32_t ph = static_cast<uint32_t>(u / NB) & 1u;
-        if (!mbar_wait_bounded(&pds_ready[s], ph, args.status, 55)) return false;
-        if (!mbar_wait_bounded(&qm_full[s], ph, args.status, 56)) return false;
-        tc_fence_after();
-        const uint32_t q_addr = smem_u32(qm_s + s * C::kQTile), do_addr = smem_u32(dom_s + s * C::kQTile);
+      for (int ks = 0; ks < D / 8; ++ks)
+        umma_tf32_w(tp, vd + static_cast<uint64_t>(((ks >> 2) * kKeyChunk + (ks & 3) * 32) >> 4),
+                    dod + static_cast<uint64_t>(((ks >> 2) * kQChunk + (ks & 3) * 32) >> 4), idesc_s, ks != 0 ? 1u : 0u);
+      umma_commit_w(&qk_empty[s]);
+      umma_commit_w(&sdp_full[s]);
+      return true;
+    };
+    auto issue_dvdk = [&](int u) {
+      const int s = u % NB;
+      const uint32_t ph = static_cast<uint32_t>(u / NB) & 1u;
+      if (!mbar_wait_bounded_w(&pds_ready[s], ph, args.status, 55)) return false;
+      if (!mbar_wait_bounded_w(&qm_full[s], ph, args.status, 56)) return false;
+      tc_fence_after();
+      const uint64_t qmd = make_smem_desc(smem_u32(qm_s + s * C::kQTile), kQChunk, 512, kLayoutSw128Base32);
+      const uint64_t domd = make_smem_desc(smem_u32(dom_s + s * C::kQTile), kQChunk, 512, kLayoutSw128Base32);
+      const uint32_t ts = tm_s(s), tp = tm_dp(s);
 #pragma unroll
-        for (int ks = 0; ks < TQB / 8; ++ks)
-          umma_tf32_ta(tm_dv, tm_s(s) + static_cast<uint32_t>(ks * 8),
-                       make_smem_desc(do_addr + ks * 1024, kQChunk, 512, kLayoutSw128Base32), idesc_d,
+      for (int ks = 0; ks < TQB / 8; ++ks)
+        umma_tf32_ta_w(tm_dv, ts + static_cast<uint32_t>(ks * 8), domd + static_cast<uint64_t>((ks * 1024) >> 4), idesc_d,
                        (u != 0 || ks != 0) ? 1u : 0u);
 #pragma unroll
-        for (int ks = 0; ks < TQB / 8; ++ks)
-          umma_tf32_ta(tm_dk, tm_dp(s) + static_cast<uint32_t>(ks * 8),
-                       make_smem_desc(q_addr + ks * 1024, kQChunk, 512, kLayoutSw128Base32), idesc_d,
+      for (int ks = 0; ks < TQB / 8; ++ks)
+        umma_tf32_ta_w(tm_dk, tp + static_cast<uint32_t>(ks * 8), qmd + static_cast<uint64_t>((ks * 1024) >> 4), idesc_d,
                        (u != 0 || ks != 0) ? 1u : 0u);
-        umma_commit(&qm_empty[s]);
-        return true;
-      };
-      for (int u = 0; u <= n_units && ok; ++u) {
-        if (NB == 2 && u < n_units) ok = issue_sdp(u);
-        if (ok && u >= 1) ok = issue_dvdk(u - 1);
-        if (NB == 1 && ok && u < n_units) ok = issue_sdp(u);
-      }
-      umma_commit(done_bar);
+      umma_commit_w(&qm_empty[s]);
+      return true;
+    };
+    for (int u = 0; u <= n_units && ok; ++u) {
+      if (NB == 2 && u < n_units) ok = issue_sdp(u);
+      if (ok && u >= 1) ok = issue_dvdk(u - 1);
+      if (NB == 1 && ok && u < n_units) ok = issue_sdp(u);
     }
+    umma_commit_w(done_bar);
     __syncwarp();
   } else {
     const int cw = warp - 2;
