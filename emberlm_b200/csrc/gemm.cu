@@ -8,6 +8,7 @@ namespace ctdk {
 int gemm_tcgen05(const float* A, const float* B, float* C, int64_t M, int64_t N, int64_t K,
                  int64_t lda, int64_t ldb, int64_t ldc, int transa, int transb, int epilogue,
                  const float* aux, cudaStream_t stream);
+void gemm_set_kblock_limit(int k_blocks);
 int gemm_3xtf32(const float* A, const float* B, float* C, int64_t M, int64_t N, int64_t K,
                 int64_t lda, int64_t ldb, int64_t ldc, int transa, int transb, int epilogue,
                 const float* aux, cudaStream_t stream);
@@ -234,7 +235,11 @@ int ctdk_gemm_ws(const float* A, const float* B, float* C, int64_t M, int64_t N,
   split_tf32_kernel<<<blocks(nb / 4), 256, 0, s>>>(B, b_hi, b_lo, nb / 4);
   rc = check_launch("ctdk_gemm_ws(split B)");
   if (rc != CTDK_OK) return rc;
+  // the leading product in accumulation runs of at most 16 k-blocks (512 deep); the two correction
+  // products are 2^-11 of it and keep the usual schedule
+  gemm_set_kblock_limit(16);
   rc = ctdk_gemm(a_hi, b_hi, C, M, N, K, lda, ldb, ldc, transa, transb, CTDK_GEMM_TF32, epilogue, aux, stream);
+  gemm_set_kblock_limit(0);
   if (rc != CTDK_OK) return rc;
   rc = ctdk_gemm(a_hi, b_lo, C, M, N, K, lda, ldb, ldc, transa, transb, CTDK_GEMM_TF32, CTDK_EPI_ACCUMULATE,
                  nullptr, stream);

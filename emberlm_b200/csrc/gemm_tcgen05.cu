@@ -487,6 +487,15 @@ int gemm_swiglu_bwd_tcgen05(const float* dy, const float* Wd, const float* gu, f
                                       stream);
 }
 
+// Upper bound on the k-blocks one unit accumulates in tensor memory (0 = none), per host thread.
+// The tensor core's fp32 accumulation loses low bits with every addition, so the error of a product
+// grows with the length of the accumulation (measured: 2.1e-5 of the largest element at K = 8192 in
+// one run against 1.3e-6 when the same K is added up from 512-deep pieces in fp32). The 3xTF32 mode
+// sets it for its leading (hi x hi) product: K is then cut into ranges of at most that many
+// k-blocks whose partial tiles are added at L2 in fp32.
+static thread_local int t_kblock_limit = 0;
+void gemm_set_kblock_limit(int k_blocks) { t_kblock_limit = k_blocks; }
+
 // Returns CTDK_OK after enqueueing, or 1 when the shape/alignment is not eligible for the
 // tensor-core path (the caller then uses the SIMT kernel).
 int gemm_tcgen05(const float* A, const float* B, float* Cp, int64_t M, int64_t N, int64_t K,
@@ -566,6 +575,12 @@ int gemm_tcgen05(const float* A, const float* B, float* Cp, int64_t M, int64_t N
       splits = sp_best;
       bn = 256;
     }
+  }
+
+  if (t_kblock_limit > 0) {
+    int64_t need = (k_blocks + t_kblock_limit - 1) / t_kblock_limit;
+    if (need > 64) need = 64;
+    if (need > splits) splits = static_cast<int>(need);
   }
 
   CUtensorMap ta, tb;
