@@ -557,6 +557,22 @@ int run_bwd_legacy(const float* qkv, const float* dout, const float* lse, const 
 
 using namespace ctdk;
 
+namespace ctdk {
+// delta[b, h, t] = sum_d dout * out (the row term of the softmax backward).
+int attn_delta_launch(const float* out, const float* dout, float* delta, int64_t B, int64_t T, int H, int D, cudaStream_t s) {
+  const int64_t items = B * T * H;
+  const int lp = D / 4;
+  const int64_t cap = static_cast<int64_t>(sm_count()) * 8;
+  const int64_t need = (items + (256 / lp) * 4 - 1) / ((256 / lp) * 4);
+  const int grid = static_cast<int>(need < cap ? need : cap);
+  if (D == 64)
+    launch_pdl(attn_delta_kernel<64>, dim3(grid), dim3(256), 0, s, out, dout, delta, B, static_cast<int>(T), H);
+  else
+    launch_pdl(attn_delta_kernel<128>, dim3(grid), dim3(256), 0, s, out, dout, delta, B, static_cast<int>(T), H);
+  return check_launch("ctdk_attn_bwd(delta)");
+}
+}  // namespace ctdk
+
 extern "C" {
 
 int ctdk_attn_fwd_p(const float* qkv, float* out, float* lse, int64_t B, int64_t T, int H, int Hk, int D,
@@ -596,7 +612,7 @@ int ctdk_attn_bwd_p(const float* qkv, const float* out, const float* dout, const
   if (rc != CTDK_OK) return rc;
   CTDK_REQUIRE(precision == CTDK_GEMM_TF32 || precision == CTDK_GEMM_3XTF32, "ctdk_attn_bwd: unknown precision");
   if (B == 0 || T == 0) return CTDK_OK;
-  CTDK_REQUIRE(qkv && out && dout && lse && delta && dqkv, "ctdk_attn_bwd: null pointer");
+  CTDK_REQUIRE(qkv && dout && lse && delta && dqkv, "ctdk_attn_bwd: null pointer");
   CTDK_REQUIRE((reinterpret_cast<uintptr_t>(qkv) & 15u) == 0 && (reinterpret_cast<uintptr_t>(out) & 15u) == 0 &&
                    (reinterpret_cast<uintptr_t>(dout) & 15u) == 0 && (reinterpret_cast<uintptr_t>(dqkv) & 7u) == 0,
                "ctdk_attn_bwd: qkv/out/dout must be 16-byte aligned");
@@ -604,19 +620,10 @@ int ctdk_attn_bwd_p(const float* qkv, const float* out, const float* dout, const
   const bool x3 = precision == CTDK_GEMM_3XTF32;
   // backward = 2x the forward's algorithmic FLOPs (recomputation is not counted)
   void* tok = prof_begin(CTDK_PROF_ATTN, 4.0 * B * H * static_cast<double>(T) * T * D, s);
-  const int64_t items = B * T * H;
-  {
-    const int lp = D / 4;
-    const int64_t cap = static_cast<int64_t>(sm_count()) * 8;
-    const int64_t need = (items + (256 / lp) * 4 - 1) / ((256 / lp) * 4);
-    const int grid = static_cast<int>(need < cap ? need : cap);
-    if (D == 64)
-      launch_pdl(attn_delta_kernel<64>, dim3(grid), dim3(256), 0, s, out, dout, delta, B, static_cast<int>(T), H);
-    else
-      launch_pdl(attn_delta_kernel<128>, dim3(grid), dim3(256), 0, s, out, dout, delta, B, static_cast<int>(T), H);
+  if (out != nullptr) {   // otherwise delta already holds rowsum(dout * out) (ctdk_gemm_dattn_delta)
+    rc = attn_delta_launch(out, dout, delta, B, T, H, D, s);
+    if (rc != CTDK_OK) return rc;
   }
-  rc = check_launch("ctdk_attn_bwd(delta)");
-  if (rc != CTDK_OK) return rc;
   // tcgen05 kernels first; each returns 1 when it does not take the shape.
   int dq_done = 1, dkv_done = 1;
   if (!x3 && !attn_use_legacy()) {

@@ -357,10 +357,16 @@ int layer_backward(Engine& e, int l, int64_t B, int64_t T, int accumulate, void*
   TRY(ctdk_rmsnorm_bwd(e.dtmp, a.hm, P + w.w_post, e.dh, G + w.w_post, e.norm_scratch, tok,
                        static_cast<int>(hid), c.rms_norm_eps, accumulate, 1, s));
   // attention: hm = x + attn Wo^T
-  TRY(gemm(e, e.dh, P + w.wo, e.dattn, tok, HD, hid, 0, 0, CTDK_EPI_STORE, nullptr, s));
+  // (the o-proj dX GEMM also forms delta = rowsum(dattn * attn) in its epilogue; the attention backward is told so)
+  if (c.precision == CTDK_GEMM_TF32) {
+    TRY(ctdk_gemm_dattn_delta(e.dh, P + w.wo, a.attn, e.dattn, e.delta, B, T, H, D, hid, CTDK_GEMM_TF32, s));
+  } else {
+    TRY(gemm(e, e.dh, P + w.wo, e.dattn, tok, HD, hid, 0, 0, CTDK_EPI_STORE, nullptr, s));
+  }
   TRY(dw_gemm(e, 2, e.dh, a.attn, G + w.wo, hid, HD, tok, wepi, s));
   TRY(dw_wait(e, 3, s));   // the layer above's qkv dW still reads dqkv
-  TRY(ctdk_attn_bwd_p(a.qkv, a.attn, e.dattn, a.lse, e.delta, e.dqkv, B, T, H, Hk, D, c.precision, s));
+  TRY(ctdk_attn_bwd_p(a.qkv, c.precision == CTDK_GEMM_TF32 ? nullptr : a.attn, e.dattn, a.lse, e.delta, e.dqkv, B, T, H, Hk, D,
+                      c.precision, s));
   TRY(ctdk_qk_norm_rope_bwd(e.dqkv, a.qkv_pre, c.qk_norm ? P + w.wqn : nullptr,
                             c.qk_norm ? P + w.wkn : nullptr, a.rstd_q, a.rstd_k,
                             c.qk_norm ? G + w.wqn : nullptr, c.qk_norm ? G + w.wkn : nullptr,

@@ -9,6 +9,9 @@ int gemm_tcgen05(const float* A, const float* B, float* C, int64_t M, int64_t N,
                  int64_t lda, int64_t ldb, int64_t ldc, int transa, int transb, int epilogue,
                  const float* aux, cudaStream_t stream);
 void gemm_set_kblock_limit(int k_blocks);
+int gemm_dattn_delta_tcgen05(const float* dy, const float* Wo, const float* out, float* dattn, float* delta, int64_t M,
+                             int64_t T, int H, int D, int64_t K, cudaStream_t stream);
+int attn_delta_launch(const float* out, const float* dout, float* delta, int64_t B, int64_t T, int H, int D, cudaStream_t s);
 int gemm_3xtf32(const float* A, const float* B, float* C, int64_t M, int64_t N, int64_t K,
                 int64_t lda, int64_t ldb, int64_t ldc, int transa, int transb, int epilogue,
                 const float* aux, cudaStream_t stream);
@@ -134,6 +137,24 @@ int ctdk_gemm_swiglu_bwd(const float* dy, const float* Wd, const float* gu, floa
   int rc = ctdk_gemm(dy, Wd, dact_scratch, M, I, K, K, I, I, 0, 0, precision, CTDK_EPI_STORE, nullptr, stream);
   if (rc != CTDK_OK) return rc;
   return ctdk_swiglu_bwd(gu, dact_scratch, dgu, M, static_cast<int>(I), stream);
+}
+
+int ctdk_gemm_dattn_delta(const float* dy, const float* Wo, const float* attn_out, float* dattn, float* delta, int64_t B,
+                          int64_t T, int H, int D, int64_t hid, int precision, void* stream) {
+  CTDK_REQUIRE(B >= 0 && T >= 0 && H > 0 && hid > 0 && (D == 64 || D == 128), "ctdk_gemm_dattn_delta: bad shape");
+  if (B == 0 || T == 0) return CTDK_OK;
+  CTDK_REQUIRE(dy && Wo && attn_out && dattn && delta, "ctdk_gemm_dattn_delta: null pointer");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int64_t M = B * T, N = static_cast<int64_t>(H) * D;
+  if (precision == CTDK_GEMM_TF32) {
+    void* tok = prof_begin(CTDK_PROF_GEMM, 2.0 * static_cast<double>(M) * N * hid, s);
+    const int rc = gemm_dattn_delta_tcgen05(dy, Wo, attn_out, dattn, delta, M, T, H, D, hid, s);
+    prof_end(tok, s);
+    if (rc <= 0) return rc;
+  }
+  int rc = ctdk_gemm(dy, Wo, dattn, M, N, hid, hid, N, N, 0, 0, precision, CTDK_EPI_STORE, nullptr, stream);
+  if (rc != CTDK_OK) return rc;
+  return attn_delta_launch(attn_out, dattn, delta, B, T, H, D, s);
 }
 
 int ctdk_gemm_swiglu(const float* A, const float* W, float* gu, float* act, int64_t M, int64_t I, int64_t K,

@@ -487,6 +487,35 @@ int gemm_swiglu_bwd_tcgen05(const float* dy, const float* Wd, const float* gu, f
                                       stream);
 }
 
+int gemm_tcgen05_2cta_dattn_delta(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const CUtensorMap& to,
+                                  bool b3d, float* delta, int M, int N, int K, int T, int H, int D, int* status,
+                                  cudaStream_t stream);
+
+// dattn[M, H*D] = dy[M, K] * Wo[K, H*D] and delta[b, h, t] = sum_d dattn * out over each head, in one paired-CTA
+// launch (M = B * T rows). Returns CTDK_OK after enqueueing, a negative status, or 1 when not eligible.
+int gemm_dattn_delta_tcgen05(const float* dy, const float* Wo, const float* out, float* dattn, float* delta, int64_t M,
+                             int64_t T, int H, int D, int64_t K, cudaStream_t stream) {
+  auto a16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; };
+  const int64_t N = static_cast<int64_t>(H) * D;
+  if (!a16(dy) || !a16(Wo) || !a16(out) || !a16(dattn) || (K & 3) || (D != 64 && D != 128)) return 1;
+  if (M < 256 || N < 256 || M > INT32_MAX || N > INT32_MAX || K > INT32_MAX || K < 1 || T < 1 || M % T != 0) return 1;
+  CUtensorMap ta, tb, tc, to;
+  int rc = make_map(&ta, dy, K, M, K, BM, false, false);
+  if (rc == CTDK_OK) {
+    const uint64_t dims[3] = {32u, static_cast<uint64_t>(K), static_cast<uint64_t>(N / 32)};
+    const uint64_t strides[2] = {static_cast<uint64_t>(N) * sizeof(float), 128u};
+    const uint32_t box[3] = {32u, 32u, 4u};
+    rc = encode_tensor_map(&tb, Wo, 3, dims, strides, box, true);
+  }
+  if (rc == CTDK_OK) rc = make_map(&tc, dattn, N, M, N, 32, false, true);
+  if (rc == CTDK_OK) rc = make_map(&to, out, N, M, N, 32, false, true);
+  if (rc != CTDK_OK) return rc;
+  int* st = device_status_word();
+  if (st == nullptr) return fail(CTDK_ELAUNCH, "gemm: no status word");
+  return gemm_tcgen05_2cta_dattn_delta(ta, tb, tc, to, true, delta, static_cast<int>(M), static_cast<int>(N), static_cast<int>(K),
+                                       static_cast<int>(T), H, D, st, stream);
+}
+
 // Upper bound on the k-blocks one unit accumulates in tensor memory (0 = none), per host thread.
 // The tensor core's fp32 accumulation loses low bits with every addition, so the error of a product
 // grows with the length of the accumulation (measured: 2.1e-5 of the largest element at K = 8192 in

@@ -50,6 +50,10 @@ struct Gemm2Args {
   int narrow;     // 1: the plain epilogue (store / add of the bare accumulator) is run by the first warp of each lane
                   //    quarter through both staging boxes of its pair, which measured ~1 % faster than eight warps with
                   //    one box each; the epilogues that compute (SwiGLU, +residual) use all eight warps
+  float* delta;   // != nullptr: C = d(attention output) [M, N = H * dl_D]; map D covers the attention output itself and the
+                  // epilogue also writes delta[(b * dl_H + h) * dl_T + t] = sum over the head's columns of C * O, the row
+                  // term of the softmax backward (row = b * dl_T + t); needs swiglu == 0, splits == 1, a plain store
+  int dl_T, dl_H, dl_D;
   int stages;     // operand ring depth: 6, or 5 when the epilogue needs 64 KB of staging (swiglu == 2)
   int* status;
 };
@@ -190,7 +194,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads2, 1)
     tma_prefetch_desc(&tmA);
     tma_prefetch_desc(&tmB);
     if (args.tma_out) tma_prefetch_desc(&tmC);
-    if (args.swiglu) tma_prefetch_desc(&tmD);
+    if (args.swiglu || args.delta != nullptr) tma_prefetch_desc(&tmD);
   }
   if (warp == 1) {
     tmem_alloc2(tmem_slot, 512);
@@ -393,6 +397,60 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads2, 1)
             }
             bulk_commit();
           }
+          __syncwarp();
+        }
+      } else if (args.delta != nullptr) {
+        // d(attention output) tile: stored as it is, and dotted with the same tile of the attention
+        // output O on the way: a lane holds one row, a warp's four chunks are whole heads (two of 64
+        // columns or one of 128). O's box is fetched by TMA while the accumulator chunk is staged
+        // and sent.
+        const int r0 = mb * 2 * BM2 + static_cast<int>(rank) * BM2 + q * 32;
+        int n_ch = (args.N - nb * BN2 + 31) / 32;
+        if (n_ch > BN2 / 32) n_ch = BN2 / 32;
+        unsigned char* box_o = epi_stage + ew * (2 * kEpiBuf);
+        unsigned char* box_c = box_o + kEpiBuf;
+        const int ch_end = n_ch < half * 4 + 4 ? n_ch : half * 4 + 4;
+        const int cph = args.dl_D >> 5;   // chunks per head
+        const int64_t bsq = grow / args.dl_T;
+        float* drow = args.delta + bsq * args.dl_H * args.dl_T + (grow - bsq * args.dl_T);
+        float hsum = 0.0f;
+#pragma unroll 1
+        for (int ch = half * 4; ch < ch_end && ok; ++ch) {
+          const int col = nb * BN2 + ch * 32;
+          if (lane == 0) {
+            bulk_wait_read<0>();   // the staging box's last store has left
+            mbar_expect_tx(&ld_bar[ew], kEpiBuf);
+            tma_load_2d(box_o, &tmD, &ld_bar[ew], col, r0);
+          }
+          float v[32];
+          tmem_ld_32x32(t_row + static_cast<uint32_t>(ch * 32), v);
+          __syncwarp();
+#pragma unroll
+          for (int c = 0; c < 8; ++c)
+            *reinterpret_cast<float4*>(box_c + lane * 128 + ((c ^ (lane & 7)) << 4)) =
+                make_float4(v[4 * c], v[4 * c + 1], v[4 * c + 2], v[4 * c + 3]);
+          fence_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            if (r0 < args.M) tma_store_2d(&tmC, box_c, col, r0);
+            bulk_commit();
+          }
+          if (!mbar_wait_bounded(&ld_bar[ew], chunk_cnt & 1u, args.status, 66)) {
+            ok = false;
+            break;
+          }
+          ++chunk_cnt;
+          const unsigned char* bo = box_o + lane * 128;
+#pragma unroll
+          for (int c = 0; c < 8; ++c) {
+            const float4 o = *reinterpret_cast<const float4*>(bo + ((c ^ (lane & 7)) << 4));
+            hsum += v[4 * c] * o.x + v[4 * c + 1] * o.y + v[4 * c + 2] * o.z + v[4 * c + 3] * o.w;
+          }
+          if ((ch + 1) % cph == 0) {
+            if (row_ok) drow[static_cast<int64_t>(col / args.dl_D) * args.dl_T] = hsum;
+            hsum = 0.0f;
+          }
+          fence_async_smem();   // the reads of O's box come before the next fetch into it
           __syncwarp();
         }
       } else if (args.swiglu) {
@@ -598,7 +656,7 @@ int launch2(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc,
 int gemm_tcgen05_2cta(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, bool a_mn, bool b_mn,
                       bool a3d, bool b3d, int tma_out, float* C, const float* aux, int64_t ldc, int M, int N, int K,
                       int epilogue, int vec_ok, int splits, int* status, cudaStream_t stream) {
-  Gemm2Args args{C, aux, ldc, M, N, K, epilogue, vec_ok, splits, a3d ? 1 : 0, b3d ? 1 : 0, tma_out, 0, 1, kStages2, status};
+  Gemm2Args args{C, aux, ldc, M, N, K, epilogue, vec_ok, splits, a3d ? 1 : 0, b3d ? 1 : 0, tma_out, 0, 1, nullptr, 0, 0, 0, kStages2, status};
   if (!a_mn && !b_mn) return launch2<false, false>(ta, tb, tc, tc, args, stream);
   if (!a_mn && b_mn) return launch2<false, true>(ta, tb, tc, tc, args, stream);
   if (a_mn && !b_mn) return launch2<true, false>(ta, tb, tc, tc, args, stream);
@@ -610,7 +668,7 @@ int gemm_tcgen05_2cta(const CUtensorMap& ta, const CUtensorMap& tb, const CUtens
 // outputs, {32, 32} boxes. N must be a multiple of 128.
 int gemm_tcgen05_2cta_swiglu(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tgu, const CUtensorMap& tact,
                              int M, int N, int K, int* status, cudaStream_t stream) {
-  Gemm2Args args{nullptr, nullptr, 0, M, N, K, CTDK_EPI_STORE, 1, 1, 0, 0, 1, 1, 0, kStages2, status};
+  Gemm2Args args{nullptr, nullptr, 0, M, N, K, CTDK_EPI_STORE, 1, 1, 0, 0, 1, 1, 0, nullptr, 0, 0, 0, kStages2, status};
   return launch2<false, false>(ta, tb, tgu, tact, args, stream);
 }
 
@@ -618,8 +676,17 @@ int gemm_tcgen05_2cta_swiglu(const CUtensorMap& ta, const CUtensorMap& tb, const
 // accumulator; tgu: gate|up [M, 2N] for loading, tdgu: d(gate)|d(up) [M, 2N] for storing, {32, 32} boxes.
 int gemm_tcgen05_2cta_swiglu_bwd(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tgu, const CUtensorMap& tdgu,
                                  bool b3d, int M, int N, int K, int* status, cudaStream_t stream) {
-  Gemm2Args args{nullptr, nullptr, 0, M, N, K, CTDK_EPI_STORE, 1, 1, 0, b3d ? 1 : 0, 1, 2, 0, kStages2 - 1, status};
+  Gemm2Args args{nullptr, nullptr, 0, M, N, K, CTDK_EPI_STORE, 1, 1, 0, b3d ? 1 : 0, 1, 2, 0, nullptr, 0, 0, 0, kStages2 - 1, status};
   return launch2<false, true>(ta, tb, tgu, tdgu, args, stream);
+}
+
+// d(attention output)[M, N] = A[M, K] * B[K, N] (B MN-major, 3-D map when b3d), stored through map tc, and
+// delta[b, h, t] = sum over head h's D columns of that product times the attention output (map to, {32, 32} boxes).
+int gemm_tcgen05_2cta_dattn_delta(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const CUtensorMap& to,
+                                  bool b3d, float* delta, int M, int N, int K, int T, int H, int D, int* status,
+                                  cudaStream_t stream) {
+  Gemm2Args args{nullptr, nullptr, 0, M, N, K, CTDK_EPI_STORE, 1, 1, 0, b3d ? 1 : 0, 1, 0, 0, delta, T, H, D, kStages2 - 1, status};
+  return launch2<false, true>(ta, tb, tc, to, args, stream);
 }
 
 }  // namespace ctdk

@@ -57,6 +57,7 @@ _SIGS = {
     "ctdk_attn_bwd_p": [_p, _p, _p, _p, _p, _p, _l, _l, _i, _i, _i, _i, _p],
     "ctdk_gemm_swiglu": [_p, _p, _p, _p, _l, _l, _l, _i, _p],
     "ctdk_gemm_swiglu_bwd": [_p, _p, _p, _p, _p, _l, _l, _l, _i, _p],
+    "ctdk_gemm_dattn_delta": [_p, _p, _p, _p, _p, _l, _l, _i, _i, _l, _i, _p],
     "ctdk_bmm": [_p, _p, _p, _l, _l, _l, _l, _i, _i, _i, _p],
     "ctdk_rmsnorm_fwd": [_p, _p, _p, _p, _l, _i, _f, _p],
     "ctdk_rmsnorm_bwd": [_p, _p, _p, _p, _p, _p, _l, _i, _f, _i, _i, _p],

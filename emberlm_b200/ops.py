@@ -94,6 +94,21 @@ def mlp_in_backward(dy, w_down, gu, precision=lib.GEMM_TF32):
     return dgu
 
 
+def oproj_backward(dy, w_o, attn_out, B, T, H, D, precision=lib.GEMM_TF32):
+    """d(attention output) [B*T, H*D] = dy [B*T, hid] @ o_proj.weight [hid, H*D] and delta [B, H, T] =
+    rowsum over each head of that product times the attention output (what the attention backward
+    needs first), from one GEMM."""
+    _chk(dy, "oproj_backward"), _chk(w_o, "oproj_backward"), _chk(attn_out, "oproj_backward")
+    M, hid = dy.shape
+    if M != B * T or tuple(w_o.shape) != (hid, H * D) or tuple(attn_out.shape) != (M, H * D):
+        raise RuntimeError("oproj_backward: shape mismatch")
+    dattn = torch.empty_like(attn_out)
+    delta = torch.empty(B, H, T, device=dy.device, dtype=dy.dtype)
+    lib.call("ctdk_gemm_dattn_delta", dy.data_ptr(), w_o.data_ptr(), attn_out.data_ptr(), dattn.data_ptr(),
+             delta.data_ptr(), B, T, H, D, hid, precision, _s())
+    return dattn, delta
+
+
 def swiglu(gu):
     _chk(gu, "swiglu")
     rows, two_i = gu.shape
@@ -273,10 +288,13 @@ def attention(qkv, B, T, H, Hk, D, precision=lib.GEMM_TF32):
     return out, lse
 
 
-def attention_backward(qkv, out, dout, lse, B, T, H, Hk, D, precision=lib.GEMM_TF32):
+def attention_backward(qkv, out, dout, lse, B, T, H, Hk, D, precision=lib.GEMM_TF32, delta=None):
+    """delta: rowsum(dout * out) per (batch, head, position) when oproj_backward has already formed it
+    (out is then not read)."""
     dqkv = torch.empty_like(qkv)
-    delta = torch.empty(B, H, T, device=qkv.device)
-    lib.call("ctdk_attn_bwd_p", qkv.data_ptr(), out.data_ptr(), dout.data_ptr(), lse.data_ptr(),
+    given = delta is not None
+    delta = delta if given else torch.empty(B, H, T, device=qkv.device)
+    lib.call("ctdk_attn_bwd_p", qkv.data_ptr(), 0 if given else out.data_ptr(), dout.data_ptr(), lse.data_ptr(),
              delta.data_ptr(), dqkv.data_ptr(), B, T, H, Hk, D, precision, _s())
     return dqkv
 

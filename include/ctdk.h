@@ -106,6 +106,18 @@ int ctdk_gemm_swiglu_bwd(const float* dy, const float* Wd, const float* gu, floa
                          float* dact_scratch, int64_t M, int64_t I, int64_t K, int precision,
                          void* stream);
 
+/* The dX product of o_proj in the backward pass (MatmulBackward, src/ops/matmul.cpp:120-168) fused with
+ * the row term of the softmax backward (softmax_backward_kernel, src/ops/softmax.cu:56-93, after the
+ * P V product's backward): dattn[B*T, H*D] = dy[B*T, hid] * Wo[hid, H*D] and delta[b, h, t] = sum over
+ * head h's D columns of dattn * attn_out, formed in the GEMM's epilogue while the tile is still in
+ * registers (attn_out's tile is fetched by TMA), so the attention output and its gradient are not
+ * read again for it. ctdk_attn_bwd(_p) called afterwards with out == NULL takes delta as given. Shapes
+ * the fused kernel does not take (3xTF32, B*T < 256, unaligned pointers) run as ctdk_gemm + the
+ * separate delta pass. D is 64 or 128. */
+int ctdk_gemm_dattn_delta(const float* dy, const float* Wo, const float* attn_out, float* dattn,
+                          float* delta, int64_t B, int64_t T, int H, int D, int64_t hid,
+                          int precision, void* stream);
+
 /* Batched variant with full-matrix strides, as cublasSgemmStridedBatched in
  * ops::bmm_impl (src/ops/matmul.cpp:51-93). */
 int ctdk_bmm(const float* A, const float* B, float* C, int64_t batch, int64_t M, int64_t N,
@@ -244,7 +256,9 @@ int ctdk_gather_ce_inputs(const int64_t* targets, const float* mask, const float
  * repeat_kv_heads and the permutes. q is read at qkv[(b*T+t)*row_stride + h*D], k at
  * column offset H*D + hk*D, v at (H+Hk)*D + hk*D; query head h uses kv head h/(H/Hk).
  * out is [B*T, H*D]; lse [B,H,T] holds the log-sum-exp of the scaled scores.
- * The backward takes dout [B*T,H*D] and writes dqkv in the packed layout.
+ * The backward takes dout [B*T,H*D] and writes dqkv in the packed layout; delta [B,H,T] is
+ * scratch for rowsum(dout * out), computed from out here, or taken as given when out is NULL
+ * (ctdk_gemm_dattn_delta has produced it).
  * ------------------------------------------------------------------------------------ */
 int ctdk_attn_fwd(const float* qkv, float* out, float* lse, int64_t B, int64_t T, int H,
                   int Hk, int D, void* stream);

@@ -429,3 +429,29 @@ def test_clip_grad_norm(K):
     assert abs(float(norm) - 0.2) < 1e-5 and float(scale) == 1.0
     big = dev(rnd((3_000_001,), 45))
     assert abs(float(K.sumsq(big)) / float((host(big).astype(np.float64) ** 2).sum()) - 1) < 1e-5
+
+
+@pytest.mark.parametrize("B,T,H,Hk,D,hid", [(2, 256, 15, 5, 64, 960), (1, 384, 16, 8, 128, 1024), (3, 100, 4, 2, 64, 256),
+                                            (1, 64, 4, 4, 64, 128)])
+def test_oproj_backward_with_delta(K, B, T, H, Hk, D, hid):
+    """The o-proj dX GEMM that also forms delta: d(attention output) equal to the plain GEMM (which may
+    cut K in two for few-tile shapes, so equal to fp32 summation order, not bit for bit),
+    delta equal to rowsum(dattn * out) (fp64) to fp32 rounding, and the attention backward fed with it
+    equal to the one that computes delta itself. The last two shapes take the unfused path (fewer
+    than 256 rows)."""
+    ops = K
+    g = torch.Generator(device="cuda").manual_seed(B * 1000 + T)
+    M = B * T
+    dy = torch.randn(M, hid, device="cuda", generator=g)
+    w = torch.randn(hid, H * D, device="cuda", generator=g) * 0.05
+    qkv = torch.randn(M, (H + 2 * Hk) * D, device="cuda", generator=g)
+    out, lse = ops.attention(qkv, B, T, H, Hk, D)
+    dattn, delta = ops.oproj_backward(dy, w, out, B, T, H, D)
+    ref = ops.matmul(dy, w, False, False)
+    assert float((dattn - ref).abs().max()) <= 2e-6 * float(ref.abs().max())
+    want = (ref.double() * out.double()).view(B, T, H, D).sum(-1).permute(0, 2, 1)
+    scale = float(want.abs().max())
+    assert float((delta.double() - want).abs().max()) <= 2e-6 * scale + 1e-6
+    a = ops.attention_backward(qkv, out, dattn, lse, B, T, H, Hk, D)
+    b = ops.attention_backward(qkv, out, dattn, lse, B, T, H, Hk, D, delta=delta)
+    assert float((a - b).abs().max()) <= 1e-5 * float(a.abs().max())
