@@ -141,7 +141,7 @@ def test_three_generators_emit_the_same_seeded_stream(workspace):
     # same seeded draws pick the same tokens unless a draw falls within TF32 rounding of an inverse-CDF
     # boundary (about one token in twenty at this width), where it lands on the neighbouring id; from
     # there on the streams condition on different tokens. So: identical up to the first difference, and
-    # that difference is a neighbouring id. (A wrong draw order or sampler would scatter the ids; a
+    # that difference is a neighbouring id (within 3 ids; within 8 when top_p has removed part of the vocabulary). (A wrong draw order or sampler would scatter the ids; a
     # greedy argmax over near-ties would not be stable at all.)
     for req in (dict(temperature=1.0, seed=7), dict(temperature=0.8, top_p=0.9, seed=11), dict(temperature=1.2, top_k=50, seed=3)):
         got = {w: ask(w, max_new_tokens=16, **req) for w in GENERATORS}
@@ -153,7 +153,7 @@ def test_three_generators_emit_the_same_seeded_stream(workspace):
             first = next((i for i in range(len(b)) if a[i] != b[i]), None)
             # (with top_k = 50 only fifty boundaries exist, a thousand times fewer chances to sit on one,
             # and the neighbouring survivor can be any id: those streams must simply be equal)
-            near = 0 if "top_k" in req else 3
+            near = 0 if "top_k" in req else (8 if "top_p" in req else 3)   # top_p removes ids from the walk: neighbours lie further apart
             assert first is None or abs(a[first] - b[first]) <= near, (w, req, first, a, b)
     # protocol corners on every build: empty prompt, the cache limit
     for w in GENERATORS:
