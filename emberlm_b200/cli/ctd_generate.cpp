@@ -65,10 +65,25 @@ std::string parse_model_path(int argc, char** argv) {
   for (int i = 1; i < argc; ++i)
     if (std::string(argv[i]) == "--model" && i + 1 < argc) model = argv[++i];
   if (model.empty()) {
-    std::cerr << "usage: " << argv[0] << " --model <path-to-fp32.safetensors>\n";
+    std::cerr << "usage: " << argv[0] << " --model <path-to-fp32.safetensors> [--precision fp32|tf32]\n";
     std::exit(2);
   }
   return model;
+}
+
+// The prompt pass: exact fp32 products by default, like the reference's generator (the token steps are
+// fp32 GEMVs in either case), so that a request draws the same tokens; --precision tf32 runs the prompt
+// on the TF32 tensor cores (long prompts, where a rounding difference of 1e-3 in the cache is acceptable).
+int parse_precision(int argc, char** argv) {
+  for (int i = 1; i + 1 < argc; ++i)
+    if (std::string(argv[i]) == "--precision") {
+      const std::string v = argv[i + 1];
+      if (v == "tf32") return CTDK_GEMM_TF32;
+      if (v == "fp32" || v == "3xtf32") return CTDK_GEMM_3XTF32;
+      std::cerr << "--precision: expected fp32 or tf32\n";
+      std::exit(2);
+    }
+  return CTDK_GEMM_3XTF32;
 }
 
 }  // namespace
@@ -98,7 +113,8 @@ int main(int argc, char** argv) try {
   st::File wfile(model_path);
   const st::Entry& emb = wfile.entry("model.embed_tokens.weight");
   if (emb.shape.size() != 2) throw std::runtime_error("autodetect_config: model.embed_tokens.weight must be 2-D");
-  const ctdk_model_config mc = cli::autodetect_config(emb.shape[0], emb.shape[1]);
+  ctdk_model_config mc = cli::autodetect_config(emb.shape[0], emb.shape[1]);
+  mc.precision = parse_precision(argc, argv);
   std::cerr << "[ctd_generate] arch: hidden=" << mc.hidden_size << " layers=" << mc.num_hidden_layers << "\n";
   const int prompt_len = static_cast<int>(input_ids.size());
   for (const int64_t id : input_ids)
@@ -153,7 +169,7 @@ int main(int argc, char** argv) try {
     bool done = false;
     while (!done && generated < max_new) {
       int n = std::min<int>(16, max_new - generated);
-      n = std::min<int>(n, max_seq - (prompt_len + generated));   // cache positions left
+      n = std::min<int>(n, max_seq + 1 - (prompt_len + generated));   // cache positions left (the last token needs none)
       if (n <= 0) {
         stop = "max_seq_len";
         break;
@@ -227,7 +243,7 @@ int main(int argc, char** argv) try {
         stop = "eos";
         break;
       }
-      if (prompt_len + fed + 1 > max_seq - 1) {   // no cache position left for this token
+      if (prompt_len + fed + 1 > max_seq) {   // no cache position left for this token
         stop = "max_seq_len";
         break;
       }

@@ -1120,7 +1120,7 @@ int ctdk_decode_prefill(void* decoder, const int64_t* ids, int64_t T, void* stre
     kv_write_rows_kernel<<<sm_count() * 4, 256, 0, s>>>(d.pqkv, d.kcache + l * cache_layer, d.vcache + l * cache_layer,
                                                         static_cast<int>(T), H, Hk, D, d.max_seq);
     DTRY(check_launch("decode kv write"));
-    DTRY(ctdk_attn_fwd(d.pqkv, d.pattn, d.plse, 1, T, H, Hk, D, s));
+    DTRY(ctdk_attn_fwd_p(d.pqkv, d.pattn, d.plse, 1, T, H, Hk, D, prec, s));
     DTRY(ctdk_gemm(d.pattn, P + w.wo, d.pb, T, hid, H * D, H * D, H * D, hid, 0, 1, prec, CTDK_EPI_RESIDUAL, d.pa, s));
     DTRY(ctdk_rmsnorm_fwd(d.pb, P + w.w_post, d.pa, nullptr, T, hid, c.rms_norm_eps, s));
     DTRY(ctdk_gemm(d.pa, P + w.wg, d.pgu, T, 2 * I, hid, hid, hid, 2 * I, 0, 1, prec, CTDK_EPI_STORE, nullptr, s));
@@ -1166,7 +1166,10 @@ int ctdk_decode_greedy(void* decoder, int64_t n_new, int64_t* out_tokens, void* 
   Decoder& d = *static_cast<Decoder*>(decoder);
   CTDK_REQUIRE(d.prompt_len > 0, "ctdk_decode_greedy: call ctdk_decode_prefill first");
   CTDK_REQUIRE(d.stepped == 0, "ctdk_decode_greedy: cannot be mixed with ctdk_decode_step after one prefill");
-  CTDK_REQUIRE(d.prompt_len + d.generated + n_new <= d.max_seq,
+  // n tokens after the prompt need n - 1 cache positions (the first comes from the prompt's logits, the
+  // last is not fed back): the reference's loop emits max_seq - prompt + 1 tokens before it reports
+  // max_seq_len (tools/ctd_generate/main.cpp:143-179)
+  CTDK_REQUIRE(d.prompt_len + d.generated + n_new <= d.max_seq + 1,
                "ctdk_decode_greedy: %lld more tokens would exceed max_seq %d", static_cast<long long>(n_new),
                d.max_seq);
   cudaStream_t s = static_cast<cudaStream_t>(stream);

@@ -619,7 +619,7 @@ class Decoder:
         ids = torch.as_tensor(input_ids, dtype=torch.int64, device=self.device).reshape(-1).contiguous()
         if ids.numel() == 0:
             raise RuntimeError("generate: empty_prompt")
-        n = min(max_new_tokens, self.max_seq_len - ids.numel())
+        n = min(max_new_tokens, self.max_seq_len - ids.numel() + 1)   # the last token needs no cache position (as the reference's loop)
         out = torch.zeros(max(n, 1), dtype=torch.int64, device=self.device)
         self.stream.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(self.stream):

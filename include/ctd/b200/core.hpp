@@ -18,6 +18,7 @@
 // Header-only.
 #pragma once
 
+#include <cstdlib>
 #include <cstddef>
 #include <cstdint>
 #include <cstring>
@@ -80,6 +81,17 @@ inline void require(bool ok, const char* msg) {
 }
 inline void require(bool ok, const std::string& msg) {
   if (!ok) throw std::runtime_error(msg);
+}
+// Precision of the per-op matrix products (matmul, bmm, Linear): TF32 tensor cores by default; with
+// CTD_MATMUL_PRECISION=fp32 in the environment they are exact fp32 products like the reference's
+// cublasSgemm (src/ops/matmul.cpp:38-47), at a fraction of the speed. The fused training engine has
+// its own setting (LlamaConfig / the "precision" key of ctd_train).
+inline int matmul_precision() {
+  static const int p = [] {
+    const char* e = std::getenv("CTD_MATMUL_PRECISION");
+    return (e != nullptr && (std::string(e) == "fp32" || std::string(e) == "3xtf32")) ? CTDK_GEMM_3XTF32 : CTDK_GEMM_TF32;
+  }();
+  return p;
 }
 inline void ctdk_ok(int rc) {
   if (rc != CTDK_OK) throw std::runtime_error(ctdk_last_error());

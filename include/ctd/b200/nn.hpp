@@ -46,7 +46,7 @@ inline std::vector<int64_t> with_last(const Tensor& x, int64_t last) {
 }
 inline void gemm(const float* A, const float* B, float* C, int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldb, int64_t ldc,
                  int ta, int tb, int epilogue = CTDK_EPI_STORE) {
-  ctdk_ok(ctdk_gemm(A, B, C, M, N, K, lda, ldb, ldc, ta, tb, CTDK_GEMM_TF32, epilogue, nullptr, nullptr));
+  ctdk_ok(ctdk_gemm(A, B, C, M, N, K, lda, ldb, ldc, ta, tb, ::ctd::detail::matmul_precision(), epilogue, nullptr, nullptr));
 }
 }  // namespace detail
 

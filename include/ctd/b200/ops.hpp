@@ -147,7 +147,7 @@ inline Tensor matmul_impl(const Tensor& a, const Tensor& b, bool transa, bool tr
   detail::require(K == Kb, "matmul: inner dims disagree");
   Tensor out = Tensor::empty({M, N}, DType::kFloat32, a.device());
   detail::ctdk_ok(ctdk_gemm(detail::f(a), detail::f(b), detail::f(out), M, N, K, a.shape()[1], b.shape()[1], N, transa ? 1 : 0,
-                            transb ? 1 : 0, CTDK_GEMM_TF32, CTDK_EPI_STORE, nullptr, nullptr));
+                            transb ? 1 : 0, ::ctd::detail::matmul_precision(), CTDK_EPI_STORE, nullptr, nullptr));
   return out;
 }
 inline Tensor bmm_impl(const Tensor& a, const Tensor& b, bool transa, bool transb) {
@@ -159,7 +159,7 @@ inline Tensor bmm_impl(const Tensor& a, const Tensor& b, bool transa, bool trans
   const int64_t Kb = transb ? b.shape()[2] : b.shape()[1], N = transb ? b.shape()[1] : b.shape()[2];
   detail::require(K == Kb, "bmm: inner dims disagree");
   Tensor out = Tensor::empty({Bt, M, N}, DType::kFloat32, a.device());
-  detail::ctdk_ok(ctdk_bmm(detail::f(a), detail::f(b), detail::f(out), Bt, M, N, K, transa ? 1 : 0, transb ? 1 : 0, CTDK_GEMM_TF32,
+  detail::ctdk_ok(ctdk_bmm(detail::f(a), detail::f(b), detail::f(out), Bt, M, N, K, transa ? 1 : 0, transb ? 1 : 0, ::ctd::detail::matmul_precision(),
                            nullptr));
   return out;
 }

@@ -74,7 +74,7 @@ def test_decode_limits_and_errors():
     ocfg, ecfg, params = build(CASES[0], 45)
     dec = E.Decoder(ecfg, max_seq_len=24)
     dec.load_parameters(params)
-    assert dec.generate(np.arange(20), 100).numel() == 4      # stops at max_seq_len
+    assert dec.generate(np.arange(20), 100).numel() == 5      # stops at max_seq_len: 24 - 20 cache positions + the token that needs none
     with pytest.raises(RuntimeError):
         dec.generate([], 4)
     with pytest.raises(RuntimeError):

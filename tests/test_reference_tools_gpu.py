@@ -8,6 +8,7 @@ end with the same weights within the TF32 tolerance; a run directory written by 
 another (weights, optimizer.m / optimizer.v by name, optimizer.step); the three generators emit
 the same seeded token stream for the same request."""
 import json
+import os
 import subprocess
 from pathlib import Path
 
@@ -129,21 +130,28 @@ def test_three_trainers_agree_and_checkpoints_interchange(workspace):
 def test_three_generators_emit_the_same_seeded_stream(workspace):
     root, w0, data, names = workspace
     prompt = [5, 17, 300, 4242, 9, 77, 12345]
-
-    def ask(which, **req):
-        r = subprocess.run([str(GENERATORS[which]), "--model", str(w0)], input=json.dumps(dict(input_ids=prompt, max_seq_len=64, **req)),
-                           capture_output=True, text=True, timeout=900)
+    # Low temperatures: with the plain random weights the logits of 49 152 tokens differ by a standard
+    # deviation of 0.5, i.e. at temperature 1 the distribution is flat and every draw sits within
+    # rounding of an inverse-CDF boundary one time in five; at 0.2 - 0.3 a few hundred tokens carry
+    # the mass.
+    def ask(which, model=w0, **req):
+        # exact fp32 products everywhere, as in the reference: this repo's generator by default, the
+        # reference's source on this repo's headers through CTD_MATMUL_PRECISION
+        r = subprocess.run([str(GENERATORS[which]), "--model", str(model)], input=json.dumps(dict(input_ids=prompt, max_seq_len=64, **req)),
+                           capture_output=True, text=True, timeout=900, env=dict(os.environ, CTD_MATMUL_PRECISION="fp32"))
         assert r.returncode == 0, f"{which}: {r.stderr[-1500:]}"
         lines = [json.loads(l) for l in r.stdout.strip().splitlines()]
         return [l["token"] for l in lines[:-1]], lines[-1]
 
-    # Sampled requests: with random weights the distribution over 49 152 tokens is nearly flat, so the
-    # same seeded draws pick the same tokens unless a draw falls within TF32 rounding of an inverse-CDF
-    # boundary (about one token in twenty at this width), where it lands on the neighbouring id; from
-    # there on the streams condition on different tokens. So: identical up to the first difference, and
-    # that difference is a neighbouring id (within 3 ids; within 8 when top_p has removed part of the vocabulary). (A wrong draw order or sampler would scatter the ids; a
-    # greedy argmax over near-ties would not be stable at all.)
-    for req in (dict(temperature=1.0, seed=7), dict(temperature=0.8, top_p=0.9, seed=11), dict(temperature=1.2, top_k=50, seed=3)):
+    # Sampled requests draw the same tokens from the same seed when sampler, draw order and logits
+    # agree. What is left between the builds is fp32 rounding (different summation orders, this repo's
+    # libm-accurate RoPE table against the reference's fast-math one): a draw that falls within it of
+    # an inverse-CDF boundary lands on the neighbouring surviving id, and from there on the streams
+    # condition on different tokens. So: identical up to the first difference; a first difference in
+    # at most one of the three requests per build; and for the pure-temperature request, where every id
+    # survives, that difference is a neighbouring id.
+    differing = {w: 0 for w in ("api", "ours")}
+    for req in (dict(temperature=0.25, seed=7), dict(temperature=0.2, top_p=0.9, seed=11), dict(temperature=0.3, top_k=50, seed=3)):
         got = {w: ask(w, max_new_tokens=16, **req) for w in GENERATORS}
         assert got["ref"][1] == {"done": True, "reason": "max_tokens", "generated_tokens": 16}
         print(req, {w: got[w][0] for w in got})
@@ -151,14 +159,20 @@ def test_three_generators_emit_the_same_seeded_stream(workspace):
             assert got[w][1] == got["ref"][1], (w, req)
             a, b = got[w][0], got["ref"][0]
             first = next((i for i in range(len(b)) if a[i] != b[i]), None)
-            # (with top_k = 50 only fifty boundaries exist, a thousand times fewer chances to sit on one,
-            # and the neighbouring survivor can be any id: those streams must simply be equal)
-            near = 0 if "top_k" in req else (8 if "top_p" in req else 3)   # top_p removes ids from the walk: neighbours lie further apart
-            assert first is None or abs(a[first] - b[first]) <= near, (w, req, first, a, b)
+            if first is not None:
+                differing[w] += 1
+                if "top_k" not in req and "top_p" not in req:
+                    assert abs(a[first] - b[first]) <= 3, (w, req, first, a, b)
+    assert max(differing.values()) <= 1, differing
+    # the TF32 prompt pass of this repo's generator is an option, not the default: it runs and answers
+    r = subprocess.run([str(GENERATORS["ours"]), "--model", str(w0), "--precision", "tf32"],
+                       input=json.dumps(dict(input_ids=prompt, max_seq_len=64, max_new_tokens=4, temperature=0.0)), capture_output=True, text=True,
+                       timeout=900)
+    assert r.returncode == 0 and json.loads(r.stdout.strip().splitlines()[-1])["generated_tokens"] == 4
     # protocol corners on every build: empty prompt, the cache limit
     for w in GENERATORS:
         r = subprocess.run([str(GENERATORS[w]), "--model", str(w0)], input=json.dumps(dict(input_ids=[])), capture_output=True, text=True,
                            timeout=900)
         assert json.loads(r.stdout.strip().splitlines()[-1]) == {"done": True, "reason": "empty_prompt"}, w
         toks, done = ask(w, max_new_tokens=200, temperature=0.0)
-        assert done["reason"] == "max_seq_len" and len(toks) <= 64 - len(prompt), w
+        assert done["reason"] == "max_seq_len" and len(toks) == 64 - len(prompt) + 1, w   # the last token needs no cache position
