@@ -1,6 +1,6 @@
 """Parity of every ctdk kernel against the numpy oracle, through the C-ABI (ctypes), on a GPU.
-Tolerances: exact-fp32 kernels 1e-5..1e-4 as the reference's own op tests (SURVEY of
-tests/test_*.cpp); TF32 tensor-core kernels relative to the largest reference entry."""
+Tolerances: exact-fp32 kernels 1e-5..1e-4 as the reference's own op tests
+(tests/test_*.cpp there); TF32 tensor-core kernels relative to the largest reference entry."""
 import math
 
 import numpy as np
