@@ -62,18 +62,30 @@ __global__ void __launch_bounds__(256) rmsnorm_fwd_kernel(const float* __restric
     const int c = threadIdx.x + j * blockDim.x;
     wv[j] = (c < H4) ? w4[c] : make_float4(0.f, 0.f, 0.f, 0.f);
   }
+  // The next row is fetched before the current one is reduced, so a CTA always has two rows of loads
+  // in flight across the block-wide reduction (at the SM clock a power-capped step runs at, one row
+  // per CTA in flight leaves the kernel latency-bound).
+  float4 xn[NV];
+  auto fetch = [&](int64_t row) {
+    const float4* x4 = reinterpret_cast<const float4*>(x) + row * H4;
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
+      const int c = threadIdx.x + j * blockDim.x;
+      xn[j] = (c < H4 && row < rows) ? __ldcs(x4 + c) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+  };
+  fetch(blockIdx.x);
   int slot = 0;
   for (int64_t row = blockIdx.x; row < rows; row += gridDim.x, slot ^= 1) {
-    const float4* x4 = reinterpret_cast<const float4*>(x) + row * H4;
     float4* y4 = reinterpret_cast<float4*>(y) + row * H4;
     float4 xv[NV];
     float acc[1] = {0.0f};
 #pragma unroll
     for (int j = 0; j < NV; ++j) {
-      const int c = threadIdx.x + j * blockDim.x;
-      xv[j] = (c < H4) ? x4[c] : make_float4(0.f, 0.f, 0.f, 0.f);
+      xv[j] = xn[j];
       acc[0] += xv[j].x * xv[j].x + xv[j].y * xv[j].y + xv[j].z * xv[j].z + xv[j].w * xv[j].w;
     }
+    fetch(row + gridDim.x);
     block_sum<1>(acc, red, slot);
     const float s = rsqrtf(acc[0] * inv_H + eps);
     if (rstd != nullptr && threadIdx.x == 0) rstd[row] = s;
@@ -377,23 +389,25 @@ __global__ void __launch_bounds__(256)
   pdl_wait();
   constexpr int D = 64 * NP, Dh = 32 * NP, TPH = 8 * NP;  // threads per head slot
   const int HT = H + 2 * Hk;
-  const int64_t items = rows * HT;
+  const bool copy_v = (out != qkv);
+  const bool has_norm = (wq != nullptr);
+  const int HS = copy_v ? HT : H + Hk;   // head slots of a row this launch touches: in place, v is neither read nor written
+  const int64_t items = rows * HS;
   const int j = threadIdx.x % TPH;
   const int64_t g0 = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) / TPH;
   const int64_t ng = (static_cast<int64_t>(gridDim.x) * blockDim.x) / TPH;
-  const bool copy_v = (out != qkv);
-  const bool has_norm = (wq != nullptr);
   const int64_t iters = (items + ng - 1) / ng;  // every lane runs the same number of shuffles
   for (int64_t k = 0; k < iters; ++k) {
     const int64_t it = g0 + k * ng;
     const bool live = it < items;
-    const int64_t row = live ? it / HT : 0;
-    const int h = live ? static_cast<int>(it - row * HT) : 0;
+    const int64_t row = live ? it / HS : 0;
+    const int h = live ? static_cast<int>(it - row * HS) : 0;
     const bool is_v = h >= H + Hk, is_q = h < H;
+    const int64_t off = (row * HT + h) * D;
     float4 a = make_float4(0.f, 0.f, 0.f, 0.f), b = a;
     if (live) {
-      a = *reinterpret_cast<const float4*>(qkv + it * D + 4 * j);
-      b = *reinterpret_cast<const float4*>(qkv + it * D + Dh + 4 * j);
+      a = *reinterpret_cast<const float4*>(qkv + off + 4 * j);
+      b = *reinterpret_cast<const float4*>(qkv + off + Dh + 4 * j);
     }
     if (has_norm) {
       float ss = a.x * a.x + a.y * a.y + a.z * a.z + a.w * a.w + b.x * b.x + b.y * b.y +
@@ -417,11 +431,9 @@ __global__ void __launch_bounds__(256)
       const int64_t t = row % T;
       const float4* tb = reinterpret_cast<const float4*>(table + t * Dh + 4 * j);
       rot4(a, b, tb[0], tb[1], 1.0f);
-    } else if (!copy_v) {
-      continue;
     }
-    *reinterpret_cast<float4*>(out + it * D + 4 * j) = a;
-    *reinterpret_cast<float4*>(out + it * D + Dh + 4 * j) = b;
+    *reinterpret_cast<float4*>(out + off + 4 * j) = a;
+    *reinterpret_cast<float4*>(out + off + Dh + 4 * j) = b;
   }
 }
 
@@ -746,7 +758,7 @@ int ctdk_qk_norm_rope_fwd(const float* qkv, float* qkv_out, const float* wq, con
   CTDK_REQUIRE(wq == nullptr || (rstd_q && rstd_k), "ctdk_qk_norm_rope_fwd: rstd required");
   CTDK_REQUIRE(wq == nullptr || qkv_out != qkv,
                "ctdk_qk_norm_rope_fwd: QK-Norm needs an out-of-place result");
-  const int64_t items = rows * (H + 2 * Hk);
+  const int64_t items = rows * (H + Hk + (qkv_out != qkv ? Hk : 0));
   const int64_t cap = static_cast<int64_t>(sm_count()) * 8;
   const int per_cta = 256 / (D / 8);  // head slots per CTA and iteration
   const int64_t need = (items + per_cta - 1) / per_cta;
