@@ -213,6 +213,92 @@ __global__ void __launch_bounds__(256)
   }
 }
 
+// RMSNorm backward, one WARP per row (H <= 1024): a row is NF float4 per lane, both reductions are
+// warp shuffles, so the eight rows of a CTA proceed independently and nothing waits on a block-wide
+// barrier between a row's loads and its stores. The CTA-per-row kernel above keeps one row plus one
+// prefetched row in flight per CTA and measured 0.70 of the copy bandwidth whatever the SM clock:
+// it is bound by bytes in flight. dw: each warp adds into its own row of shared memory, the eight
+// rows are summed in a fixed order at the end, one partial row per CTA (grid <= 2 per SM, so the
+// finalize pass reads a quarter of the partial rows the other kernel leaves).
+template <int NF>
+__global__ void __launch_bounds__(256, 2)
+    rmsnorm_bwd_rows_kernel(const float* __restrict__ dy, const float* __restrict__ x,
+                            const float* __restrict__ w, float* __restrict__ dx,
+                            float* __restrict__ partial, int64_t rows, int H4, float inv_H,
+                            float eps, int add_to_dx) {
+  pdl_launch();
+  pdl_wait();
+  extern __shared__ float4 sdw4[];   // [8][H4]: each warp's running dw (its own row of shared memory, no atomics)
+  const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+  const float4* w4 = reinterpret_cast<const float4*>(w);
+  const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
+  float4* mydw = sdw4 + wid * H4;
+#pragma unroll
+  for (int j = 0; j < NF; ++j) {
+    const int c = lane + 32 * j;
+    if (c < H4) mydw[c] = zero4;
+  }
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * 8;
+  for (int64_t row = static_cast<int64_t>(blockIdx.x) * 8 + wid; row < rows; row += stride) {
+    const float4* x4 = reinterpret_cast<const float4*>(x) + row * H4;
+    const float4* g4 = reinterpret_cast<const float4*>(dy) + row * H4;
+    float4* dx4 = reinterpret_cast<float4*>(dx) + row * H4;
+    float4 xv[NF], gv[NF], pv[NF];   // all of a row's loads are issued before anything waits on them
+#pragma unroll
+    for (int j = 0; j < NF; ++j) {
+      const int c = lane + 32 * j;
+      xv[j] = c < H4 ? __ldcs(x4 + c) : zero4;
+      gv[j] = c < H4 ? __ldcs(g4 + c) : zero4;
+      pv[j] = (c < H4 && add_to_dx) ? dx4[c] : zero4;
+    }
+    float a0 = 0.0f, a1 = 0.0f;
+#pragma unroll
+    for (int j = 0; j < NF; ++j) {
+      const int c = lane + 32 * j;
+      const float4 wv = c < H4 ? __ldg(w4 + c) : zero4;
+      a0 += xv[j].x * xv[j].x + xv[j].y * xv[j].y + xv[j].z * xv[j].z + xv[j].w * xv[j].w;
+      a1 += gv[j].x * wv.x * xv[j].x + gv[j].y * wv.y * xv[j].y + gv[j].z * wv.z * xv[j].z + gv[j].w * wv.w * xv[j].w;
+    }
+    a0 = warp_sum(a0);
+    a1 = warp_sum(a1);
+    const float s = rsqrtf(a0 * inv_H + eps);
+    const float k = s * s * a1 * inv_H;
+#pragma unroll
+    for (int j = 0; j < NF; ++j) {
+      const int c = lane + 32 * j;
+      if (c < H4) {
+        const float4 wv = __ldg(w4 + c);
+        float4 o;
+        o.x = s * (gv[j].x * wv.x - xv[j].x * k) + pv[j].x;   // pv is zero unless add_to_dx
+        o.y = s * (gv[j].y * wv.y - xv[j].y * k) + pv[j].y;
+        o.z = s * (gv[j].z * wv.z - xv[j].z * k) + pv[j].z;
+        o.w = s * (gv[j].w * wv.w - xv[j].w * k) + pv[j].w;
+        dx4[c] = o;
+        float4 d = mydw[c];
+        d.x += gv[j].x * xv[j].x * s;
+        d.y += gv[j].y * xv[j].y * s;
+        d.z += gv[j].z * xv[j].z * s;
+        d.w += gv[j].w * xv[j].w * s;
+        mydw[c] = d;
+      }
+    }
+  }
+  __syncthreads();
+  float4* p4 = reinterpret_cast<float4*>(partial) + static_cast<int64_t>(blockIdx.x) * H4;
+  for (int c = threadIdx.x; c < H4; c += blockDim.x) {
+    float4 t = sdw4[c];
+#pragma unroll
+    for (int k2 = 1; k2 < 8; ++k2) {
+      const float4 u = sdw4[k2 * H4 + c];
+      t.x += u.x;
+      t.y += u.y;
+      t.z += u.z;
+      t.w += u.w;
+    }
+    p4[c] = t;
+  }
+}
+
 // Generic backward (any H): partial sums accumulated in the CTA's own partial row in global
 // memory (each element is owned by one thread, so no atomics are needed).
 __global__ void __launch_bounds__(256)
@@ -592,10 +678,24 @@ int ctdk_rmsnorm_bwd(const float* dy, const float* x, const float* w, float* dx,
   void* prof = prof_begin(CTDK_PROF_NORM_BWD, (add_to_dx ? 16.0 : 12.0) * static_cast<double>(rows) * H, s);
   int64_t cap = static_cast<int64_t>(sm_count()) * 8;
   if (cap > kNormPartialRows) cap = kNormPartialRows;
-  const int grid = static_cast<int>(rows < cap ? rows : cap);
+  int grid = static_cast<int>(rows < cap ? rows : cap);
   const bool vec = (H % 4 == 0) && aligned16(dy) && aligned16(x) && aligned16(w) &&
                    aligned16(dx) && aligned16(dw_scratch) && H <= 4096;
-  if (vec) {
+  if (vec && H <= 1024 && rows >= 8 * static_cast<int64_t>(sm_count())) {
+    // one warp per row
+    const int H4 = H / 4;
+    int64_t g = (rows + 7) / 8;
+    const int64_t gcap = static_cast<int64_t>(sm_count()) * 2;
+    if (g > gcap) g = gcap;
+    grid = static_cast<int>(g);
+    const size_t smem = static_cast<size_t>(8) * H4 * sizeof(float4);
+    if (H4 <= 128)
+      launch_pdl(rmsnorm_bwd_rows_kernel<4>, dim3(grid), dim3(256), smem, s, dy, x, w, dx, dw_scratch, rows, H4,
+                 1.0f / static_cast<float>(H), eps, add_to_dx);
+    else
+      launch_pdl(rmsnorm_bwd_rows_kernel<8>, dim3(grid), dim3(256), smem, s, dy, x, w, dx, dw_scratch, rows, H4,
+                 1.0f / static_cast<float>(H), eps, add_to_dx);
+  } else if (vec) {
     const int H4 = H / 4;
     int threads = ((H4 + 31) / 32) * 32;
     if (threads > 256) threads = 256;
