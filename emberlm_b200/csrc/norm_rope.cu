@@ -905,8 +905,10 @@ int ctdk_qk_norm_rope_bwd(float* dqkv, const float* qkv_pre, const float* wq, co
   CTDK_REQUIRE(!has_norm || (qkv_pre && rstd_q && rstd_k && dwq && dwk && scratch),
                "ctdk_qk_norm_rope_bwd: QK-Norm needs qkv_pre, rstd, dw and scratch");
   const int64_t items = rows * (H + Hk);
-  int64_t cap = static_cast<int64_t>(sm_count()) * 3;
-  if (cap > kMaxPartialRows) cap = kMaxPartialRows;
+  // with QK-Norm every CTA leaves a dw partial row, so the grid is kept small; without it the grid only
+  // has to fill the SMs
+  int64_t cap = static_cast<int64_t>(sm_count()) * (has_norm ? 3 : 8);
+  if (has_norm && cap > kMaxPartialRows) cap = kMaxPartialRows;
   const int per_cta = 256 / (D / 8);
   const int64_t need = (items + per_cta - 1) / per_cta;
   const int grid = static_cast<int>(need < cap ? need : cap);
