@@ -59,6 +59,107 @@ __global__ void __launch_bounds__(256)
   }
 }
 
+// The same for rows that fit in the registers of one CTA (V <= 512 * 4 * NV, 16-byte aligned rows,
+// in-place dlogits): every logit of the row is requested at once (NV float4 per thread in flight,
+// i.e. the whole row), max and sum are formed from registers, and the rewrite needs no second read.
+// Rows whose weight is 0 and whose loss is masked are zero-filled without being read.
+template <int NV>
+__global__ void __launch_bounds__(512, 1)
+    ce_masked_rows_kernel(float* __restrict__ logits, const int64_t* __restrict__ targets,
+                          const float* __restrict__ loss_mask, const float* __restrict__ row_weight,
+                          float* __restrict__ loss_sum, float* __restrict__ lse_out, int64_t n, int64_t V) {
+  __shared__ float s_red[16];
+  __shared__ float s_out;
+  const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+  const int V4 = static_cast<int>(V >> 2);
+  auto block_reduce = [&](float v, bool is_max) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float u = __shfl_xor_sync(0xffffffffu, v, o);
+      v = is_max ? fmaxf(v, u) : v + u;
+    }
+    if (lane == 0) s_red[wid] = v;
+    __syncthreads();
+    if (wid == 0) {
+      float t = lane < 16 ? s_red[lane] : (is_max ? -FLT_MAX : 0.0f);
+#pragma unroll
+      for (int o = 8; o > 0; o >>= 1) {
+        const float u = __shfl_xor_sync(0xffffffffu, t, o);
+        t = is_max ? fmaxf(t, u) : t + u;
+      }
+      if (lane == 0) s_out = t;
+    }
+    __syncthreads();
+    const float r = s_out;
+    __syncthreads();   // s_red / s_out are reused
+    return r;
+  };
+  for (int64_t row = blockIdx.x; row < n; row += gridDim.x) {
+    float4* z4 = reinterpret_cast<float4*>(logits + row * V);
+    const float mk = loss_mask != nullptr ? loss_mask[row] : 1.0f;
+    const float rw = row_weight[row];
+    const bool need_fwd = (mk != 0.0f) || (lse_out != nullptr) || (rw != 0.0f);
+    if (!need_fwd) {
+      for (int i = threadIdx.x; i < V4; i += blockDim.x) z4[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+      continue;
+    }
+    float4 x[NV];
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
+      const int i = threadIdx.x + j * 512;
+      x[j] = i < V4 ? z4[i] : make_float4(-FLT_MAX, -FLT_MAX, -FLT_MAX, -FLT_MAX);
+    }
+    float m = -FLT_MAX;
+#pragma unroll
+    for (int j = 0; j < NV; ++j) m = fmaxf(m, fmaxf(fmaxf(x[j].x, x[j].y), fmaxf(x[j].z, x[j].w)));
+    m = block_reduce(m, true);
+    float sum = 0.0f;
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
+      // exp(x - m) is kept: it is the numerator of the probability written below
+      x[j].x = __expf(x[j].x - m);
+      x[j].y = __expf(x[j].y - m);
+      x[j].z = __expf(x[j].z - m);
+      x[j].w = __expf(x[j].w - m);
+      sum += (x[j].x + x[j].y) + (x[j].z + x[j].w);   // padding: exp(-FLT_MAX - m) = 0
+    }
+    sum = block_reduce(sum, false);
+    const int64_t tgt = targets[row];
+    if (threadIdx.x == 0) {
+      const float lse = m + logf(sum);
+      if (lse_out != nullptr) lse_out[row] = lse;
+      if (mk != 0.0f) {
+        // the target's logit is still in memory: the row is rewritten only after this read (bar.sync below)
+        const float zt = (tgt >= 0 && tgt < V) ? logits[row * V + tgt] : 0.0f;
+        atomicAdd(&loss_sum[0], mk * (lse - zt));
+        atomicAdd(&loss_sum[1], mk);
+      }
+    }
+    __syncthreads();
+    if (rw == 0.0f) {
+      for (int i = threadIdx.x; i < V4; i += blockDim.x) z4[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+    } else {
+      const float sc = rw / sum;
+#pragma unroll
+      for (int j = 0; j < NV; ++j) {
+        const int i = threadIdx.x + j * 512;
+        if (i < V4) {
+          float4 o = make_float4(x[j].x * sc, x[j].y * sc, x[j].z * sc, x[j].w * sc);
+          const int64_t c = static_cast<int64_t>(i) << 2;
+          if (tgt >= c && tgt < c + 4) {
+            const int k = static_cast<int>(tgt - c);
+            if (k == 0) o.x -= rw;
+            else if (k == 1) o.y -= rw;
+            else if (k == 2) o.z -= rw;
+            else o.w -= rw;
+          }
+          z4[i] = o;
+        }
+      }
+    }
+  }
+}
+
 // One CTA per row. Pass 1: online (max, sum) over the row. Pass 2 (optional): rewrite the
 // row as row_weight*(p - onehot). Rows whose weight is 0 are zero-filled without being read.
 __global__ void __launch_bounds__(512)
@@ -304,9 +405,18 @@ int ctdk_ce_masked(float* logits, const int64_t* targets, const float* loss_mask
   // one read of every logit, one rewrite when the block becomes dlogits (all rows counted: the
   // engine compacts the supervised rows before the head, so every row of a block is live)
   void* prof = prof_begin(CTDK_PROF_CE, (dlogits_inplace ? 8.0 : 4.0) * static_cast<double>(n) * V, static_cast<cudaStream_t>(stream));
-  ce_masked_kernel<<<static_cast<int>(n < cap ? n : cap), 512, 0,
-                     static_cast<cudaStream_t>(stream)>>>(
-      logits, targets, loss_mask, row_weight, loss_sum, lse_out, n, V, dlogits_inplace, vec);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int64_t cap1 = static_cast<int64_t>(sm_count());
+  const unsigned g1 = static_cast<unsigned>(n < cap1 ? n : cap1);
+  if (vec && dlogits_inplace && V <= 512 * 4 * 8)
+    ce_masked_rows_kernel<8><<<g1, 512, 0, st>>>(logits, targets, loss_mask, row_weight, loss_sum, lse_out, n, V);
+  else if (vec && dlogits_inplace && V <= 512 * 4 * 16)
+    ce_masked_rows_kernel<16><<<g1, 512, 0, st>>>(logits, targets, loss_mask, row_weight, loss_sum, lse_out, n, V);
+  else if (vec && dlogits_inplace && V <= 512 * 4 * 24)
+    ce_masked_rows_kernel<24><<<g1, 512, 0, st>>>(logits, targets, loss_mask, row_weight, loss_sum, lse_out, n, V);
+  else
+    ce_masked_kernel<<<static_cast<int>(n < cap ? n : cap), 512, 0, st>>>(
+        logits, targets, loss_mask, row_weight, loss_sum, lse_out, n, V, dlogits_inplace, vec);
   prof_end(prof, static_cast<cudaStream_t>(stream));
   return check_launch("ctdk_ce_masked");
 }
