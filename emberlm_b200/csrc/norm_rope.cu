@@ -788,13 +788,26 @@ int ctdk_rmsnorm_bwd_static(const float* dy, const float* x, const float* w, flo
   if (rc != CTDK_OK) return rc;
   int64_t cap = static_cast<int64_t>(sm_count()) * 2;
   if (cap > kStaticRows) cap = kStaticRows;
-  const int grid = static_cast<int>(rows < cap ? rows : cap);
+  int grid = static_cast<int>(rows < cap ? rows : cap);
   // Nothing in the array has to start at zero: each of the `grid` CTAs overwrites its whole
   // partial row (the generic kernel zeroes its row itself) and the finalize pass reads only
   // those rows, so contents left by an earlier call are never observed.
   const bool vec =
       (H % 4 == 0) && aligned16(dy) && aligned16(x) && aligned16(w) && aligned16(dx);
-  if (vec) {
+  if (vec && H <= 1024 && rows >= 8 * static_cast<int64_t>(sm_count())) {
+    // one warp per row, as ctdk_rmsnorm_bwd does for these shapes (dx is then bit-identical to it:
+    // a row's result does not depend on the grid)
+    const int H4 = H / 4;
+    const int64_t g = (rows + 7) / 8;
+    grid = static_cast<int>(g < cap ? g : cap);
+    const size_t smem = static_cast<size_t>(8) * H4 * sizeof(float4);
+    if (H4 <= 128)
+      launch_pdl(rmsnorm_bwd_rows_kernel<4>, dim3(grid), dim3(256), smem, s, dy, x, w, dx, scratch, rows, H4,
+                 1.0f / static_cast<float>(H), eps, add_to_dx);
+    else
+      launch_pdl(rmsnorm_bwd_rows_kernel<8>, dim3(grid), dim3(256), smem, s, dy, x, w, dx, scratch, rows, H4,
+                 1.0f / static_cast<float>(H), eps, add_to_dx);
+  } else if (vec) {
     const int H4 = H / 4;
     int threads = ((H4 + 31) / 32) * 32;
     if (threads > 256) threads = 256;
