@@ -162,7 +162,7 @@ __global__ void __launch_bounds__(512, 1)
 
 // One CTA per row. Pass 1: online (max, sum) over the row. Pass 2 (optional): rewrite the
 // row as row_weight*(p - onehot). Rows whose weight is 0 are zero-filled without being read.
-__global__ void __launch_bounds__(512)
+__global__ void __launch_bounds__(512, 2)
     ce_masked_kernel(float* __restrict__ logits, const int64_t* __restrict__ targets,
                      const float* __restrict__ loss_mask, const float* __restrict__ row_weight,
                      float* __restrict__ loss_sum, float* __restrict__ lse_out, int64_t n,
@@ -187,7 +187,24 @@ __global__ void __launch_bounds__(512)
       };
       if (vec_ok) {
         const float4* z4 = reinterpret_cast<const float4*>(z);
-        for (int64_t i = threadIdx.x; i < (V >> 2); i += blockDim.x) {
+        const int64_t V4 = V >> 2, bd = blockDim.x;
+        int64_t i = threadIdx.x;
+        // four loads in flight per thread before the (serial) running max / sum takes them in
+        for (; i + 3 * bd < V4; i += 4 * bd) {
+          float4 x[4];
+#pragma unroll
+          for (int u = 0; u < 4; ++u) x[u] = z4[i + u * bd];
+          float mx = m;
+#pragma unroll
+          for (int u = 0; u < 4; ++u) mx = fmaxf(mx, fmaxf(fmaxf(x[u].x, x[u].y), fmaxf(x[u].z, x[u].w)));
+          if (mx > m) {
+            s *= __expf(m - mx);
+            m = mx;
+          }
+#pragma unroll
+          for (int u = 0; u < 4; ++u) s += __expf(x[u].x - m) + __expf(x[u].y - m) + __expf(x[u].z - m) + __expf(x[u].w - m);
+        }
+        for (; i < V4; i += bd) {
           const float4 x = z4[i];
           const float mx = fmaxf(fmaxf(x.x, x.y), fmaxf(x.z, x.w));
           if (mx > m) {
@@ -254,6 +271,7 @@ __global__ void __launch_bounds__(512)
         const int64_t tgt = targets[row];
         if (vec_ok) {
           float4* z4 = reinterpret_cast<float4*>(z);
+#pragma unroll 4
           for (int64_t i = threadIdx.x; i < (V >> 2); i += blockDim.x) {
             float4 x = z4[i];
             x.x = __expf(x.x - lse);
